@@ -1,0 +1,102 @@
+// RMSNorm fused with what feeds it: the residual add, the embedding lookup and a
+// row gather.  All arithmetic is fp32; one rounding at the store.
+//
+//   v   = (ids ? table[ids[r]] : resid[r]) + (pending ? pending[r] : 0)      (fp32)
+//   resid[r] = v                                  (when write_resid)
+//   out[i]  = (v * rsqrt(mean(v^2) + eps)) * w    (qwen3_runtime/layers/ops.py:17-37)
+//
+// `rows` (optional) selects which source rows are processed; output row i then
+// comes from source row rows[i] (used for the final norm, which only runs on the
+// rows whose logits are wanted, qwen3_runtime/models/qwen3.py:263-264).
+#include "common.cuh"
+
+template <typename T>
+__global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restrict__ resid,
+                                  const int* __restrict__ ids, const T* __restrict__ table,
+                                  const int* __restrict__ rows, const float* __restrict__ w,
+                                  T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+  extern __shared__ float vals[];  // H floats, then 33 for the reduction
+  float* red = vals + H;
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  const T* trow = nullptr;
+  if (ids) {
+    int id = ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    trow = table + (long)id * H;
+  }
+  const T* prow = pending ? pending + src * H : nullptr;
+  float* rrow = resid ? resid + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = trow ? to_f32(trow[i]) : rrow[i];
+    if (prow) v += to_f32(prow[i]);
+    if (write_resid) rrow[i] = v;
+    vals[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = rsqrtf(total / (float)H + eps);
+  T* orow = out + (long)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>((vals[i] * rstd) * w[i]);
+}
+
+template <typename T>
+static int launch_fused_norm(const void* pending, float* resid, const int* ids, const void* table,
+                             const int* rows, const float* w, void* out, int num_rows, int H, float eps,
+                             int write_resid, int vocab, cudaStream_t stream) {
+  if (num_rows == 0) return Q3_OK;
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(fused_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  fused_norm_kernel<T><<<num_rows, threads, smem, stream>>>(
+      (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
+  return q3_launch_status();
+}
+
+// out[num_rows, H]; resid fp32 [*, H] (may be null only when ids is given and
+// write_resid is 0); pending/table/out have `dtype`; w is fp32 [H].
+Q3_EXPORT int q3_fused_norm(int dtype, const void* pending, float* resid, const int* ids, const void* table,
+                            const int* rows, const float* w, void* out, int num_rows, int H, float eps,
+                            int write_resid, int vocab, cudaStream_t stream) {
+  if (!w || !out || H < 1) return Q3_ERR_ARGUMENT;
+  if (!ids && !resid) return Q3_ERR_ARGUMENT;
+  if (ids && !table) return Q3_ERR_ARGUMENT;
+  if (write_resid && !resid) return Q3_ERR_ARGUMENT;
+  if (dtype == Q3_DTYPE_F32)
+    return launch_fused_norm<float>(pending, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
+                                    vocab, stream);
+  if (dtype == Q3_DTYPE_BF16)
+    return launch_fused_norm<bf16>(pending, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
+                                   vocab, stream);
+  return Q3_ERR_ARGUMENT;
+}
+
+// ---- SwiGLU product: out[t, i] = silu(gu[t, i]) * gu[t, I + i]  (layers/ops.py:23-25) ----
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / I;
+  const int i = (int)(idx - t * I);
+  const float g = to_f32(gu[t * 2 * I + i]);
+  const float u = to_f32(gu[t * 2 * I + I + i]);
+  out[idx] = from_f32<T>((g / (1.f + expf(-g))) * u);
+}
+
+Q3_EXPORT int q3_silu_mul(int dtype, const void* gu, void* out, int num_rows, int I, cudaStream_t stream) {
+  if (!gu || !out || I < 1) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * I;
+  if (total == 0) return Q3_OK;
+  const int threads = 256;
+  const long blocks = (total + threads - 1) / threads;
+  if (dtype == Q3_DTYPE_F32)
+    silu_mul_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I);
+  else if (dtype == Q3_DTYPE_BF16)
+    silu_mul_kernel<bf16><<<(unsigned)blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, total, I);
+  else
+    return Q3_ERR_ARGUMENT;
+  return q3_launch_status();
+}

@@ -1,0 +1,113 @@
+// Per-head q/k RMSNorm, rotary position encoding and the write of keys and values
+// into their cache pages, in one pass over the QKV projection's output.
+//
+// One warp handles one (token, head).  For a q or k head (models/qwen3.py:101-103):
+//   y = (x * rsqrt(mean(x^2) + eps)) * w          over the head's D values, fp32
+//   rotate-half on the first 2*rot_half dims with cos/sin[position] (layers/rope.py:7-11)
+// q is written back in place (the attention kernels read it from the QKV buffer);
+// k goes to its slot of the key pages; v heads are copied to the value pages
+// unchanged (kv/paged.py:74-84).  Slot of position p: page = block_table[seq][p / ps],
+// row p % ps.  Page layout [pages, kv_heads, page_size, D].
+#include "common.cuh"
+
+template <typename T, int WARPS>
+__global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, int nq, int nkv, int D,
+                                          const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                          float eps, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, int rot_half, int max_pos,
+                                          const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                          const int* __restrict__ block_table, int max_pages,
+                                          T* __restrict__ kpages, T* __restrict__ vpages, int ps,
+                                          int num_tokens, int write_kv) {
+  extern __shared__ float stage[];  // WARPS * D
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = write_kv ? nq + 2 * nkv : nq;
+  const long item = (long)blockIdx.x * WARPS + warp;
+  if (item >= (long)num_tokens * heads) return;
+  const int t = (int)(item / heads);
+  const int hi = (int)(item - (long)t * heads);
+  T* x = qkv + (long)t * row_stride + (long)hi * D;
+  int p = positions[t];
+  long cache_row = 0;
+  if (hi >= nq) {
+    const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
+    const int page = block_table[(long)token_seq[t] * max_pages + p / ps];
+    cache_row = (((long)page * nkv + kvh) * ps + (p % ps)) * D;
+  }
+  if (hi >= nq + nkv) {  // value head: plain copy
+    T* dst = vpages + cache_row;
+    for (int d = lane; d < D; d += 32) dst[d] = x[d];
+    return;
+  }
+  float* xs = stage + warp * D;
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = to_f32(x[d]);
+    xs[d] = v;
+    ss += v * v;
+  }
+  const float* w = hi < nq ? q_w : k_w;
+  const float rstd = w ? rsqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
+  __syncwarp();
+  if (p >= max_pos) p = max_pos - 1;
+  const float* cs = cos_t ? cos_t + (long)p * rot_half : nullptr;
+  const float* sn = cos_t ? sin_t + (long)p * rot_half : nullptr;
+  T* dst = hi < nq ? x : kpages + cache_row;
+  for (int d = lane; d < D; d += 32) {
+    float y = w ? (xs[d] * rstd) * w[d] : xs[d];
+    if (cs && d < 2 * rot_half) {
+      const int i = d < rot_half ? d : d - rot_half;
+      const int pd = d < rot_half ? d + rot_half : d - rot_half;
+      const float yp = w ? (xs[pd] * rstd) * w[pd] : xs[pd];
+      y = d < rot_half ? y * cs[i] - yp * sn[i] : y * cs[i] + yp * sn[i];
+    }
+    dst[d] = from_f32<T>(y);
+  }
+}
+
+Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq, int nkv, int D,
+                                    const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                    const float* sin_t, int rot_half, int max_pos, const int* positions,
+                                    const int* token_seq, const int* block_table, int max_pages, void* kpages,
+                                    void* vpages, int ps, int num_tokens, int write_kv, cudaStream_t stream) {
+  if (!qkv || !positions || nq < 1 || nkv < 1 || D < 1) return Q3_ERR_ARGUMENT;
+  if (write_kv && (!token_seq || !block_table || !kpages || !vpages || ps < 1)) return Q3_ERR_ARGUMENT;
+  if (cos_t && (!sin_t || rot_half < 1 || 2 * rot_half > D)) return Q3_ERR_ARGUMENT;
+  if (num_tokens == 0) return Q3_OK;
+  constexpr int WARPS = 4;
+  const size_t smem = (size_t)WARPS * D * sizeof(float);
+  if (smem > 48 * 1024) return Q3_ERR_UNSUPPORTED;
+  const long items = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq);
+  const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+  if (dtype == Q3_DTYPE_F32)
+    qk_norm_rope_store_kernel<float, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
+        (float*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, rot_half, max_pos, positions,
+        token_seq, block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+  else if (dtype == Q3_DTYPE_BF16)
+    qk_norm_rope_store_kernel<bf16, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
+        (bf16*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, rot_half, max_pos, positions,
+        token_seq, block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+  else
+    return Q3_ERR_ARGUMENT;
+  return q3_launch_status();
+}
+
+// cos/sin tables [max_pos, half]: angle = float(p) * inv_freq[j], as an fp32 product
+// (layers/rope.py:17-22); accurate cosf/sinf (this file is never built with fast math).
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ cos_t,
+                                  float* __restrict__ sin_t, int max_pos, int half) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)max_pos * half) return;
+  const int p = (int)(idx / half), j = (int)(idx % half);
+  const float angle = (float)p * inv_freq[j];
+  cos_t[idx] = cosf(angle);
+  sin_t[idx] = sinf(angle);
+}
+
+Q3_EXPORT int q3_rope_table(const float* inv_freq, float* cos_t, float* sin_t, int max_pos, int half,
+                            cudaStream_t stream) {
+  if (!inv_freq || !cos_t || !sin_t || max_pos < 1 || half < 1) return Q3_ERR_ARGUMENT;
+  const long total = (long)max_pos * half;
+  rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, cos_t, sin_t, max_pos, half);
+  return q3_launch_status();
+}

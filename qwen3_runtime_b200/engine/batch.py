@@ -1,0 +1,182 @@
+"""From ``(request, its next tokens, wanted places)`` to the device arrays of a step.
+
+All integer metadata of a step is packed into one pinned host buffer and copied to
+the device with a single transfer; the parts see slices of that device buffer.
+Parity: qwen3_runtime/engine/batch.py:45-60 (ids, positions, cu_seqlens, kv_lens,
+block tables, rows that get logits) -- here as int32 arrays on the device, and with
+explicit wanted places instead of "the last row if the request caught up".
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..parts.base import StepContext
+
+
+class BatchError(ValueError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next ``tokens`` (they follow what the cache
+    already holds for it) and ``want``, indices into ``tokens`` whose logits are asked for."""
+
+    cache: RequestCache
+    tokens: list[int]
+    want: list[int]
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+class BatchBuilder:
+    RING = 4  # pinned staging buffers in flight
+
+    def __init__(self, cache: CacheManager, device, *, vocab_size: int, max_positions: int):
+        self.cache = cache
+        self.device = device
+        self.vocab_size = vocab_size
+        self.max_positions = max_positions
+        self._host: list[torch.Tensor] = []
+        self._events: list[torch.cuda.Event | None] = []
+        self._dev: torch.Tensor | None = None
+        self._turn = 0
+        self._capacity = 0
+        self.pin = torch.device(device).type == "cuda"
+
+    def _buffers(self, need: int):
+        if need > self._capacity:
+            self._capacity = max(4096, 1 << (need - 1).bit_length())
+            self._host = [torch.empty(self._capacity, dtype=torch.int32, pin_memory=self.pin)
+                          for _ in range(self.RING)]
+            self._events = [None] * self.RING
+            self._dev = torch.empty(self._capacity, dtype=torch.int32, device=self.device)
+        self._turn = (self._turn + 1) % self.RING
+        ev = self._events[self._turn]
+        if ev is not None:
+            ev.synchronize()
+        return self._host[self._turn], self._dev
+
+    def build(self, entries: list[StepEntry], *, pad_to: int | None = None, table_width: int | None = None,
+              scratch_page: int = 0, scratch_slot: int = 0, device_buffer: torch.Tensor | None = None,
+              all_rows: bool = False) -> StepContext:
+        """Pack a step.  ``pad_to`` appends dummy one-token sequences (writing to the
+        scratch page) so that a decode batch fills a captured batch size; ``table_width``
+        fixes the block-table width; ``device_buffer`` is a preallocated int32 buffer that
+        the metadata is copied into (captured steps read from fixed addresses)."""
+        if not entries:
+            raise BatchError("a step needs at least one entry")
+        ps = self.cache.page_size
+        n_paged = len(self.cache.paged_groups)
+        B_real = len(entries)
+        B = max(B_real, pad_to or 0)
+        ids: list[int] = []
+        lens = []
+        for e in entries:
+            n = len(e.tokens)
+            if n < 1:
+                raise BatchError(f"request {e.cache.request_id!r} brings no tokens")
+            start = e.cache.num_computed
+            if start + n > e.cache.num_reserved:
+                raise BatchError(f"request {e.cache.request_id!r}: pages are reserved for "
+                                 f"{e.cache.num_reserved} tokens, the step needs {start + n}")
+            if start + n > self.max_positions:
+                raise BatchError(f"request {e.cache.request_id!r} would reach position {start + n - 1}; "
+                                 f"the model's position encoding covers {self.max_positions}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise BatchError(f"request {e.cache.request_id!r}: wanted place {w} is outside its {n} tokens")
+            ids.extend(e.tokens)
+            lens.append(n)
+        T_real = len(ids)
+        T = T_real + (B - B_real)
+        ids_np = np.asarray(ids, dtype=np.int64)
+        if ids_np.size and (ids_np.min() < 0 or ids_np.max() >= self.vocab_size):
+            bad = int(ids_np[(ids_np < 0) | (ids_np >= self.vocab_size)][0])
+            raise BatchError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+        width = max(1, max((len(t) for e in entries for t in e.cache.tables), default=1))
+        if table_width is not None:
+            if table_width < width:
+                raise BatchError("fixed block-table width is smaller than a request's table")
+            width = table_width
+        else:
+            width = _round_up(width, 8)
+        rows: list[int] = []
+        # section offsets inside the int32 buffer (each 4-int aligned => 16-byte aligned)
+        off, sections = 0, {}
+        for name, size in (("ids", T), ("pos", T), ("seq", T), ("cu", B + 1), ("kv", B), ("slot", B),
+                           ("rows", T), *[(f"bt{g}", B * width) for g in range(n_paged)]):
+            sections[name] = (off, size)
+            off += _round_up(size, 4)
+        host, dev = self._buffers(off)
+        if device_buffer is not None:
+            if device_buffer.numel() < off:
+                raise BatchError("preallocated step buffer is too small")
+            dev = device_buffer
+        h = host.numpy()
+
+        def sec(name):
+            o, s = sections[name]
+            return h[o:o + s]
+
+        sec("ids")[:T_real] = ids_np
+        sec("ids")[T_real:] = 0
+        pos, seq, cu, kv, slot = sec("pos"), sec("seq"), sec("cu"), sec("kv"), sec("slot")
+        cu[0] = 0
+        t = 0
+        for b, (e, n) in enumerate(zip(entries, lens)):
+            start = e.cache.num_computed
+            pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+            seq[t:t + n] = b
+            rows.extend(t + w for w in e.want)
+            t += n
+            cu[b + 1] = t
+            kv[b] = start + n
+            slot[b] = e.cache.slot
+            for g in range(n_paged):
+                bt = sec(f"bt{g}")[b * width:(b + 1) * width]
+                table = e.cache.tables[g]
+                bt[:len(table)] = table
+                bt[len(table):] = scratch_page
+        for b in range(B_real, B):  # padding rows: one token at position 0 of the scratch page
+            pos[t] = 0
+            seq[t] = b
+            t += 1
+            cu[b + 1] = t
+            kv[b] = 1
+            slot[b] = scratch_slot
+            for g in range(n_paged):
+                sec(f"bt{g}")[b * width:(b + 1) * width] = scratch_page
+        if all_rows:
+            rows_np = np.arange(T, dtype=np.int32)
+        else:
+            rows_np = np.asarray(rows, dtype=np.int32)
+        R = int(rows_np.size)
+        sec("rows")[:R] = rows_np
+        dev[:off].copy_(host[:off], non_blocking=True)
+        if self.pin:
+            ev = self._events[self._turn] or torch.cuda.Event()
+            ev.record()
+            self._events[self._turn] = ev
+
+        def dsec(name, size=None):
+            o, s = sections[name]
+            return dev[o:o + (s if size is None else size)]
+
+        return StepContext(
+            num_tokens=T, num_seqs=B,
+            token_ids=dsec("ids"), positions=dsec("pos"), token_seq=dsec("seq"), cu_seqlens=dsec("cu"),
+            kv_lens=dsec("kv"), state_slots=dsec("slot"),
+            block_tables=[dsec(f"bt{g}").view(B, width) for g in range(n_paged)],
+            logit_rows=dsec("rows", R), num_logit_rows=R,
+            max_query_len=max(lens), max_kv_len=int(kv[:B].max()),
+            decode_only=all(n == 1 for n in lens),
+            host_cu_seqlens=[int(x) for x in cu], host_kv_lens=[int(x) for x in kv[:B]],
+        )

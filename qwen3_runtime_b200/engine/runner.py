@@ -1,0 +1,59 @@
+"""The step function.
+
+``ModelRunner.run(entries)`` takes a batch of (request, its next tokens, wanted
+places) -- portions of prompts beside single decoded tokens, cut anywhere -- runs
+exactly those tokens as one batch against the cache that earlier steps left, stores
+their keys and values, and returns float32 logits at the wanted places, in the order
+of the entries and of each entry's ``want``.  It samples nothing: the engine samples
+from what it returns, and trace replay writes it to disk.
+Parity: qwen3_runtime/engine/model_runner.py:107-192 (``run`` / ``run_logits`` /
+``_run_group``); there is no prefill/decode split here, one launch sequence serves
+every mix.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..parts.model import DecoderModel
+from .batch import BatchBuilder, StepEntry
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage, *,
+                 max_positions: int, cuda_graph: bool = False, graph_batch_sizes=(1, 2, 4, 8, 16, 32, 64)):
+        self.model = model
+        self.cache = cache
+        self.storage = storage
+        self.device = model.ctx.device
+        self.builder = BatchBuilder(cache, self.device, vocab_size=model.spec.vocab_size,
+                                    max_positions=max_positions)
+        self.graphs = None
+        if cuda_graph:
+            from .graph import DecodeGraphs
+
+            self.graphs = DecodeGraphs(self, graph_batch_sizes)
+        self.num_steps = 0
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """One step; returns logits ``[sum(len(want)), vocab]`` float32, or None."""
+        resets = [e.cache.slot for e in entries if e.cache.needs_state_reset]
+        if resets:
+            self.storage.zero_state_slots(resets)
+            for e in entries:
+                e.cache.needs_state_reset = False
+        logits = None
+        if self.graphs is not None:
+            logits = self.graphs.try_run(entries)
+        if logits is None:
+            step = self.builder.build(entries, scratch_page=self.storage.scratch_page,
+                                      scratch_slot=self.storage.scratch_slot)
+            logits = self.model.forward(step, self.storage)
+        else:
+            logits = logits if logits.numel() else None
+        for e in entries:
+            self.cache.commit(e.cache, len(e.tokens))
+        self.num_steps += 1
+        return logits

@@ -1,0 +1,3 @@
+"""Built-in architectures.  Importing this package registers them."""
+
+from . import qwen3  # noqa: F401

@@ -1,0 +1,213 @@
+"""The kernel table of the engine: thin Python wrappers over the ``extern "C"``
+launchers in ``csrc/``.
+
+There is one implementation per operation and no fallback: constructing
+:class:`CudaOps` without a CUDA device, or without a working nvcc to build the
+kernels, raises.  Wrappers check sizes and refuse, with a clear message, what a
+kernel does not support; they never substitute another code path silently.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+_CODES = {1: "unsupported size or option", 2: "CUDA launch failed", 3: "bad argument"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KernelsUnavailable(RuntimeError):
+    pass
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_CODES.get(code, code)}")
+
+
+_SIGNATURES = {
+    "norm": {
+        "q3_fused_norm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "q3_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    },
+    "rope_kv": {
+        "q3_qk_norm_rope_store": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                  c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "q3_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    },
+    "attention_generic": {
+        "q3_paged_attention_generic": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                       c_void_p],
+    },
+    "gemm_f32": {
+        "q3_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "sampling": {
+        "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    },
+}
+
+
+class CudaOps:
+    """Kernels on the current CUDA device.  ``groups`` are compiled up front (in
+    parallel); any other group is compiled when first used."""
+
+    name = "cuda-sm100a"
+
+    def __init__(self, groups: list[str] | None = None):
+        if not torch.cuda.is_available():
+            raise KernelsUnavailable(
+                "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
+                "no CUDA device is visible and there is no CPU path"
+            )
+        major, _minor = torch.cuda.get_device_capability()
+        if major != 10:
+            raise KernelsUnavailable(
+                f"the kernels are compiled for sm_100a; this device reports sm_{major}{_minor}"
+            )
+        self._fn: dict[str, ctypes._CFuncPtr] = {}
+        if groups:
+            build.compile_groups([g for g in groups])
+
+    def prepare(self, groups: list[str]) -> None:
+        """Compile (in parallel) the kernel groups a model is going to use."""
+        build.compile_groups([g for g in groups if g in _SIGNATURES])
+
+    # ---- plumbing -------------------------------------------------------------------
+    def _get(self, group: str, name: str):
+        fn = self._fn.get(name)
+        if fn is None:
+            lib = build.load_group(group)
+            fn = getattr(lib, name)
+            fn.argtypes = _SIGNATURES[group][name]
+            fn.restype = c_int
+            self._fn[name] = fn
+        return fn
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    # ---- norms ----------------------------------------------------------------------
+    def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
+                   write_resid=True, num_rows=None):
+        """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu."""
+        H = weight.numel()
+        n = out.shape[0] if num_rows is None else num_rows
+        vocab = table.shape[0] if table is not None else 0
+        fn = self._get("norm", "q3_fused_norm")
+        _check(fn(_dtype_code(out.dtype), _ptr(pending), _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
+                  _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab, self._stream()),
+               f"fused_norm(H={H})")
+        return out
+
+    def silu_mul(self, gate_up, out):
+        I = out.shape[-1]
+        fn = self._get("norm", "q3_silu_mul")
+        _check(fn(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I, self._stream()), "silu_mul")
+        return out
+
+    # ---- position encoding + cache write -----------------------------------------------
+    def rope_table(self, inv_freq: torch.Tensor, max_positions: int):
+        half = inv_freq.numel()
+        cos = torch.empty((max_positions, half), dtype=torch.float32, device=inv_freq.device)
+        sin = torch.empty_like(cos)
+        fn = self._get("rope_kv", "q3_rope_table")
+        _check(fn(_ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half, self._stream()), "rope_table")
+        return cos, sin
+
+    def qk_norm_rope_store(self, qkv, *, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
+                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+        T = qkv.shape[0]
+        rot_half = cos.shape[1] if cos is not None else 0
+        max_pos = cos.shape[0] if cos is not None else 0
+        max_pages = block_table.shape[1] if block_table is not None else 0
+        if head_dim * 16 > 48 * 1024:
+            raise KernelError(f"qk_norm_rope_store: head_dim={head_dim} is too large (limit 3072)")
+        fn = self._get("rope_kv", "q3_qk_norm_rope_store")
+        _check(fn(_dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads, head_dim,
+                  _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
+                  _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages),
+                  page_size, T, int(bool(write_kv)), self._stream()), "qk_norm_rope_store")
+
+    # ---- attention --------------------------------------------------------------------
+    def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
+                        token_seq, positions, out, page_size, scale, window, step=None):
+        """Causal attention of every token of the step over its sequence's pages."""
+        T = out.shape[0]
+        if head_dim % 8 or head_dim > 256:
+            raise KernelError(
+                f"paged_attention: head_dim={head_dim} is not supported (multiples of 8 up to 256 are)")
+        fn = self._get("attention_generic", "q3_paged_attention_generic")
+        _check(fn(_dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                  block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,
+                  head_dim, page_size, float(scale), int(window or 0), self._stream()), "paged_attention")
+        return out
+
+    # ---- matrix products ----------------------------------------------------------------
+    def linear(self, x, weight, out=None, out_dtype=None):
+        """``x[M, K] @ weight[N, K]^T``.  float32: this engine's FMA kernel (no TF32).
+        bfloat16: the library product with fp32 accumulation, as the reference's
+        ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77, 134-135)."""
+        M, K = x.shape
+        N = weight.shape[0]
+        if weight.shape[1] != K:
+            raise KernelError(f"linear: x is [{M},{K}] but weight is {list(weight.shape)}")
+        if x.dtype == torch.float32:
+            if out is None:
+                out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+            fn = self._get("gemm_f32", "q3_gemm_f32")
+            _check(fn(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
+                      self._stream()), "gemm_f32")
+            return out
+        if out_dtype is not None and out_dtype != x.dtype:
+            return torch.mm(x, weight.t(), out_dtype=out_dtype)
+        if out is None:
+            return torch.mm(x, weight.t())
+        return torch.mm(x, weight.t(), out=out)
+
+    # ---- sampling ---------------------------------------------------------------------
+    def argmax(self, logits, want_logprob=False):
+        R, V = logits.shape
+        token = torch.empty(R, dtype=torch.int32, device=logits.device)
+        logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
+        fn = self._get("sampling", "q3_argmax")
+        _check(fn(_ptr(logits), R, V, _ptr(token), _ptr(logprob), self._stream()), "argmax")
+        return token, logprob
+
+    def sample(self, logits, temperature, uniform, want_logprob=False):
+        R, V = logits.shape
+        token = torch.empty(R, dtype=torch.int32, device=logits.device)
+        logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
+        fn = self._get("sampling", "q3_sample")
+        _check(fn(_ptr(logits), R, V, _ptr(temperature), _ptr(uniform), _ptr(token), _ptr(logprob),
+                  self._stream()), "sample")
+        return token, logprob
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

@@ -1,0 +1,97 @@
+"""Grouped-query attention over the paged cache.
+
+q/k/v projection (one fused product), optional per-head RMSNorm on q and k, position
+encoding on q and k, store of k and v into the cache pages, causal attention of every
+token over its sequence's pages (optionally only a window of them), output projection.
+Parity: qwen3_runtime/models/qwen3.py:62-127 and attention/pytorch.py:18-47.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.layout import KVLayerSpec
+from ..config.spec import PartSpec
+from .base import BuildContext, ParamSpec, Part, StepContext, build_part, register_part
+
+
+class PagedAttention(Part):
+    category = "mixer"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden_size = int(spec["hidden_size"])
+        self.num_heads = int(spec["num_heads"])
+        self.num_kv_heads = int(spec["num_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.qk_norm_eps = spec.get("qk_norm_eps")
+        self.window = spec.get("window") or None
+        self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ValueError(
+                f"head_dim={self.head_dim} is not supported: the attention kernels take multiples of 16 up to 256")
+        pos_spec = spec.get("position") or PartSpec("none")
+        self.position = build_part("position", pos_spec, ctx)
+        if self.position.style not in ("none", "neox"):
+            raise ValueError(f"the fused q/k kernel has no {self.position.style!r} position encoding")
+        self.q_size = self.num_heads * self.head_dim
+        self.kv_size = self.num_kv_heads * self.head_dim
+        self.qkv_weight = self.o_weight = self.q_norm_weight = self.k_norm_weight = None
+
+    def param_specs(self):
+        specs = {
+            "q_proj.weight": ParamSpec((self.q_size, self.hidden_size)),
+            "k_proj.weight": ParamSpec((self.kv_size, self.hidden_size)),
+            "v_proj.weight": ParamSpec((self.kv_size, self.hidden_size)),
+            "o_proj.weight": ParamSpec((self.hidden_size, self.q_size)),
+        }
+        if self.qk_norm_eps is not None:
+            specs["q_norm.weight"] = ParamSpec((self.head_dim,), "vector")
+            specs["k_norm.weight"] = ParamSpec((self.head_dim,), "vector")
+        return specs
+
+    def load(self, tensors):
+        # one product for q, k and v: rows of q, then k, then v (utils/loader.py:44-47)
+        self.qkv_weight = torch.cat(
+            [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0).contiguous()
+        self.o_weight = tensors["o_proj.weight"].contiguous()
+        self.q_norm_weight = tensors.get("q_norm.weight")
+        self.k_norm_weight = tensors.get("k_norm.weight")
+
+    def kernel_groups(self):
+        groups = ["rope_kv", "attention_generic", *self.position.kernel_groups()]
+        if self.ctx.dtype == torch.float32:
+            groups.append("gemm_f32")
+        return groups
+
+    def cache_spec(self):
+        return KVLayerSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
+        ops = self.ops
+        T = h.shape[0]
+        weight = self.qkv_weight if cache.writes else self.qkv_weight[: self.q_size]
+        qkv = ops.linear(h, weight)
+        tables = self.position.rotation_tables()
+        cos, sin = tables if tables is not None else (None, None)
+        block_table = step.block_tables[cache.paged_index]
+        ops.qk_norm_rope_store(
+            qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+            q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
+            eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos=cos, sin=sin,
+            positions=step.positions, token_seq=step.token_seq, block_table=block_table,
+            k_pages=cache.k_pages, v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
+        ctx_out = torch.empty((T, self.q_size), dtype=h.dtype, device=h.device)
+        ops.paged_attention(
+            qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+            head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,
+            token_seq=step.token_seq, positions=step.positions, out=ctx_out, page_size=cache.page_size,
+            scale=self.scale, window=self.window, step=step)
+        return ops.linear(ctx_out, self.o_weight)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

@@ -1,0 +1,127 @@
+"""What every part is, and the registry that finds a part class by category and kind.
+
+Categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``block``.  A part is
+built from a :class:`PartSpec` (its sizes and constants) and a :class:`BuildContext`
+(dtype, device, kernel table); it declares its tensors with :meth:`Part.param_specs`
+(names relative to the part's own prefix) and receives them, already on the device,
+in :meth:`Part.load`.  Registering a new kind is one :func:`register_part` call, which
+a test or an extension can make without touching this package.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from ..config.spec import PartSpec
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """A stored tensor a part needs.  ``kind`` decides how it is kept on the device:
+
+    ``matrix``  -- operand of a matrix product or lookup table: the compute dtype;
+    ``vector``  -- small per-channel parameter: float32 (a lossless copy of bfloat16
+                   storage; a tensor stored in 32-bit stays 32-bit);
+    ``int``     -- integer table: int32.
+    """
+
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+
+
+@dataclass
+class BuildContext:
+    dtype: torch.dtype
+    device: torch.device
+    ops: Any  # the kernel table (qwen3_runtime_b200.ops.cuda.CudaOps in production)
+    shared: dict = field(default_factory=dict)  # tables shared between parts (e.g. rotary cos/sin)
+
+
+@dataclass
+class StepContext:
+    """The batch of one step as the parts see it (device tensors are int32)."""
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T] absolute position of each token in its sequence
+    token_seq: torch.Tensor  # [T] row of the batch (sequence) each token belongs to
+    cu_seqlens: torch.Tensor  # [B + 1] first token of each sequence in the packed batch
+    kv_lens: torch.Tensor  # [B] tokens in the cache after this step
+    state_slots: torch.Tensor  # [B] fixed-size state slot of each sequence
+    block_tables: list[torch.Tensor]  # per paged cache group: [B, max_pages]
+    logit_rows: torch.Tensor  # [R] packed rows whose logits are wanted
+    num_logit_rows: int
+    max_query_len: int  # host copies of batch extremes, for kernel choice
+    max_kv_len: int
+    decode_only: bool  # every sequence brings exactly one token
+    # host copies (lists) for parts that need them without a device read
+    host_cu_seqlens: list[int] = field(default_factory=list)
+    host_kv_lens: list[int] = field(default_factory=list)
+    extras: dict = field(default_factory=dict)  # per-step scratch shared by the layers of a step
+
+
+class Part:
+    category = ""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+        self.ops = ctx.ops
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no tensors")
+
+    def kernel_groups(self) -> list[str]:
+        """CUDA source groups this part launches (compiled before the first step)."""
+        return []
+
+
+_REGISTRY: dict[tuple[str, str], Callable[[PartSpec, BuildContext], Part]] = {}
+
+
+def register_part(category: str, kind: str, factory: Callable[[PartSpec, BuildContext], Part],
+                  *, replace: bool = False) -> None:
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category {category!r}; one of {CATEGORIES}")
+    if (category, kind) in _REGISTRY and not replace:
+        raise ValueError(f"{category} part {kind!r} is already registered")
+    _REGISTRY[(category, kind)] = factory
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY.pop((category, kind), None)
+
+
+def build_part(category: str, spec: PartSpec, ctx: BuildContext) -> Part:
+    try:
+        factory = _REGISTRY[(category, spec.kind)]
+    except KeyError:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise ValueError(f"no {category} part of kind {spec.kind!r} is registered (known: {known})") from None
+    return factory(spec, ctx)
+
+
+class ResidualStream:
+    """The residual sum of a step, kept in float32, plus what has not been added yet.
+
+    ``pending`` is the output of the last sublayer; the next norm adds it to ``resid``
+    and normalises in one kernel.  A fresh stream holds an embedding lookup instead of
+    values: the first norm gathers the rows, stores them as ``resid`` and normalises.
+    """
+
+    def __init__(self, num_tokens: int, hidden_size: int, *, ids: torch.Tensor, table: torch.Tensor):
+        self.num_tokens = num_tokens
+        self.hidden_size = hidden_size
+        self.embed: tuple[torch.Tensor, torch.Tensor] | None = (ids, table)
+        self.resid: torch.Tensor | None = None
+        self.pending: torch.Tensor | None = None

@@ -1,0 +1,45 @@
+"""Dense gated feed-forward (SwiGLU): down(silu(gate x) * up x), no biases
+(qwen3_runtime/models/qwen3.py:130-138; layers/ops.py:23-25)."""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, ParamSpec, Part, StepContext, register_part
+
+
+class GatedMLP(Part):
+    category = "feed_forward"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden_size = int(spec["hidden_size"])
+        self.intermediate_size = int(spec["intermediate_size"])
+        activation = spec.get("activation", "silu")
+        if activation != "silu":
+            raise ValueError(f"gated_mlp has a silu kernel only, not {activation!r}")
+        self.gate_up_weight = self.down_weight = None
+
+    def param_specs(self):
+        return {
+            "gate_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
+            "up_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
+            "down_proj.weight": ParamSpec((self.hidden_size, self.intermediate_size)),
+        }
+
+    def load(self, tensors):
+        # one product for gate and up: gate rows first (utils/loader.py:51-53)
+        self.gate_up_weight = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.down_weight = tensors["down_proj.weight"].contiguous()
+
+    def kernel_groups(self):
+        return ["norm", "gemm_f32"] if self.ctx.dtype == torch.float32 else ["norm"]
+
+    def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
+        gate_up = self.ops.linear(h, self.gate_up_weight)
+        mid = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        self.ops.silu_mul(gate_up, mid)
+        return self.ops.linear(mid, self.down_weight)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

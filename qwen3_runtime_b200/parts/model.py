@@ -1,0 +1,87 @@
+"""The decoder: embedding, blocks in their run order, final norm, output head.
+
+Built from a :class:`ModelSpec`; knows no architecture by name.  Parity for the
+Qwen3 instance: qwen3_runtime/models/qwen3.py:190-266.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.layout import CacheLayout
+from ..config.spec import ModelSpec
+from .base import BuildContext, ParamSpec, ResidualStream, StepContext, build_part
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+        self.ops = ctx.ops
+        self.blocks = [build_part("block", b, ctx) for b in spec.blocks]
+        self.final_norm = build_part("norm", spec.final_norm, ctx)
+        self.embed: torch.Tensor | None = None
+        self.head: torch.Tensor | None = None
+        self.loaded = False
+
+    # ---- tensors ----------------------------------------------------------------------
+    def expected_tensors(self) -> dict[str, ParamSpec]:
+        """Every stored tensor by its checkpoint name, in a fixed order."""
+        s = self.spec
+        out: dict[str, ParamSpec] = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        for i, block in enumerate(self.blocks):
+            prefix = s.block_prefix.format(index=i)
+            for name, ps in block.param_specs().items():
+                out[prefix + name] = ps
+        for name, ps in self.final_norm.param_specs().items():
+            out[s.final_norm_prefix + name] = ps
+        if not s.tie_word_embeddings:
+            out[s.head_name] = ParamSpec((s.vocab_size, s.hidden_size))
+        return out
+
+    def ignorable_tensors(self) -> set[str]:
+        """Names a checkpoint may hold that the model does not read (a tied model's copy
+        of the head, utils/loader.py:39-40)."""
+        return {self.spec.head_name} if self.spec.tie_word_embeddings else set()
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        """``tensors``: every expected name -> tensor already on the device."""
+        s = self.spec
+        self.embed = tensors[s.embed_name].contiguous()
+        for i, block in enumerate(self.blocks):
+            prefix = s.block_prefix.format(index=i)
+            block.load({n[len(prefix):]: t for n, t in tensors.items() if n.startswith(prefix)})
+        fp = s.final_norm_prefix
+        self.final_norm.load({n[len(fp):]: t for n, t in tensors.items() if n.startswith(fp)})
+        self.head = self.embed if s.tie_word_embeddings else tensors[s.head_name].contiguous()
+        self.loaded = True
+
+    def kernel_groups(self) -> list[str]:
+        groups = {"norm", "sampling"}
+        for part in [*self.blocks, self.final_norm]:
+            groups.update(part.kernel_groups())
+        return sorted(groups)
+
+    # ---- cache ------------------------------------------------------------------------
+    def cache_layout(self) -> CacheLayout:
+        specs = {}
+        for run in self.spec.order:
+            if run.writes:
+                specs[run.cache] = self.blocks[run.block].cache_spec()
+        for run in self.spec.order:
+            if not run.writes and specs[run.cache] != self.blocks[run.block].cache_spec():
+                raise ValueError(f"a run entry reads cache layer {run.cache} whose layout differs from its own")
+        return CacheLayout(specs)
+
+    # ---- one step -----------------------------------------------------------------------
+    def forward(self, step: StepContext, storage) -> torch.Tensor | None:
+        """Run the step's tokens through every run entry; float32 logits ``[R, V]`` at
+        ``step.logit_rows`` (None when no logits are wanted)."""
+        s = self.spec
+        stream = ResidualStream(step.num_tokens, s.hidden_size, ids=step.token_ids, table=self.embed)
+        for run in s.order:
+            self.blocks[run.block].forward(stream, step, storage.view(run.cache, run.writes))
+        if step.num_logit_rows == 0:
+            return None
+        h = self.final_norm.add_norm(stream, rows=step.logit_rows, num_rows=step.num_logit_rows)
+        return self.ops.linear(h, self.head, out_dtype=torch.float32)

@@ -1,0 +1,126 @@
+"""Plain torch statements of what each CUDA kernel of the engine computes.
+
+Two uses, both in tests only: (1) the per-kernel GPU tests compare every kernel with
+the function of the same name here; (2) the CPU tests put this table in place of the
+kernel table so that the engine's host logic (batching, cache, scheduler, replay) can
+be exercised without a GPU.  Loops are deliberately simple; nothing here is fast.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+class TorchOps:
+    name = "torch-emulation"
+
+    def prepare(self, groups):
+        pass
+
+    # ---- norms ----------------------------------------------------------------------
+    def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
+                   write_resid=True, num_rows=None):
+        n = out.shape[0] if num_rows is None else num_rows
+        src = rows[:n].long() if rows is not None else torch.arange(n, device=out.device)
+        if ids is not None:
+            v = table[ids.long()[src]].float()
+        else:
+            v = resid[src].float()
+        if pending is not None:
+            v = v + pending[src].float()
+        if write_resid:
+            resid[src] = v
+        var = v.pow(2).mean(-1, keepdim=True)
+        out[:n] = ((v * torch.rsqrt(var + eps)) * weight.float()).to(out.dtype)
+        return out
+
+    def silu_mul(self, gate_up, out):
+        I = out.shape[-1]
+        g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+        out.copy_(((g / (1 + torch.exp(-g))) * u).to(out.dtype))
+        return out
+
+    # ---- position encoding + cache write -----------------------------------------------
+    def rope_table(self, inv_freq, max_positions):
+        ang = torch.arange(max_positions, dtype=torch.float32, device=inv_freq.device)[:, None] * inv_freq[None, :]
+        return ang.cos(), ang.sin()
+
+    def qk_norm_rope_store(self, qkv, *, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
+                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+        T = qkv.shape[0]
+        D = head_dim
+        pos = positions.long()
+
+        def norm_rope(x, w):  # x [T, n, D] float
+            if w is not None:
+                x = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)) * w.float()
+            if cos is not None:
+                half = cos.shape[1]
+                c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+                x1, x2, rest = x[..., :half], x[..., half:2 * half], x[..., 2 * half:]
+                x = torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
+            return x
+
+        nq, nkv = num_heads, num_kv_heads
+        q = qkv[:, : nq * D].reshape(T, nq, D).float()
+        qkv[:, : nq * D] = norm_rope(q, q_weight).reshape(T, nq * D).to(qkv.dtype)
+        if not write_kv:
+            return
+        k = norm_rope(qkv[:, nq * D:(nq + nkv) * D].reshape(T, nkv, D).float(), k_weight).to(qkv.dtype)
+        v = qkv[:, (nq + nkv) * D:(nq + 2 * nkv) * D].reshape(T, nkv, D)
+        for t in range(T):
+            p = int(pos[t])
+            page = int(block_table[int(token_seq[t]), p // page_size])
+            k_pages[page, :, p % page_size, :] = k[t]
+            v_pages[page, :, p % page_size, :] = v[t]
+
+    # ---- attention --------------------------------------------------------------------
+    def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
+                        token_seq, positions, out, page_size, scale, window, step=None):
+        T = out.shape[0]
+        D = head_dim
+        group = num_heads // num_kv_heads
+        for t in range(T):
+            p = int(positions[t])
+            lo = max(0, p - window + 1) if window else 0
+            table = block_table[int(token_seq[t])]
+            js = torch.arange(lo, p + 1)
+            pages = table[(js // page_size).to(table.device)].long()
+            offs = (js % page_size).to(pages.device)
+            keys = k_pages[pages, :, offs, :].float()  # [n, nkv, D]
+            vals = v_pages[pages, :, offs, :].float()
+            qt = q[t, : num_heads * D].reshape(num_heads, D).float()
+            kh = keys.repeat_interleave(group, dim=1)  # [n, nq, D]
+            vh = vals.repeat_interleave(group, dim=1)
+            scores = torch.einsum("hd,nhd->hn", qt, kh) * scale
+            probs = torch.softmax(scores, dim=-1)
+            out[t] = torch.einsum("hn,nhd->hd", probs, vh).reshape(-1).to(out.dtype)
+        return out
+
+    # ---- matrix products ----------------------------------------------------------------
+    def linear(self, x, weight, out=None, out_dtype=None):
+        res = x.float() @ weight.float().t()
+        res = res.to(out_dtype or x.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    # ---- sampling ---------------------------------------------------------------------
+    def argmax(self, logits, want_logprob=False):
+        tok = logits.argmax(-1).to(torch.int32)
+        lp = None
+        if want_logprob:
+            lp = torch.log_softmax(logits.float(), -1).gather(1, tok.long()[:, None])[:, 0]
+        return tok, lp
+
+    def sample(self, logits, temperature, uniform, want_logprob=False):
+        probs = torch.softmax(logits.float() / temperature[:, None], -1)
+        cdf = probs.cumsum(-1)
+        idx = torch.searchsorted(cdf, uniform[:, None].contiguous(), right=True)[:, 0].clamp(0, logits.shape[1] - 1)
+        lp = None
+        if want_logprob:
+            lp = torch.log(probs.gather(1, idx[:, None])[:, 0].clamp_min(1e-30))
+        return idx.to(torch.int32), lp
