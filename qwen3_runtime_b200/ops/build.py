@@ -62,7 +62,7 @@ def find_nvcc() -> str:
 def _writable(path: Path) -> bool:
     try:
         path.mkdir(parents=True, exist_ok=True)
-        probe = path / f".probe-{os.getpid()}"
+        probe = path / f".probe-{os.getpid()}-{threading.get_ident()}"
         probe.write_text("")
         probe.unlink()
         return True
@@ -145,6 +145,7 @@ def compile_groups(groups: list[str], *, verbose: bool = True) -> dict[str, Path
     """Compile several groups in parallel (one nvcc each)."""
     results: dict[str, Path] = {}
     errors: list[BaseException] = []
+    build_dir()  # settle the folder before the threads start
 
     def work(g: str) -> None:
         try:

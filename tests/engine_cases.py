@@ -1,0 +1,178 @@
+"""Engine-versus-plain comparisons, written once and run twice: on the CPU with the torch
+statements of the kernels (tests/emulated_ops.py) in place of the kernel table -- that
+checks batching, cache and scheduling -- and on the GPU with the real kernels, in
+float32 and bfloat16."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+import plain_model as pm
+from helpers import (TINY, first_mismatch, make_model_dir, max_abs_diff, peak_tokens, random_ids, run_trace,
+                     trace_mixed, trace_portions, trace_tail_decode, trace_whole)
+from qwen3_runtime_b200.engine.factory import build_engine, build_runtime, load_model
+
+# Tolerances, fixed in advance.  float32: the engine and the plain implementation do the
+# same arithmetic in different orders; observed differences are a few 1e-6 on logits of
+# magnitude ~4.  bfloat16: activations are rounded to 8 bits of mantissa between kernels,
+# which moves logits by about a percent of their range; the plain side rounds at the same
+# places, so what is left is rounding that fell the other way.
+TOL_F32 = 3e-5
+REL_TOL_BF16 = 0.03  # of max |logit|
+
+
+def tolerance(dtype: str, scale: float) -> float:
+    return TOL_F32 * max(1.0, scale / 4.0) if dtype == "float32" else REL_TOL_BF16 * scale
+
+
+def plain_logits(folder, requests, dtype):
+    raw, w = pm.read_model_dir(folder)
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    return {rid: pm.forward_logits(raw, w, toks, act_dtype=act) for rid, toks in requests.items()}
+
+
+def requests_for(name, lengths, seed=0):
+    vocab = TINY[name]["config"].vocab_size
+    return {f"r{i}": random_ids(vocab, n, seed * 100 + i) for i, n in enumerate(lengths)}
+
+
+def make_runtime(folder, name, dtype, ops, device, *, num_pages, max_live=4, cuda_graph=False):
+    model, cfg, _ = load_model(folder, dtype=dtype, device=device, ops=ops)
+    return build_runtime(model, max_positions=cfg.max_position_embeddings, block_size=TINY[name]["page_size"],
+                         num_kv_blocks=num_pages, max_num_seqs=max_live, cuda_graph=cuda_graph)
+
+
+def check_against(got, want, dtype, what):
+    scale = max(float(v.abs().max()) for v in want.values())
+    tol = tolerance(dtype, scale)
+    bad = first_mismatch(got, want, tol)
+    assert bad is None, (f"{what}: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g} "
+                         f"(tolerance {tol:.3g}, logits up to {scale:.3g})")
+    n = sum(len(v) for v in got.values())
+    assert n == sum(v.shape[0] for v in want.values()), f"{what}: {n} positions compared"
+
+
+def case_four_schedules(tmp_path, name, dtype, ops, device, lengths=(100, 37, 61, 150, 45, 83)):
+    """Whole / tail decoded one by one / changing portions / mixed with page reuse, each
+    against the plain implementation, and against the whole-sequence run."""
+    folder = make_model_dir(tmp_path, name)
+    requests = requests_for(name, lengths)
+    want = plain_logits(folder, requests, dtype)
+    ps = TINY[name]["page_size"]
+    results = {}
+    for kind, steps in (("whole", trace_whole(requests)), ("tail", trace_tail_decode(requests)),
+                        ("portions", trace_portions(requests, seed=1)), ("mixed", trace_mixed(requests, seed=2))):
+        # a pool that holds exactly the peak: pages are returned and handed out again
+        pages = peak_tokens(steps, 64) // ps
+        rt = make_runtime(folder, name, dtype, ops, device, num_pages=pages)
+        got = run_trace(rt, steps, poison=True)
+        check_against(got, want, dtype, f"{name} {dtype} {kind}")
+        assert rt.cache.num_free_pages == rt.cache.num_pages
+        results[kind] = got
+    # cutting and batching change nothing beyond rounding
+    whole = {rid: torch.stack([rows[p] for p in sorted(rows)]) for rid, rows in results["whole"].items()}
+    scale = max(float(v.abs().max()) for v in whole.values())
+    if dtype == "float32":
+        # the float32 kernels reduce in an order that depends on the position only: bit-identical
+        cut_tol = 0.0 if getattr(ops, "name", "").startswith("cuda") else tolerance(dtype, scale)
+    else:
+        cut_tol = REL_TOL_BF16 * scale
+    for kind in ("tail", "portions", "mixed"):
+        bad = first_mismatch(results[kind], whole, cut_tol)
+        assert bad is None, f"{name} {dtype} {kind} vs whole: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g}"
+    return results
+
+
+def case_first_tokens(tmp_path, name, dtype, ops, device):
+    """The first tokens of a sequence: length-1 and length-2 requests, and position 0 alone."""
+    folder = make_model_dir(tmp_path, name)
+    requests = requests_for(name, (1, 2, 3, 1), seed=3)
+    want = plain_logits(folder, requests, dtype)
+    rt = make_runtime(folder, name, dtype, ops, device, num_pages=16)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:1], "want": [0]} for r, t in requests.items()], "end": []},
+             {"step": 1, "entries": [{"id": r, "tokens": t[1:], "want": list(range(len(t) - 1))}
+                                     for r, t in requests.items() if len(t) > 1], "end": list(requests)}]
+    check_against(run_trace(rt, steps), want, dtype, f"{name} {dtype} first tokens")
+
+
+def case_long_decode(tmp_path, name, dtype, ops, device, prompt=5, total=300):
+    """Long decoding: a short prompt, then hundreds of single-token steps across many pages."""
+    folder = make_model_dir(tmp_path, name)
+    requests = requests_for(name, (total,), seed=4)
+    want = plain_logits(folder, requests, dtype)
+    rt = make_runtime(folder, name, dtype, ops, device, num_pages=-(-total // TINY[name]["page_size"]) + 1)
+    got = run_trace(rt, trace_tail_decode(requests, tail=total - prompt), check=False)
+    check_against(got, want, dtype, f"{name} {dtype} long decode")
+
+
+def case_greedy_generation(tmp_path, name, dtype, ops, device, *, cuda_graph=False):
+    """Greedy generation through the engine equals recomputing the whole sequence for every token
+    with the plain implementation -- alone, batched, and with so few pages that a request is
+    preempted and recomputed."""
+    folder = make_model_dir(tmp_path, name)
+    raw, w = pm.read_model_dir(folder)
+    ps = TINY[name]["page_size"]
+    prompts = list(requests_for(name, (7, 19, 5, 13), seed=5).values())
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = [pm.greedy_generate(raw, w, p, 8, act_dtype=act) for p in prompts]
+    eng = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=64, max_num_seqs=4,
+                       max_num_batched_tokens=6, cuda_graph=cuda_graph)
+    alone = [eng.generate(p, max_tokens=8) for p in prompts]
+    batched = eng.generate_batch(prompts, max_tokens=8)
+    assert eng.cache.num_free_pages == eng.cache.num_pages
+    # so few pages that they run out: two prompts that fill the pool exactly, so that neither can
+    # take its first decoded token; the younger is preempted and later recomputed from its start
+    vocab = TINY[name]["config"].vocab_size
+    tight_prompts = [random_ids(vocab, 2 * ps, 77), random_ids(vocab, ps, 78)]
+    tight_want = [pm.greedy_generate(raw, w, p, 8, act_dtype=act) for p in tight_prompts]
+    tight = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=3,
+                         max_num_seqs=4, max_num_batched_tokens=64, cuda_graph=cuda_graph)
+    squeezed = tight.generate_batch(tight_prompts, max_tokens=8)
+    assert tight.scheduler.num_preemptions >= 1, "the tight pool was meant to force a preemption"
+    assert tight.cache.num_free_pages == tight.cache.num_pages
+    roomy = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=64,
+                         max_num_seqs=4, max_num_batched_tokens=64, cuda_graph=cuda_graph)
+    unsqueezed = roomy.generate_batch(tight_prompts, max_tokens=8)
+    assert roomy.scheduler.num_preemptions == 0
+    if dtype == "float32":
+        assert alone == want and batched == want and squeezed == tight_want and unsqueezed == tight_want
+    else:
+        # greedy ids may flip where two logits are within bfloat16 rounding of each other; the
+        # engine's own three ways must still agree with each other on most tokens
+        agree = sum(a == b for x, y in zip(alone, want) for a, b in zip(x, y))
+        assert agree >= 0.7 * 8 * len(prompts), (alone, want)
+        assert batched == alone and squeezed == unsqueezed
+    return alone
+
+
+def case_temperature_sampling(tmp_path, name, dtype, ops, device):
+    """Temperature sampling with a seed: the same tokens alone and in a batch, and equal to
+    the plain implementation drawing with the same uniform numbers."""
+    from qwen3_runtime_b200 import SamplingParams
+    from qwen3_runtime_b200.engine.request import make_generator
+
+    folder = make_model_dir(tmp_path, name)
+    raw, w = pm.read_model_dir(folder)
+    ps = TINY[name]["page_size"]
+    prompts = list(requests_for(name, (5, 13, 30), seed=6).values())
+    sp = [SamplingParams(temperature=0.8, seed=40 + i) for i in range(3)]
+    eng = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=64, max_num_seqs=3,
+                       max_num_batched_tokens=6, cuda_graph=False)
+    batched = eng.generate_batch(prompts, max_tokens=8, sampling=sp)
+    alone = [eng.generate(p, max_tokens=8, sampling=s) for p, s in zip(prompts, sp)]
+    assert batched == alone
+    if dtype != "float32":
+        return
+    for p, s, got in zip(prompts, sp, alone):
+        gen = make_generator(s.seed)
+        ids = list(p)
+        for tok in got:
+            u = float(torch.rand((), dtype=torch.float32, generator=gen))
+            probs = pm.temperature_probs(pm.forward_logits(raw, w, ids)[-1], s.temperature)
+            cdf = probs.double().cumsum(0)
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            # the chosen token's interval of the CDF contains u (up to float32 rounding of the sums)
+            assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5, (tok, u, lo, float(cdf[tok]))
+            ids.append(tok)

@@ -1,0 +1,304 @@
+"""Each part of a block alone against the plain implementation's function for it, and the
+generality of the parts: a run order that names a layer twice, a layer that reads another
+layer's cache, an attention window, and a toy mixer with state of its own that is defined
+and registered here, without any change to the framework's files.  Run on the CPU with the
+torch statements of the kernels and on the GPU with the kernels."""
+
+from __future__ import annotations
+
+import torch
+
+import plain_model as pm
+from helpers import TINY, TEST_STD, random_ids
+from qwen3_runtime_b200.cache import CacheManager
+from qwen3_runtime_b200.cache.layout import CacheLayout, StateLayerSpec
+from qwen3_runtime_b200.cache.storage import CacheStorage
+from qwen3_runtime_b200.config import LayerRun, ModelSpec, PartSpec
+from qwen3_runtime_b200.engine.batch import BatchBuilder, StepEntry
+from qwen3_runtime_b200.engine.factory import build_runtime
+from qwen3_runtime_b200.models.qwen3 import qwen3_spec
+from qwen3_runtime_b200.parts import (BuildContext, DecoderModel, ParamSpec, Part, ResidualStream, build_part,
+                                      register_part, unregister_part)
+from qwen3_runtime_b200.weights import DictSource, load_into, random_state
+from qwen3_runtime_b200.weights.loader import place
+
+TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype, scale):
+    return (2e-5 if dtype == "float32" else 2e-2) * max(1.0, scale)
+
+
+def ctx_for(dtype, ops, device):
+    return BuildContext(dtype=TD[dtype], device=torch.device(device), ops=ops)
+
+
+def load_part(part, tensors, ctx):
+    part.load({n: place(tensors[n], ps, ctx.dtype, ctx.device) for n, ps in part.param_specs().items()})
+
+
+def draw(specs, seed):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for n, ps in specs.items():
+        t = torch.randn(ps.shape, generator=g)
+        out[n] = (1 + 0.1 * t if ps.kind == "vector" else TEST_STD * t).to(torch.bfloat16)
+    return out
+
+
+class OnePartHarness:
+    """A cache and a step context for a single mixer: two sequences, one mid-way (portion after
+    some cached tokens), one fresh."""
+
+    def __init__(self, mixer, ctx, page_size=4):
+        self.layout = CacheLayout({0: mixer.cache_spec()})
+        self.cache = CacheManager(self.layout.group_specs, page_size, 32, 4)
+        self.storage = CacheStorage(self.layout, page_size, 32, 4, ctx.dtype, ctx.device)
+        self.builder = BatchBuilder(self.cache, ctx.device, vocab_size=1 << 20, max_positions=4096)
+        self.handles = {}
+
+    def step(self, spans):
+        entries = []
+        for rid, n in spans:
+            rc = self.handles.get(rid) or self.handles.setdefault(rid, self.cache.open(rid))
+            self.cache.reserve(rc, n)
+            entries.append(StepEntry(rc, [0] * n, []))
+        step = self.builder.build(entries)
+        return step, entries
+
+    def commit(self, entries):
+        for e in entries:
+            self.cache.commit(e.cache, len(e.tokens))
+
+
+def case_norm_part(dtype, ops, device):
+    ctx = ctx_for(dtype, ops, device)
+    norm = build_part("norm", PartSpec("rmsnorm", dict(size=80, eps=3e-5)), ctx)
+    t = draw(norm.param_specs(), 1)
+    load_part(norm, t, ctx)
+    table = (torch.randn(50, 80) * 0.5).to(ctx.dtype).to(ctx.device)
+    ids = torch.tensor([3, 49, 0, 7], dtype=torch.int32, device=ctx.device)
+    stream = ResidualStream(4, 80, ids=ids, table=table)
+    h = norm.add_norm(stream)
+    x = table.float().cpu()[ids.cpu().long()]
+    want = pm.rmsnorm(x, t["weight"].float(), 3e-5)
+    assert float((h.float().cpu() - want).abs().max()) <= tol(dtype, float(want.abs().max()))
+    assert torch.equal(stream.resid.cpu(), x) and stream.embed is None
+    pend = (torch.randn(4, 80) * 0.3).to(ctx.dtype).to(ctx.device)
+    stream.pending = pend
+    h2 = norm.add_norm(stream)
+    x2 = x + pend.float().cpu()
+    want2 = pm.rmsnorm(x2, t["weight"].float(), 3e-5)
+    assert float((h2.float().cpu() - want2).abs().max()) <= tol(dtype, float(want2.abs().max()))
+    assert torch.equal(stream.resid.cpu(), x2) and stream.pending is None
+
+
+def case_position_part(dtype, ops, device):
+    ctx = ctx_for(dtype, ops, device)
+    pos = build_part("position", PartSpec("rope_neox", dict(rotary_dim=48, theta=5e5, max_positions=300)), ctx)
+    cos, sin = pos.rotation_tables()
+    c, s = pm.rope_tables(48, 5e5, torch.arange(300))
+    assert float((cos.cpu() - c).abs().max()) < 2e-6 and float((sin.cpu() - s).abs().max()) < 2e-6
+    assert pos.rotation_tables()[0] is cos  # one table per (dim, theta, length), shared by the layers
+    assert build_part("position", PartSpec("none"), ctx).rotation_tables() is None
+
+
+def case_mixer_part(dtype, ops, device, name="C"):
+    """The attention part alone: a request fed in two portions equals the plain attention part
+    on the whole sequence."""
+    cfg = TINY[name]["config"]
+    ctx = ctx_for(dtype, ops, device)
+    spec = qwen3_spec(cfg).blocks[0]["mixer"]
+    mixer = build_part("mixer", spec, ctx)
+    t = draw(mixer.param_specs(), 2)
+    load_part(mixer, t, ctx)
+    T = 23
+    x = (torch.randn(T, cfg.hidden_size, generator=torch.Generator().manual_seed(3))).to(ctx.dtype)
+    harness = OnePartHarness(mixer, ctx)
+    outs = []
+    for lo, hi in ((0, 9), (9, T)):
+        step, entries = harness.step([("a", hi - lo)])
+        outs.append(mixer.forward(x[lo:hi].to(ctx.device).contiguous(), step, harness.storage.view(0)).float().cpu())
+        harness.commit(entries)
+    got = torch.cat(outs)
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    w = {"p." + k: v for k, v in t.items()}
+    want, _ = pm.attention_part(x.float(), {k: v.float() for k, v in w.items()}, "p.", cfg.to_hf_config(),
+                                torch.arange(T), act_dtype=act)
+    assert float((got - want).abs().max()) <= tol(dtype, float(want.abs().max()))
+
+
+def case_feed_forward_part(dtype, ops, device):
+    ctx = ctx_for(dtype, ops, device)
+    ff = build_part("feed_forward", PartSpec("gated_mlp", dict(hidden_size=80, intermediate_size=112)), ctx)
+    t = draw(ff.param_specs(), 4)
+    load_part(ff, t, ctx)
+    x = torch.randn(9, 80, generator=torch.Generator().manual_seed(5)).to(ctx.dtype)
+    got = ff.forward(x.to(ctx.device), None).float().cpu()
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = pm.swiglu_part(x.float(), {"p." + k: v.float() for k, v in t.items()}, "p.", act_dtype=act)
+    assert float((got - want).abs().max()) <= tol(dtype, float(want.abs().max()))
+
+
+def _toy_model(spec: ModelSpec, cfg, dtype, ops, device, seed=9):
+    ctx = ctx_for(dtype, ops, device)
+    model = DecoderModel(spec, ctx)
+    g = torch.Generator().manual_seed(seed)
+    tensors = {}
+    for n, ps in model.expected_tensors().items():
+        t = torch.randn(ps.shape, generator=g)
+        tensors[n] = (1 + 0.05 * t if ps.kind == "vector" else TEST_STD * t).to(torch.bfloat16)
+    load_into(model, DictSource(tensors))
+    return model, tensors
+
+
+def _run_cut(model, cfg, ids, page_size=4, cuts=(5, 2, 9, 1, 1, 30)):
+    rt = build_runtime(model, max_positions=cfg.max_position_embeddings, block_size=page_size, num_kv_blocks=40,
+                       max_num_seqs=2)
+    rc = rt.cache.open("a")
+    outs, i = [], 0
+    for n in cuts:
+        n = min(n, len(ids) - i)
+        if n <= 0:
+            break
+        rt.cache.reserve(rc, n)
+        outs.append(rt.runner.run([StepEntry(rc, ids[i:i + n], list(range(n)))]).float().cpu())
+        i += n
+    rt.cache.check_invariants()
+    return torch.cat(outs), rt
+
+
+def case_run_order_layer_twice_and_shared_cache(dtype, ops, device):
+    """Order is data: block 0 runs twice (weights shared, a cache layer per run), and the last
+    run reads the keys and values that block 1 stored instead of storing its own."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    order = (LayerRun(0, 0), LayerRun(1, 1), LayerRun(0, 2), LayerRun(1, 1, writes=False))
+    spec = ModelSpec(base.vocab_size, base.hidden_size, base.blocks, order, base.final_norm, True)
+    model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+    ids = random_ids(cfg.vocab_size, 40, 21)
+    got, rt = _run_cut(model, cfg, ids)
+    assert len(rt.model.cache_layout().groups[0].cache_ids) == 3  # three cache layers for four runs
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = pm.forward_logits(cfg.to_hf_config(), tensors, ids, act_dtype=act,
+                             order=[(r.block, r.cache, r.writes) for r in order])
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= (3e-5 if dtype == "float32" else 0.03) * max(1.0, scale)
+
+
+def case_window_attention(dtype, ops, device, window=7):
+    """A window is a parameter of the attention part; its cache group returns pages behind the window."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    blocks = []
+    for i, b in enumerate(base.blocks):  # layer 0 keeps everything, layer 1 looks back `window` tokens
+        mixer = PartSpec("paged_attention", {**b["mixer"].params, "window": window if i == 1 else None})
+        blocks.append(PartSpec("pre_norm", {**b.params, "mixer": mixer}))
+    spec = ModelSpec(base.vocab_size, base.hidden_size, tuple(blocks), base.order, base.final_norm, True)
+    model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+    ids = random_ids(cfg.vocab_size, 48, 22)
+    got, rt = _run_cut(model, cfg, ids)
+    kinds = [g.spec.kind for g in rt.model.cache_layout().groups]
+    assert kinds == ["full", "window"]
+    rc = next(iter(rt.cache.live.values()))
+    assert len([p for p in rc.tables[0] if p >= 0]) == 12 and len([p for p in rc.tables[1] if p >= 0]) <= 3
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    raw = cfg.to_hf_config()
+    # the plain model with the window in layer 1 only: run it layer by layer
+    h, wc = pm.forward_hidden({**raw, "num_hidden_layers": 1}, tensors, ids, act_dtype=act)
+    w1 = {k.replace("model.layers.1.", "model.layers.0."): v for k, v in tensors.items() if ".layers.1." in k}
+    w1["model.embed_tokens.weight"] = torch.eye(1)  # unused below
+    pos = torch.arange(len(ids))
+    wf = {k: v.float() for k, v in tensors.items()}
+    n = pm._round(pm.rmsnorm(h, wf["model.layers.1.input_layernorm.weight"], raw["rms_norm_eps"]), act)
+    a, _ = pm.attention_part(n, wf, "model.layers.1.self_attn.", raw, pos, act_dtype=act, window=window)
+    h = h + a
+    n = pm._round(pm.rmsnorm(h, wf["model.layers.1.post_attention_layernorm.weight"], raw["rms_norm_eps"]), act)
+    h = h + pm.swiglu_part(n, wf, "model.layers.1.mlp.", act_dtype=act)
+    want = pm._round(pm.rmsnorm(h, wf["model.norm.weight"], raw["rms_norm_eps"]), act) @ wf["model.embed_tokens.weight"].T
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= (3e-5 if dtype == "float32" else 0.03) * max(1.0, scale)
+
+
+class DecayStateMixer(Part):
+    """A toy mixer with fixed-size state of its own: s_t = decay * s_{t-1} + x_t W_in, out_t = s_t W_out.
+    It keeps one vector per request in a state slot, reads it at the start of a portion and writes
+    it back at the end.  (Plain torch on whatever device it is given; it is a test fixture, not a
+    model of anything.)"""
+
+    category = "mixer"
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.hidden, self.width, self.decay = int(spec["hidden_size"]), int(spec["state_size"]), float(spec["decay"])
+
+    def param_specs(self):
+        return {"in_proj.weight": ParamSpec((self.width, self.hidden)), "out_proj.weight": ParamSpec((self.hidden, self.width))}
+
+    def load(self, tensors):
+        self.w_in, self.w_out = tensors["in_proj.weight"].float(), tensors["out_proj.weight"].float()
+
+    def cache_spec(self):
+        return StateLayerSpec((self.width,), "float32")
+
+    def forward(self, h, step, cache):
+        out = torch.empty_like(h)
+        u = h.float() @ self.w_in.t()
+        slots = step.state_slots.tolist()
+        for b in range(step.num_seqs):
+            lo, hi = step.host_cu_seqlens[b], step.host_cu_seqlens[b + 1]
+            s = cache.state[slots[b]].clone()
+            for t in range(lo, hi):
+                s = self.decay * s + u[t]
+                out[t] = (s @ self.w_out.t()).to(h.dtype)
+            if cache.writes:
+                cache.state[slots[b]] = s
+        return out
+
+
+def case_toy_state_mixer(dtype, ops, device):
+    """Register, build and step a mixer with per-request state next to an attention layer."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    register_part("mixer", "toy_decay_state", DecayStateMixer)
+    try:
+        toy = PartSpec("toy_decay_state", dict(hidden_size=cfg.hidden_size, state_size=24, decay=0.8))
+        blocks = (base.blocks[0], PartSpec("pre_norm", {**base.blocks[1].params, "mixer": toy}))
+        spec = ModelSpec(base.vocab_size, base.hidden_size, blocks, base.order, base.final_norm, True)
+        model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+        assert "model.layers.1.self_attn.in_proj.weight" in tensors
+        layout = model.cache_layout()
+        assert [g.spec.kind for g in layout.groups] == ["full", "state"]
+        rt = build_runtime(model, max_positions=512, block_size=4, num_kv_blocks=40, max_num_seqs=3)
+        reqs = {"a": random_ids(cfg.vocab_size, 30, 31), "b": random_ids(cfg.vocab_size, 17, 32)}
+
+        def run(plan):
+            handles, got = {}, {k: [] for k in reqs}
+            done = {k: 0 for k in reqs}
+            for spans in plan:
+                entries = []
+                for rid, n in spans:
+                    rc = handles.get(rid) or handles.setdefault(rid, rt.cache.open(rid))
+                    rt.cache.reserve(rc, n)
+                    entries.append(StepEntry(rc, reqs[rid][done[rid]:done[rid] + n], list(range(n))))
+                logits = rt.runner.run(entries).float().cpu()
+                row = 0
+                for rid, n in spans:
+                    got[rid].append(logits[row:row + n])
+                    row += n
+                    done[rid] += n
+            for rc in handles.values():
+                rt.cache.close(rc)
+            return {k: torch.cat(v) for k, v in got.items()}
+
+        whole = run([[("a", 30)], [("b", 17)]])
+        # portions and decode steps mixed in one batch; the slots were used before, so the state
+        # must have been zeroed when the requests started again
+        mixed = run([[("a", 7), ("b", 2)], [("a", 1), ("b", 9)], [("b", 1)], [("a", 20), ("b", 5)], [("a", 2)]])
+        t = 3e-5 if dtype == "float32" else 0.03 * float(whole["a"].abs().max())
+        for k in reqs:
+            assert float((whole[k] - mixed[k]).abs().max()) <= t
+        # and the state matters: with another decay the logits move
+        assert float((whole["a"][5:] - whole["a"][:-5]).abs().max()) > 1e-3
+    finally:
+        unregister_part("mixer", "toy_decay_state")

@@ -1,0 +1,49 @@
+"""Engine versus plain implementation on the GPU with the real kernels, float32 and bfloat16."""
+
+import pytest
+
+import engine_cases as ec
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    return CudaOps()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_four_schedules(tmp_path, ops, name, dtype):
+    ec.case_four_schedules(tmp_path, name, dtype, ops, "cuda")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_four_schedules_long_requests(tmp_path, ops, dtype):
+    """Hundreds of keys per query, many pages per request."""
+    ec.case_four_schedules(tmp_path, "B", dtype, ops, "cuda", lengths=(400, 333, 257, 480))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_first_tokens(tmp_path, ops, name, dtype):
+    ec.case_first_tokens(tmp_path, name, dtype, ops, "cuda")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode(tmp_path, ops, dtype):
+    ec.case_long_decode(tmp_path, "B", dtype, ops, "cuda", total=300)
+
+
+@pytest.mark.parametrize("cuda_graph", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation(tmp_path, ops, name, dtype, cuda_graph):
+    ec.case_greedy_generation(tmp_path, name, dtype, ops, "cuda", cuda_graph=cuda_graph)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling(tmp_path, ops, dtype):
+    ec.case_temperature_sampling(tmp_path, "B", dtype, ops, "cuda")

@@ -1,0 +1,314 @@
+"""Each CUDA kernel alone against its plain torch statement (tests/emulated_ops.py), at sizes
+other than the tiny models': real Qwen3 layer sizes and awkward ones (widths and vocabularies
+that are no power of two, odd page sizes, head sizes in steps of 16, uneven head groups)."""
+
+import math
+
+import pytest
+import torch
+
+from emulated_ops import TorchOps
+
+pytestmark = pytest.mark.gpu
+
+REF = TorchOps()
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    return CudaOps()
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+def close(got, want, dtype, what, f32_tol=2e-5, bf16_tol=2e-2):
+    tol = f32_tol if dtype == torch.float32 else bf16_tol
+    scale = max(1.0, float(want.float().abs().max()))
+    diff = float((got.float() - want.float()).abs().max())
+    assert diff <= tol * scale, f"{what}: max |diff| {diff:.3g} > {tol * scale:.3g}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,T", [(2560, 33), (333, 7), (4096, 2), (80, 130), (12288, 3)])
+def test_fused_norm_variants(ops, dtype, H, T):
+    w = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(1))).cuda()
+    eps = 1e-5
+    # (a) residual add + norm, residual updated in place
+    resid = rand((T, H), torch.float32, 2)
+    pend = rand((T, H), dtype, 3)
+    r1, r2 = resid.clone(), resid.clone()
+    o1 = torch.empty((T, H), dtype=dtype, device="cuda")
+    o2 = torch.empty_like(o1)
+    ops.fused_norm(o1, w, eps, resid=r1, pending=pend)
+    REF.fused_norm(o2, w, eps, resid=r2, pending=pend)
+    close(o1, o2, dtype, "add+norm")
+    assert torch.equal(r1, r2), "the residual sum is a float32 add of the same two numbers"
+    # (b) embedding lookup + norm
+    V = 1000
+    table = rand((V, H), dtype, 4)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(5)).int().cuda()
+    r1 = torch.empty((T, H), dtype=torch.float32, device="cuda")
+    r2 = torch.empty_like(r1)
+    ops.fused_norm(o1, w, eps, resid=r1, ids=ids, table=table)
+    REF.fused_norm(o2, w, eps, resid=r2, ids=ids, table=table)
+    close(o1, o2, dtype, "embed+norm")
+    assert torch.equal(r1, r2)
+    # (c) gathered rows, residual untouched
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32).cuda()
+    before = resid.clone()
+    g1 = torch.empty((3, H), dtype=dtype, device="cuda")
+    g2 = torch.empty_like(g1)
+    ops.fused_norm(g1, w, eps, resid=resid, pending=pend, rows=rows, write_resid=False)
+    REF.fused_norm(g2, w, eps, resid=resid.clone(), pending=pend, rows=rows, write_resid=False)
+    close(g1, g2, dtype, "gather+add+norm")
+    assert torch.equal(resid, before)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("I,T", [(9728, 5), (111, 64), (160, 1)])
+def test_silu_mul(ops, dtype, I, T):
+    gu = rand((T, 2 * I), dtype, 6, scale=3.0)
+    a = torch.empty((T, I), dtype=dtype, device="cuda")
+    b = torch.empty_like(a)
+    ops.silu_mul(gu, a)
+    REF.silu_mul(gu, b)
+    close(a, b, dtype, "silu_mul", bf16_tol=1e-2)
+
+
+def test_rope_table_matches_host_formula(ops):
+    for D, theta, n in ((128, 1e6, 5000), (48, 1e4, 300)):
+        inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+        cos, sin = ops.rope_table(inv.cuda(), n)
+        ang = torch.arange(n, dtype=torch.float)[:, None] * inv[None, :]
+        assert float((cos.cpu() - ang.cos()).abs().max()) < 2e-6
+        assert float((sin.cpu() - ang.sin()).abs().max()) < 2e-6
+
+
+def make_cache(num_pages, nkv, ps, D, dtype, seed):
+    k = rand((num_pages, nkv, ps, D), dtype, seed)
+    v = rand((num_pages, nkv, ps, D), dtype, seed + 1)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,D,ps,rot,write", [(32, 8, 128, 16, 128, True), (6, 3, 48, 7, 48, True),
+                                                    (5, 5, 80, 1, 32, True), (4, 1, 16, 32, 16, False)])
+def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write):
+    T, B, maxp = 37, 3, 12
+    g = torch.Generator().manual_seed(7)
+    seq = torch.randint(0, B, (T,), generator=g).int()
+    # distinct (seq, position) pairs so that no two tokens write the same slot
+    pos = torch.zeros(T, dtype=torch.int32)
+    used = {}
+    for t in range(T):
+        s = int(seq[t])
+        used[s] = used.get(s, 20) + 1
+        pos[t] = used[s]
+    bt = torch.randperm(B * maxp, generator=g).int().view(B, maxp)
+    width = (nq + 2 * nkv) * D if write else nq * D
+    qkv = rand((T, width), dtype, 8)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    inv = 1.0 / (1e4 ** (torch.arange(0, rot, 2, dtype=torch.float) / rot))
+    cos, sin = ops.rope_table(inv.cuda(), 256)
+    outs = []
+    for impl in (ops, REF):
+        x = qkv.clone()
+        k, v = make_cache(B * maxp, nkv, ps, D, dtype, 9)
+        impl.qk_norm_rope_store(x, num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=qw, k_weight=kw, eps=1e-6,
+                                cos=cos, sin=sin, positions=pos.cuda(), token_seq=seq.cuda(), block_table=bt.cuda(),
+                                k_pages=k, v_pages=v, page_size=ps, write_kv=write)
+        outs.append((x, k, v))
+    (x1, k1, v1), (x2, k2, v2) = outs
+    close(x1[:, : nq * D], x2[:, : nq * D], dtype, "q")
+    close(k1, k2, dtype, "k pages")
+    assert torch.equal(v1, v2), "values are copied bit for bit"
+    if write:  # slots that no token of the step owns are untouched
+        k0, _ = make_cache(B * maxp, nkv, ps, D, dtype, 9)
+        assert int((k1 != k0).any(dim=-1).any(dim=1).sum()) == T
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_norm_rope_store_without_norm_or_rotation(ops, dtype):
+    T, nq, nkv, D, ps = 5, 2, 1, 32, 4
+    qkv = rand((T, (nq + 2 * nkv) * D), dtype, 10)
+    pos = torch.arange(T, dtype=torch.int32).cuda()
+    seq = torch.zeros(T, dtype=torch.int32).cuda()
+    bt = torch.tensor([[1, 0]], dtype=torch.int32).cuda()
+    k, v = make_cache(2, nkv, ps, D, dtype, 11)
+    x = qkv.clone()
+    ops.qk_norm_rope_store(x, num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=None, k_weight=None, eps=0.0,
+                           cos=None, sin=None, positions=pos, token_seq=seq, block_table=bt, k_pages=k, v_pages=v,
+                           page_size=ps, write_kv=True)
+    assert torch.equal(x, qkv)
+    assert torch.equal(k[1, 0, :4], qkv[:4, nq * D:(nq + 1) * D]) and torch.equal(k[0, 0, 0], qkv[4, nq * D:(nq + 1) * D])
+
+
+def attention_problem(nq, nkv, D, ps, lens, qlens, dtype, seed, num_pages=None):
+    """A ragged batch: sequence b has ``lens[b]`` keys in the cache and its last ``qlens[b]`` are queries."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    maxp = max(-(-n // ps) for n in lens) + 1
+    num_pages = num_pages or B * maxp + 3
+    perm = torch.randperm(num_pages, generator=g).int()
+    bt = perm[: B * maxp].view(B, maxp).contiguous()
+    k, v = make_cache(num_pages, nkv, ps, D, dtype, seed + 1)
+    seq, pos = [], []
+    for b, (n, ql) in enumerate(zip(lens, qlens)):
+        seq += [b] * ql
+        pos += list(range(n - ql, n))
+    T = len(seq)
+    q = rand((T, (nq + 2 * nkv) * D), dtype, seed + 2)
+    return dict(q=q, k=k, v=v, bt=bt.cuda(), seq=torch.tensor(seq, dtype=torch.int32).cuda(),
+                pos=torch.tensor(pos, dtype=torch.int32).cuda(), T=T)
+
+
+def run_attention(impl, pr, nq, nkv, D, ps, dtype, window=None, scale=None):
+    out = torch.zeros((pr["T"], nq * D), dtype=dtype, device="cuda")
+    impl.paged_attention(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D, k_pages=pr["k"],
+                         v_pages=pr["v"], block_table=pr["bt"], token_seq=pr["seq"], positions=pr["pos"], out=out,
+                         page_size=ps, scale=scale or 1 / math.sqrt(D), window=window)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,D,ps,window", [(32, 8, 128, 16, None), (6, 3, 48, 7, None), (8, 2, 64, 16, 33),
+                                                 (4, 4, 16, 1, None), (5, 1, 80, 32, 100), (2, 1, 256, 8, None)])
+def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, D, ps, window):
+    lens, qlens = [300, 1, 77, 129, 64], [1, 1, 77, 40, 2]  # decode, first token, whole prompt, portion, tiny portion
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, dtype, 20)
+    a = run_attention(ops, pr, nq, nkv, D, ps, dtype, window)
+    b = run_attention(REF, pr, nq, nkv, D, ps, dtype, window)
+    close(a, b, dtype, "attention", f32_tol=1e-5, bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """Random keys give near-uniform weights that hide a wrong page or offset.  Here one key, far
+    back, in the middle of a page, is made to carry all the weight; the output must be that
+    key's value.  Then the key one position past the window's edge must be ignored."""
+    nq, nkv, D, ps = 8, 2, 128, 16
+    n = 700
+    for far in (0, 5, 16 * 9 + 15, 16 * 10, n - 1):
+        pr = attention_problem(nq, nkv, D, ps, [n], [1], dtype, 30 + far)
+        q = pr["q"]
+        q[:] = 0
+        q[0, : nq * D] = 4.0  # every query head: a constant vector
+        page, off = int(pr["bt"][0, far // ps]), far % ps
+        pr["k"][:] = pr["k"] * 0.01
+        pr["k"][page, :, off, :] = 4.0  # score 16 * 128 / sqrt(128) = 181 against ~0
+        out = run_attention(ops, pr, nq, nkv, D, ps, dtype)
+        want = pr["v"][page, :, off, :].float().repeat_interleave(nq // nkv, dim=0).reshape(-1)
+        close(out[0], want, dtype, f"far key at {far}", f32_tol=1e-6, bf16_tol=1e-6)
+        # a window that ends one key after `far` must not see it
+        window = n - 1 - far
+        if window >= 1:
+            out_w = run_attention(ops, pr, nq, nkv, D, ps, dtype, window=window)
+            ref_w = run_attention(REF, pr, nq, nkv, D, ps, dtype, window=window)
+            close(out_w, ref_w, dtype, f"window edge excludes {far}", f32_tol=1e-5, bf16_tol=1e-2)
+            assert float((out_w[0].float() - want).abs().max()) > 0.1
+            out_in = run_attention(ops, pr, nq, nkv, D, ps, dtype, window=window + 1)
+            close(out_in[0], want, dtype, f"window edge includes {far}", f32_tol=1e-6, bf16_tol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_ignores_what_lies_beyond_a_sequence(ops, dtype):
+    """Slots after a sequence's last key (rest of its last page, pages of other requests) hold NaN."""
+    nq, nkv, D, ps = 4, 2, 64, 16
+    lens, qlens = [21, 40], [21, 1]
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, dtype, 40)
+    ref = run_attention(REF, pr, nq, nkv, D, ps, dtype)
+    used = torch.zeros(pr["k"].shape[0], ps, dtype=torch.bool)
+    for b, n in enumerate(lens):
+        for j in range(n):
+            used[int(pr["bt"][b, j // ps]), j % ps] = True
+    mask = (~used).cuda()[:, None, :, None].expand_as(pr["k"])
+    pr["k"][mask] = float("nan")
+    pr["v"][mask] = float("nan")
+    out = run_attention(ops, pr, nq, nkv, D, ps, dtype)
+    assert torch.isfinite(out).all()
+    close(out, ref, dtype, "attention with poisoned free slots", f32_tol=1e-5, bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2560, 2560), (7, 333, 130), (64, 96, 64), (65, 160, 96), (300, 301, 80),
+                                   (2, 1000, 9)])
+def test_gemm_f32_is_exact_fp32_and_row_invariant(ops, M, N, K):
+    x = rand((M, K), torch.float32, 50)
+    w = rand((N, K), torch.float32, 51)
+    got = ops.linear(x, w)
+    want = (x.double() @ w.double().t())
+    assert float((got.double() - want).abs().max()) <= 2e-6 * math.sqrt(K) * float(want.abs().max() + 1)
+    # TF32 would be off by ~1e-3 relative: make sure we are far below it
+    assert float((got.double() - want).abs().max()) < 1e-4 * float(want.abs().max())
+    # a row's result does not depend on how many rows are computed with it
+    alone = ops.linear(x[M - 1:M].contiguous(), w)
+    assert torch.equal(alone[0], got[M - 1])
+    if M > 2:
+        part = ops.linear(x[1:M].contiguous(), w)
+        assert torch.equal(part, got[1:])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2560, 2560), (8, 19456, 2560), (300, 304, 96), (5, 151936, 64)])
+def test_linear_bf16(ops, M, N, K):
+    x = rand((M, K), torch.bfloat16, 52)
+    w = rand((N, K), torch.bfloat16, 53, scale=0.05)
+    want = x.float() @ w.float().t()
+    close(ops.linear(x, w), want, torch.bfloat16, "linear bf16", bf16_tol=1e-2)
+    f32 = ops.linear(x, w, out_dtype=torch.float32)
+    assert f32.dtype == torch.float32
+    close(f32, want, torch.float32, "linear bf16 -> f32", f32_tol=1e-4)
+
+
+@pytest.mark.parametrize("V,R", [(151936, 3), (301, 5), (32, 1), (4099, 64)])
+def test_argmax_lowest_index_on_ties(ops, V, R):
+    logits = rand((R, V), torch.float32, 60)
+    logits[0, V // 3] = 50.0
+    logits[0, V - 1] = 50.0  # tie: the lower index wins
+    tok, lp = ops.argmax(logits, want_logprob=True)
+    want = logits.argmax(-1)
+    assert tok[0].item() == V // 3
+    assert torch.equal(tok.long()[1:], want[1:])
+    ref_lp = torch.log_softmax(logits, -1).gather(1, tok.long()[:, None])[:, 0]
+    assert float((lp - ref_lp).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("V,R", [(151936, 4), (301, 16), (4099, 3)])
+def test_sample_inverse_cdf(ops, V, R):
+    g = torch.Generator().manual_seed(61)
+    logits = rand((R, V), torch.float32, 62, scale=3.0)
+    temp = (0.5 + torch.rand(R, generator=g)).cuda()
+    for trial in range(4):
+        u = torch.rand(R, generator=g).cuda()
+        tok, lp = ops.sample(logits, temp, u, want_logprob=True)
+        probs = torch.softmax(logits.double() / temp.double()[:, None], -1)
+        cdf = probs.cumsum(-1)
+        for r in range(R):
+            t = int(tok[r])
+            lo = float(cdf[r, t - 1]) if t > 0 else 0.0
+            assert lo - 2e-6 <= float(u[r]) <= float(cdf[r, t]) + 2e-6, (r, t, float(u[r]), lo, float(cdf[r, t]))
+            assert abs(float(lp[r]) - math.log(float(probs[r, t]))) < 1e-3
+    # u = 0 picks the first token with any probability; u just below 1 the last one
+    tok, _ = ops.sample(logits, temp, torch.zeros(R).cuda())
+    assert tok.tolist() == [0] * R
+    peaked = torch.full((1, V), -1e4).cuda()
+    peaked[0, V - 2] = 0.0
+    tok, _ = ops.sample(peaked, torch.ones(1).cuda(), torch.tensor([0.9999]).cuda())
+    assert tok.item() == V - 2
+
+
+def test_kernels_refuse_sizes_they_do_not_support(ops):
+    from qwen3_runtime_b200.ops.cuda import KernelError
+
+    pr = attention_problem(2, 1, 264, 16, [5], [1], torch.float32, 70)
+    with pytest.raises(KernelError, match="head_dim=264"):
+        run_attention(ops, pr, 2, 1, 264, 16, torch.float32)
+    with pytest.raises(KernelError):
+        ops.linear(torch.zeros(2, 8).cuda(), torch.zeros(4, 9).cuda())
+    with pytest.raises(KernelError, match="float32 and bfloat16"):
+        ops.silu_mul(torch.zeros(2, 8, dtype=torch.float16).cuda(), torch.zeros(2, 4, dtype=torch.float16).cuda())
