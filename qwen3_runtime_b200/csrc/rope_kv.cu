@@ -31,7 +31,9 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   long cache_row = 0;
   if (hi >= nq) {
     const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
+    if (p < 0 || p / ps >= max_pages) return;  // no page in the table for this position: write nothing
     const int page = block_table[(long)token_seq[t] * max_pages + p / ps];
+    if (page < 0) return;
     cache_row = (((long)page * nkv + kvh) * ps + (p % ps)) * D;
   }
   if (hi >= nq + nkv) {  // value head: plain copy

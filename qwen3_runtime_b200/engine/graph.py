@@ -1,0 +1,92 @@
+"""CUDA graphs for decode-only steps.
+
+A step in which every request brings exactly one token launches a few hundred small
+kernels; replaying them from a captured graph removes the launch cost.  One graph per
+(batch-size bucket, block-table width bucket): the batch is padded to the bucket with
+dummy sequences that write to the cache's scratch page, the step's integer metadata is
+copied into a fixed device buffer that the captured kernels read, and logits come out
+of a fixed buffer.  Kernel choices inside a captured step depend on the bucket only,
+never on the lengths of the moment.
+Parity: qwen3_runtime/engine/cuda_graph.py:79-249 (one graph per batch size, static
+input and logits buffers, metadata refreshed outside the capture).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .batch import StepEntry
+
+
+@dataclass
+class _Captured:
+    graph: torch.cuda.CUDAGraph
+    meta: torch.Tensor  # fixed int32 device buffer with the step's metadata
+    logits: torch.Tensor  # [bucket, vocab] float32, rewritten by every replay
+
+
+def _bucket(n: int, sizes: list[int]) -> int | None:
+    for s in sizes:
+        if n <= s:
+            return s
+    return None
+
+
+class DecodeGraphs:
+    def __init__(self, runner, batch_sizes):
+        self.runner = runner
+        self.sizes = sorted(int(s) for s in batch_sizes)
+        self.captured: dict[tuple[int, int], _Captured] = {}
+        self.replays = 0
+
+    def try_run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Logits for the entries that want them (an empty tensor when none does), or None
+        when the step is not a decode-only step that fits a bucket."""
+        if any(len(e.tokens) != 1 for e in entries):
+            return None
+        B = len(entries)
+        bucket = _bucket(B, self.sizes)
+        if bucket is None:
+            return None
+        need = max((len(t) for e in entries for t in e.cache.tables), default=1)
+        width = max(8, 1 << (max(need, 1) - 1).bit_length())
+        key = (bucket, width)
+        cap = self.captured.get(key)
+        if cap is None:
+            cap = self._capture(key, entries)
+        self._fill(cap, entries, bucket, width)
+        cap.graph.replay()
+        self.replays += 1
+        wanted = [i for i, e in enumerate(entries) if e.want]
+        if len(wanted) == B:
+            return cap.logits[:B]
+        if not wanted:
+            return cap.logits[:0]
+        return cap.logits[torch.tensor(wanted, dtype=torch.long, device=cap.logits.device)]
+
+    def _fill(self, cap: _Captured, entries, bucket: int, width: int):
+        r = self.runner
+        return r.builder.build(entries, pad_to=bucket, table_width=width, scratch_page=r.storage.scratch_page,
+                               scratch_slot=r.storage.scratch_slot, device_buffer=cap.meta, all_rows=True)
+
+    def _capture(self, key, entries) -> _Captured:
+        bucket, width = key
+        r = self.runner
+        n_paged = len(r.cache.paged_groups)
+        meta = torch.zeros(8 * bucket + 64 + n_paged * bucket * width, dtype=torch.int32, device=r.device)
+        cap = _Captured(torch.cuda.CUDAGraph(), meta, None)
+        step = self._fill(cap, entries, bucket, width)
+        step.extras["captured_width"] = width
+        # warm up on a side stream (loads kernels, builds shared tables), then capture
+        side = torch.cuda.Stream(device=r.device)
+        side.wait_stream(torch.cuda.current_stream(r.device))
+        with torch.cuda.stream(side):
+            r.model.forward(step, r.storage)
+        torch.cuda.current_stream(r.device).wait_stream(side)
+        torch.cuda.synchronize(r.device)
+        with torch.cuda.graph(cap.graph):
+            cap.logits = r.model.forward(step, r.storage)
+        self.captured[key] = cap
+        return cap

@@ -100,7 +100,8 @@ def make_cache(num_pages, nkv, ps, D, dtype, seed):
 @pytest.mark.parametrize("nq,nkv,D,ps,rot,write", [(32, 8, 128, 16, 128, True), (6, 3, 48, 7, 48, True),
                                                     (5, 5, 80, 1, 32, True), (4, 1, 16, 32, 16, False)])
 def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write):
-    T, B, maxp = 37, 3, 12
+    T, B = 37, 3
+    maxp = (21 + T) // ps + 1  # every position below has a page in the table
     g = torch.Generator().manual_seed(7)
     seq = torch.randint(0, B, (T,), generator=g).int()
     # distinct (seq, position) pairs so that no two tokens write the same slot
