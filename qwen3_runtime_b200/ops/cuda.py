@@ -90,6 +90,7 @@ class CudaOps:
                 f"the kernels are compiled for sm_100a; this device reports sm_{major}{_minor}"
             )
         self._fn: dict[str, ctypes._CFuncPtr] = {}
+        self.launches = 0  # kernels of this engine launched (or captured) through this table
         if groups:
             build.compile_groups([g for g in groups])
 
@@ -112,6 +113,10 @@ class CudaOps:
     def _stream() -> int:
         return torch.cuda.current_stream().cuda_stream
 
+    def _call(self, group: str, name: str, what: str, *args) -> None:
+        self.launches += 1
+        _check(self._get(group, name)(*args, self._stream()), what)
+
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
                    write_resid=True, num_rows=None):
@@ -119,16 +124,15 @@ class CudaOps:
         H = weight.numel()
         n = out.shape[0] if num_rows is None else num_rows
         vocab = table.shape[0] if table is not None else 0
-        fn = self._get("norm", "q3_fused_norm")
-        _check(fn(_dtype_code(out.dtype), _ptr(pending), _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
-                  _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab, self._stream()),
-               f"fused_norm(H={H})")
+        self._call("norm", "q3_fused_norm", f"fused_norm(H={H})",
+                   _dtype_code(out.dtype), _ptr(pending), _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
+                  _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab)
         return out
 
     def silu_mul(self, gate_up, out):
         I = out.shape[-1]
-        fn = self._get("norm", "q3_silu_mul")
-        _check(fn(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I, self._stream()), "silu_mul")
+        self._call("norm", "q3_silu_mul", "silu_mul",
+                   _dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I)
         return out
 
     # ---- position encoding + cache write -----------------------------------------------
@@ -136,8 +140,8 @@ class CudaOps:
         half = inv_freq.numel()
         cos = torch.empty((max_positions, half), dtype=torch.float32, device=inv_freq.device)
         sin = torch.empty_like(cos)
-        fn = self._get("rope_kv", "q3_rope_table")
-        _check(fn(_ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half, self._stream()), "rope_table")
+        self._call("rope_kv", "q3_rope_table", "rope_table",
+                   _ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half)
         return cos, sin
 
     def qk_norm_rope_store(self, qkv, *, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
@@ -148,11 +152,11 @@ class CudaOps:
         max_pages = block_table.shape[1] if block_table is not None else 0
         if head_dim * 16 > 48 * 1024:
             raise KernelError(f"qk_norm_rope_store: head_dim={head_dim} is too large (limit 3072)")
-        fn = self._get("rope_kv", "q3_qk_norm_rope_store")
-        _check(fn(_dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads, head_dim,
+        self._call("rope_kv", "q3_qk_norm_rope_store", "qk_norm_rope_store",
+                   _dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads, head_dim,
                   _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
                   _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages),
-                  page_size, T, int(bool(write_kv)), self._stream()), "qk_norm_rope_store")
+                  page_size, T, int(bool(write_kv)))
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
@@ -162,10 +166,10 @@ class CudaOps:
         if head_dim % 8 or head_dim > 256:
             raise KernelError(
                 f"paged_attention: head_dim={head_dim} is not supported (multiples of 8 up to 256 are)")
-        fn = self._get("attention_generic", "q3_paged_attention_generic")
-        _check(fn(_dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
+                   _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,
-                  head_dim, page_size, float(scale), int(window or 0), self._stream()), "paged_attention")
+                  head_dim, page_size, float(scale), int(window or 0))
         return out
 
     # ---- matrix products ----------------------------------------------------------------
@@ -180,9 +184,8 @@ class CudaOps:
         if x.dtype == torch.float32:
             if out is None:
                 out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-            fn = self._get("gemm_f32", "q3_gemm_f32")
-            _check(fn(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
-                      self._stream()), "gemm_f32")
+            self._call("gemm_f32", "q3_gemm_f32", "gemm_f32", _ptr(x), x.stride(0), _ptr(weight),
+                       weight.stride(0), _ptr(out), out.stride(0), M, N, K)
             return out
         if out_dtype is not None and out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
@@ -195,17 +198,16 @@ class CudaOps:
         R, V = logits.shape
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
-        fn = self._get("sampling", "q3_argmax")
-        _check(fn(_ptr(logits), R, V, _ptr(token), _ptr(logprob), self._stream()), "argmax")
+        self._call("sampling", "q3_argmax", "argmax",
+                   _ptr(logits), R, V, _ptr(token), _ptr(logprob))
         return token, logprob
 
     def sample(self, logits, temperature, uniform, want_logprob=False):
         R, V = logits.shape
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
-        fn = self._get("sampling", "q3_sample")
-        _check(fn(_ptr(logits), R, V, _ptr(temperature), _ptr(uniform), _ptr(token), _ptr(logprob),
-                  self._stream()), "sample")
+        self._call("sampling", "q3_sample", "sample",
+                   _ptr(logits), R, V, _ptr(temperature), _ptr(uniform), _ptr(token), _ptr(logprob))
         return token, logprob
 
 
