@@ -406,6 +406,60 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:200]}"}
 
 
+def run_profile_step(args) -> dict:
+    """A few eager (not graph-replayed) steps of one kind, for a profiler to list kernels:
+    ``--only decode`` (``--batch`` requests of ``--context`` tokens) or ``--only prefill``."""
+    import torch
+
+    from qwen3_runtime_b200.config import Qwen3Config
+    from qwen3_runtime_b200.engine.batch import StepEntry
+    from qwen3_runtime_b200.engine.factory import build_model, build_runtime
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+    from qwen3_runtime_b200.weights.random_init import RandomDeviceSource, expected_tensors_for
+
+    shape = dict(SHAPE)
+    if args.layers:
+        shape["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config(**shape)
+    ops = CudaOps()
+    model = build_model(cfg, RandomDeviceSource(expected_tensors_for(cfg), SEED, "cuda"), dtype="bfloat16", ops=ops)
+    tokens = args.batch * (args.context + args.steps + args.warmup + 64) + PREFILL_TOKENS
+    rt = build_runtime(model, max_positions=cfg.max_position_embeddings, block_size=PAGE,
+                       num_kv_blocks=-(-tokens // PAGE), max_num_seqs=args.batch, cuda_graph=args.graph)
+    gen = torch.Generator().manual_seed(SEED)
+    times = []
+    if args.only == "decode":
+        handles = []
+        for i in range(args.batch):
+            rc = rt.cache.open(i)
+            rt.cache.reserve(rc, args.context)
+            rt.cache.commit(rc, args.context)
+            handles.append(rc)
+        for s in range(args.warmup + args.steps):
+            entries = []
+            for rc in handles:
+                rt.cache.reserve(rc, 1)
+                entries.append(StepEntry(rc, torch.randint(1, 1000, (1,), generator=gen).tolist(), [0]))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            rt.runner.run(entries)
+            torch.cuda.synchronize()
+            times.append((time.perf_counter() - t0) * 1e3)
+    else:
+        for s in range(args.warmup + args.steps):
+            rc = rt.cache.open("p")
+            rt.cache.reserve(rc, PREFILL_TOKENS)
+            toks = torch.randint(1, 1000, (PREFILL_TOKENS,), generator=gen).tolist()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            rt.runner.run([StepEntry(rc, toks, [PREFILL_TOKENS - 1])])
+            torch.cuda.synchronize()
+            times.append((time.perf_counter() - t0) * 1e3)
+            rt.cache.close(rc)
+    return {"only": args.only, "batch": args.batch, "context": args.context, "layers": cfg.num_hidden_layers,
+            "graph": args.graph, "ms_per_step_wall": [round(t, 3) for t in times[args.warmup:]]}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -414,10 +468,18 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the full model (0 = all 36)")
     parser.add_argument("--context", type=int, default=CONTEXT)
+    parser.add_argument("--only", choices=["decode", "prefill"], default=None,
+                        help="run just a few steps of one kind (for profilers); prints wall times")
+    parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode steps")
+    parser.add_argument("--graph", action=argparse.BooleanOptionalAction, default=False,
+                        help="--only: replay decode steps from a CUDA graph")
     args = parser.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         print("bench.py: this engine runs on ONE GPU; --gpus > 1 is not supported")
         return 2
+    if args.only:
+        print(json.dumps(run_profile_step(args)))
+        return 0
     args.warmup = max(3, args.warmup)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -1,0 +1,383 @@
+// Split-KV decode attention over the paged cache, bfloat16, for sequences that bring
+// exactly one query token.  Memory-bound: the job is to stream a sequence's keys and
+// values once at full HBM bandwidth.
+//
+// Grid (split, kv head, sequence).  A block handles one slice of one sequence's keys for
+// one kv head and all `group = nq / nkv` query heads that read it: the group's queries are
+// the (zero-padded) 16 rows of an m16n8k16 tensor-core tile, so a key or value loaded once
+// serves every head of the group (the reference's Triton kernel does the same with
+// BLOCK_H = 16, kernels/triton_decode.py:280-444).  Keys and values arrive in tiles of 64
+// through a 2-stage cp.async pipeline into XOR-swizzled shared memory; each of the 4 warps
+// takes 16 keys of a tile, keeps its own online-softmax state (fp32, exp2 with the scale
+// folded in) and the warps merge at the end.  Slots outside [lo, kv_len) are zero-filled,
+// never read, so stale or poisoned pages cannot leak in.
+//
+// With more than one split a block writes a normalised partial result and its log-sum-exp
+// to scratch (mid_o [seqs, nq, splits, D] fp32, mid_lse [seqs, nq, splits]); a second
+// kernel merges the splits (triton_decode.py:447-501).  Slices are cut at multiples of 64
+// keys counted from the first visible key, so an empty slice writes lse = -inf.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE = 64;     // keys per pipeline stage
+constexpr int WARPS = 4;     // each takes 16 keys of a tile
+constexpr int THREADS = WARPS * 32;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bf16 tile whose chunks
+// are XOR-swizzled within each row, so that 8 rows at one logical chunk hit 8 bank groups.
+template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
+  constexpr int CHUNKS = D / 8;
+  static_assert(CHUNKS >= 8 && (CHUNKS & (CHUNKS - 1)) == 0, "head_dim must be 64, 128 or 256 here");
+  return (row * CHUNKS + (chunk ^ (row & 7))) * 16;
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpages,
+                        const bf16* __restrict__ vpages, const int* __restrict__ block_table, int max_pages,
+                        const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
+                        const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
+                        float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
+                        int num_splits, int stages) {
+  constexpr int CHUNKS = D / 8;
+  constexpr int TILE_BYTES = TILE * D * 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* q_s = smem;                  // [16][D] bf16
+  unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile)
+
+  const int split = blockIdx.x, kvh = blockIdx.y;
+  const int slot = blockIdx.z;                // index into the partial buffers
+  const int seq = seq_list ? seq_list[slot] : slot;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = nq / nkv;
+  const int kv_len = kv_lens[seq];
+  const int tok = cu_seqlens[seq];
+  const int p = kv_len - 1;
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int begin0 = lo & ~(TILE - 1);
+  const int total = kv_len - begin0;
+  int per = (total + num_splits - 1) / num_splits;
+  per = (per + TILE - 1) & ~(TILE - 1);
+  const int k_begin = begin0 + split * per;
+  const int k_end = min(kv_len, k_begin + per);
+  const int* bt = block_table + (long)seq * max_pages;
+
+  if (k_begin >= k_end) {  // nothing visible in this slice
+    if (num_splits > 1 && tid < G)
+      mid_lse[((long)slot * nq + kvh * G + tid) * num_splits + split] = -INFINITY;
+    return;
+  }
+
+  // ---- the group's queries: rows 0..G-1 of a 16-row tile, the rest zero -----------------
+  for (int c = tid; c < 16 * CHUNKS; c += THREADS) {
+    const int row = c / CHUNKS, chunk = c % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + (long)tok * q_stride + (long)(kvh * G + row) * D + chunk * 8);
+    *reinterpret_cast<uint4*>(q_s + swz<D>(row, chunk)) = v;
+  }
+
+  const int num_tiles = (k_end - k_begin + TILE - 1) / TILE;
+  // A thread copies one 16-byte chunk column of 8 consecutive keys.  When the page size is
+  // a multiple of 8 those keys lie in one page: one block-table lookup per thread per tile.
+  constexpr int ROWS_PER_PASS = THREADS / CHUNKS * 8;  // keys covered by one pass of the block
+  const bool page_fast = (ps & 7) == 0;
+  auto load_tile = [&](int tile, int stage) {
+    unsigned char* k_dst = kv_s + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* v_dst = k_dst + TILE_BYTES;
+    const int base = k_begin + tile * TILE;
+    const int chunk = tid % CHUNKS;
+    for (int r0 = (tid / CHUNKS) * 8; r0 < TILE; r0 += ROWS_PER_PASS) {
+      const int j0 = base + r0;
+      if (page_fast) {
+        long src = 0;
+        if (j0 < k_end && j0 + 8 > lo) {
+          const int page = bt[j0 / ps];
+          src = (((long)page * nkv + kvh) * ps + (j0 % ps)) * D + chunk * 8;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = j0 + i;
+          const bool valid = j >= lo && j < k_end;
+          const int off = swz<D>(r0 + i, chunk);
+          cp_async16(smem_u32(k_dst + off), kpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
+          cp_async16(smem_u32(v_dst + off), vpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
+        }
+      } else {
+        for (int i = 0; i < 8; ++i) {
+          const int j = j0 + i;
+          const bool valid = j >= lo && j < k_end;
+          long src = 0;
+          if (valid) {
+            const int page = bt[j / ps];
+            src = (((long)page * nkv + kvh) * ps + (j % ps)) * D + chunk * 8;
+          }
+          const int off = swz<D>(r0 + i, chunk);
+          cp_async16(smem_u32(k_dst + off), kpages + src, valid ? 16 : 0);
+          cp_async16(smem_u32(v_dst + off), vpages + src, valid ? 16 : 0);
+        }
+      }
+    }
+  };
+
+  for (int s = 0; s < stages - 1; ++s) {
+    if (s < num_tiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  __syncthreads();  // q_s is complete
+
+  uint32_t qa[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks)
+    ldmatrix_x4(qa[ks], smem_u32(q_s + swz<D>(lane & 15, 2 * ks + (lane >> 4))));
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // rows lane/4 and lane/4 + 8, in units of raw scores
+  float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
+
+  for (int tile = 0; tile < num_tiles; ++tile) {
+    if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
+    __syncthreads();
+    {
+      const int nxt = tile + stages - 1;
+      if (nxt < num_tiles) load_tile(nxt, nxt % stages);
+      cp_async_commit();
+    }
+    const unsigned char* k_t = kv_s + (size_t)(tile % stages) * 2 * TILE_BYTES;
+    const unsigned char* v_t = k_t + TILE_BYTES;
+    const int key0 = k_begin + tile * TILE + warp * 16;  // this warp's 16 keys
+    if (key0 >= k_end) continue;                          // (uniform per warp)
+
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kb[4];
+      const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      ldmatrix_x4(kb, smem_u32(k_t + swz<D>(row, 2 * ks + ((lane >> 3) & 1))));
+      mma_bf16(s[0], qa[ks], kb[0], kb[1]);
+      mma_bf16(s[1], qa[ks], kb[2], kb[3]);
+    }
+    // mask, running max
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = key0 + n * 8 + 2 * (lane & 3) + (e & 1);
+        if (j < lo || j >= k_end) s[n][e] = -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+      }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = exp2f((m_run[r] - m_use[r]) * scale_log2);  // m_run = -inf -> 0
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+    uint32_t pa[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pv[n][e] = exp2f((s[n][e] - m_use[e >> 1]) * scale_log2);
+          l_run[e >> 1] += pv[n][e];
+        }
+      pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+      pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+      pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+      pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // the running max moved
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      uint32_t vb[4];
+      const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      ldmatrix_x4_trans(vb, smem_u32(v_t + swz<D>(row, 2 * i + (lane >> 4))));
+      mma_bf16(o[2 * i], pa, vb[0], vb[1]);
+      mma_bf16(o[2 * i + 1], pa, vb[2], vb[3]);
+    }
+  }
+
+  // ---- merge the 4 warps ------------------------------------------------------------------
+  cp_async_wait<0>();
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float* o_s = reinterpret_cast<float*>(kv_s);          // [WARPS][16][D]
+  float* ml_s = o_s + WARPS * 16 * D;                   // [WARPS][16][2]
+  {
+    const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      float* base = o_s + ((size_t)warp * 16) * D + i * 8 + c0;
+      base[(size_t)r0 * D] = o[i][0];
+      base[(size_t)r0 * D + 1] = o[i][1];
+      base[(size_t)(r0 + 8) * D] = o[i][2];
+      base[(size_t)(r0 + 8) * D + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      ml_s[(warp * 16 + r0) * 2] = m_run[0];
+      ml_s[(warp * 16 + r0) * 2 + 1] = l_run[0];
+      ml_s[(warp * 16 + r0 + 8) * 2] = m_run[1];
+      ml_s[(warp * 16 + r0 + 8) * 2 + 1] = l_run[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += THREADS) {
+    const int g = idx / D, d = idx - g * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, ml_s[(w * 16 + g) * 2]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = ml_s[(w * 16 + g) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f((mw - m) * scale_log2);
+      l += ml_s[(w * 16 + g) * 2 + 1] * f;
+      acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+    }
+    const int head = kvh * G + g;
+    const float val = acc / l;
+    if (num_splits == 1) {
+      out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(val);
+    } else {
+      mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = val;
+      if (d == 0) mid_lse[((long)slot * nq + head) * num_splits + split] = m * scale_log2 + log2f(l);
+    }
+  }
+}
+
+// out[token of seq, head, :] = sum_s w_s * mid_o[s] / sum_s w_s,  w_s = 2^(lse_s - max lse)
+__global__ void decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ seq_list,
+                                      bf16* __restrict__ out, int nq, int D, int num_splits) {
+  const int slot = blockIdx.y, head = blockIdx.x;
+  const int seq = seq_list ? seq_list[slot] : slot;
+  const int tok = cu_seqlens[seq];
+  const float* lse = mid_lse + ((long)slot * nq + head) * num_splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, lse[s]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f, wsum = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ls = lse[s];
+      if (ls == -INFINITY) continue;
+      const float w = exp2f(ls - mx);
+      wsum += w;
+      acc += w * mid_o[(((long)slot * nq + head) * num_splits + s) * D + d];
+    }
+    out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(acc / wsum);
+  }
+}
+
+template <int D>
+int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
+                  int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
+                  float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
+                  int num_splits, cudaStream_t stream) {
+  const int stages = 2;
+  const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
+  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
+  const size_t smem = 16 * D * 2 + (pipe > merge ? pipe : merge);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid(num_splits, nkv, num_seqs);
+  decode_attention_kernel<D><<<grid, THREADS, smem, stream>>>(
+      q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq,
+      nkv, ps, scale * 1.4426950408889634f, window, num_splits, stages);
+  if (q3_launch_status() != Q3_OK) return Q3_ERR_LAUNCH;
+  if (num_splits > 1) {
+    dim3 cgrid(nq, num_seqs);
+    decode_combine_kernel<<<cgrid, D < 128 ? D : 128, 0, stream>>>(mid_o, mid_lse, cu_seqlens, seq_list, out, nq, D,
+                                                                   num_splits);
+  }
+  return q3_launch_status();
+}
+
+}  // namespace
+
+// Attention for `num_seqs` one-token sequences: those listed in seq_list (indices into
+// kv_lens / cu_seqlens / block_table rows), or sequences 0..num_seqs-1 when it is null.
+// Scratch: mid_o needs num_seqs*nq*num_splits*D floats and mid_lse num_seqs*nq*num_splits
+// floats when num_splits > 1 (both may be null otherwise).  head_dim 64, 128 or 256;
+// group size nq/nkv at most 16; bfloat16 only.
+Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void* kpages, const void* vpages,
+                                        const int* block_table, int max_pages, const int* kv_lens,
+                                        const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
+                                        float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
+                                        int window, int num_splits, cudaStream_t stream) {
+  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
+  if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
+  if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
+  if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
+  if (num_seqs == 0) return Q3_OK;
+  if (num_seqs > 65535 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
+#define Q3_DECODE_CASE(DIM)                                                                                       \
+  case DIM:                                                                                                       \
+    return launch_decode<DIM>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,  \
+                              max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs, nq, \
+                              nkv, ps, scale, window, num_splits, stream)
+  switch (D) {
+    Q3_DECODE_CASE(64);
+    Q3_DECODE_CASE(128);
+    Q3_DECODE_CASE(256);
+    default:
+      return Q3_ERR_UNSUPPORTED;
+  }
+#undef Q3_DECODE_CASE
+}

@@ -62,8 +62,16 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                        c_void_p],
     },
+    "attention_decode": {
+        "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                      c_float, c_int, c_int, c_void_p],
+    },
     "gemm_f32": {
         "q3_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "gemm_small_m": {
+        "q3_gemm_small_m": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "sampling": {
         "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -166,10 +174,49 @@ class CudaOps:
         if head_dim % 8 or head_dim > 256:
             raise KernelError(
                 f"paged_attention: head_dim={head_dim} is not supported (multiples of 8 up to 256 are)")
+        if (step is not None and step.decode_only and out.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
+                and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
+            return self.paged_attention_decode(
+                q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, k_pages=k_pages,
+                v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
+                out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
+                max_kv_len=step.extras.get("captured_width", 0) * page_size or step.max_kv_len)
         self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,
                   head_dim, page_size, float(scale), int(window or 0))
+        return out
+
+    SM_COUNT = 148
+    DECODE_MIN_KEYS_PER_SPLIT = 256
+
+    def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int) -> int:
+        """How many slices each sequence's keys are cut into: enough blocks to fill the GPU
+        about six times over (three blocks are resident per SM), but no slice shorter than 256 keys.  Depends only on sizes that
+        are fixed for a captured step (qwen3_runtime/kernels/triton_decode.py:122-133 has the
+        same shape of rule for an RTX 4090)."""
+        by_length = max(1, -(-max_kv_len // self.DECODE_MIN_KEYS_PER_SPLIT))
+        by_blocks = max(1, -(-6 * self.SM_COUNT // (num_seqs * num_kv_heads)))
+        return int(min(by_length, by_blocks, 64))
+
+    def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
+                               block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
+                               max_kv_len, seq_list=None, num_splits=None):
+        """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu)."""
+        if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
+            raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
+        if window:
+            max_kv_len = min(max_kv_len, int(window) + 63)
+        splits = num_splits or self.decode_splits(num_seqs, num_kv_heads, max_kv_len)
+        mid_o = mid_lse = None
+        if splits > 1:
+            mid_o = torch.empty((num_seqs, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
+            mid_lse = torch.empty((num_seqs, num_heads, splits), dtype=torch.float32, device=out.device)
+        self.launches += 1 if splits > 1 else 0  # the merge kernel
+        self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
+                   _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                   _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
+                   num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits)
         return out
 
     # ---- matrix products ----------------------------------------------------------------
@@ -187,11 +234,36 @@ class CudaOps:
             self._call("gemm_f32", "q3_gemm_f32", "gemm_f32", _ptr(x), x.stride(0), _ptr(weight),
                        weight.stride(0), _ptr(out), out.stride(0), M, N, K)
             return out
+        if self._small_m_ok(x, weight):
+            odt = out_dtype or x.dtype
+            if out is None:
+                out = torch.empty((M, N), dtype=odt, device=x.device)
+            self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m", 1 if odt == torch.float32 else 0,
+                       _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K)
+            return out
         if out_dtype is not None and out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         if out is None:
             return torch.mm(x, weight.t())
         return torch.mm(x, weight.t(), out=out)
+
+    SMALL_M = 16
+
+    def _small_m_ok(self, x, weight) -> bool:
+        return (x.dtype == torch.bfloat16 and x.shape[0] <= self.SMALL_M and x.shape[1] % 8 == 0
+                and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1
+                and weight.stride(1) == 1 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def gated_linear(self, x, gate_up_weight, out):
+        """``out = silu(x @ W_gate^T) * (x @ W_up^T)`` with ``gate_up_weight = [W_gate; W_up]``:
+        one kernel for a handful of tokens, else the product followed by the SwiGLU kernel."""
+        M, K = x.shape
+        I = out.shape[1]
+        if self._small_m_ok(x, gate_up_weight):
+            self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m(swiglu)", 2, _ptr(x), x.stride(0),
+                       _ptr(gate_up_weight), gate_up_weight.stride(0), _ptr(out), out.stride(0), M, I, K)
+            return out
+        return self.silu_mul(self.linear(x, gate_up_weight), out)
 
     # ---- sampling ---------------------------------------------------------------------
     def argmax(self, logits, want_logprob=False):

@@ -33,12 +33,11 @@ class GatedMLP(Part):
         self.down_weight = tensors["down_proj.weight"].contiguous()
 
     def kernel_groups(self):
-        return ["norm", "gemm_f32"] if self.ctx.dtype == torch.float32 else ["norm"]
+        return ["norm", "gemm_f32"] if self.ctx.dtype == torch.float32 else ["norm", "gemm_small_m"]
 
     def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
-        gate_up = self.ops.linear(h, self.gate_up_weight)
         mid = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        self.ops.silu_mul(gate_up, mid)
+        self.ops.gated_linear(h, self.gate_up_weight, mid)
         return self.ops.linear(mid, self.down_weight)
 
 

@@ -108,6 +108,9 @@ class TorchOps:
             return out
         return res
 
+    def gated_linear(self, x, gate_up_weight, out):
+        return self.silu_mul(self.linear(x, gate_up_weight), out)
+
     # ---- sampling ---------------------------------------------------------------------
     def argmax(self, logits, want_logprob=False):
         tok = logits.argmax(-1).to(torch.int32)

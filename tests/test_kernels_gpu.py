@@ -237,6 +237,73 @@ def test_attention_ignores_what_lies_beyond_a_sequence(ops, dtype):
     close(out, ref, dtype, "attention with poisoned free slots", f32_tol=1e-5, bf16_tol=1e-2)
 
 
+def decode_problem(nq, nkv, D, ps, lens, seed):
+    pr = attention_problem(nq, nkv, D, ps, lens, [1] * len(lens), torch.bfloat16, seed)
+    pr["kv_lens"] = torch.tensor(lens, dtype=torch.int32).cuda()
+    pr["cu"] = torch.arange(len(lens) + 1, dtype=torch.int32).cuda()
+    return pr
+
+
+def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list=None, out=None):
+    out = out if out is not None else torch.zeros((pr["T"], nq * D), dtype=torch.bfloat16, device="cuda")
+    n = len(lens) if seq_list is None else seq_list.numel()
+    ops.paged_attention_decode(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D,
+                               k_pages=pr["k"], v_pages=pr["v"], block_table=pr["bt"], kv_lens=pr["kv_lens"],
+                               cu_seqlens=pr["cu"], out=out, page_size=ps, scale=1 / math.sqrt(D), window=window,
+                               num_seqs=n, max_kv_len=max(lens), seq_list=seq_list, num_splits=splits)
+    return out
+
+
+@pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 16), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
+                                          (14, 2, 64, 3), (40, 8, 128, 64)])
+@pytest.mark.parametrize("splits", [None, 1, 3, 8])
+def test_decode_attention_split_kv(ops, nq, nkv, D, ps, splits):
+    lens = [1, 63, 64, 65, 700, 129, 2, 1000]
+    pr = decode_problem(nq, nkv, D, ps, lens, 80)
+    want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16)
+    got = run_decode(ops, pr, nq, nkv, D, ps, lens, splits=splits)
+    close(got, want, torch.bfloat16, f"decode attention splits={splits}", bf16_tol=1e-2)
+    for window in (1, 64, 100):
+        want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16, window=window)
+        got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
+        close(got, want, torch.bfloat16, f"decode attention window={window} splits={splits}", bf16_tol=1e-2)
+
+
+def test_decode_attention_far_key_poison_and_subset(ops):
+    nq, nkv, D, ps = 32, 8, 128, 16
+    lens = [900, 333, 64]
+    pr = decode_problem(nq, nkv, D, ps, lens, 81)
+    # everything that is not a live key is NaN
+    used = torch.zeros(pr["k"].shape[0], ps, dtype=torch.bool)
+    for b, n in enumerate(lens):
+        for j in range(n):
+            used[int(pr["bt"][b, j // ps]), j % ps] = True
+    mask = (~used).cuda()[:, None, :, None].expand_as(pr["k"])
+    clean_k, clean_v = pr["k"].clone(), pr["v"].clone()
+    pr["k"][mask] = float("nan")
+    pr["v"][mask] = float("nan")
+    got = run_decode(ops, pr, nq, nkv, D, ps, lens, splits=5)
+    assert torch.isfinite(got).all()
+    pr2 = dict(pr, k=torch.where(mask, torch.zeros_like(clean_k), clean_k), v=torch.where(mask, torch.zeros_like(clean_v), clean_v))
+    close(got, run_attention(REF, pr2, nq, nkv, D, ps, torch.bfloat16), torch.bfloat16, "poisoned pool", bf16_tol=1e-2)
+    # one far key carries all the weight
+    for far in (0, 77, 16 * 20 + 15, 899):
+        pr3 = dict(pr2, k=pr2["k"] * 0.01, q=pr2["q"].clone())
+        pr3["q"][0, : nq * D] = 4.0
+        page, off = int(pr["bt"][0, far // ps]), far % ps
+        pr3["k"][page, :, off, :] = 4.0
+        got = run_decode(ops, pr3, nq, nkv, D, ps, lens, splits=4)
+        want = pr3["v"][page, :, off, :].float().repeat_interleave(nq // nkv, dim=0).reshape(-1)
+        close(got[0], want, torch.bfloat16, f"far key {far}", bf16_tol=1e-6)
+    # a subset of the sequences (a mixed step hands the one-token sequences to this kernel)
+    seqs = torch.tensor([2, 0], dtype=torch.int32).cuda()
+    out = torch.full((3, nq * D), 7.0, dtype=torch.bfloat16, device="cuda")
+    run_decode(ops, pr2, nq, nkv, D, ps, lens, splits=3, seq_list=seqs, out=out)
+    full = run_attention(REF, pr2, nq, nkv, D, ps, torch.bfloat16)
+    close(out[[0, 2]], full[[0, 2]], torch.bfloat16, "subset", bf16_tol=1e-2)
+    assert bool((out[1] == 7.0).all())
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 2560, 2560), (7, 333, 130), (64, 96, 64), (65, 160, 96), (300, 301, 80),
                                    (2, 1000, 9)])
 def test_gemm_f32_is_exact_fp32_and_row_invariant(ops, M, N, K):
@@ -264,6 +331,40 @@ def test_linear_bf16(ops, M, N, K):
     f32 = ops.linear(x, w, out_dtype=torch.float32)
     assert f32.dtype == torch.float32
     close(f32, want, torch.float32, "linear bf16 -> f32", f32_tol=1e-4)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(2560, 2560), (6144, 2560), (2560, 9728), (2560, 4096), (301, 80), (160, 96),
+                                 (151936, 64), (24, 8), (17, 4096)])
+def test_gemm_small_m(ops, M, N, K):
+    x = rand((M, K), torch.bfloat16, 54)
+    w = rand((N, K), torch.bfloat16, 55, scale=0.05)
+    assert ops._small_m_ok(x, w)
+    want = x.float() @ w.float().t()
+    close(ops.linear(x, w), want, torch.bfloat16, "small-M linear", bf16_tol=1e-2)
+    close(ops.linear(x, w, out_dtype=torch.float32), want, torch.float32, "small-M linear fp32 out", f32_tol=2e-5)
+    # a view with a row stride (the q rows of the fused qkv weight) and a strided input
+    wide = rand((M, K + 8), torch.bfloat16, 56)
+    close(ops.linear(wide[:, :K], w[: max(1, N // 2)]), wide[:, :K].float() @ w[: max(1, N // 2)].float().t(),
+          torch.bfloat16, "strided", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(9728, 2560), (112, 80), (160, 96), (24, 4096)])
+def test_gated_linear_small_m(ops, M, I, K):
+    x = rand((M, K), torch.bfloat16, 57)
+    w = rand((2 * I, K), torch.bfloat16, 58, scale=0.05)
+    out = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
+    ops.gated_linear(x, w, out)
+    g, u = x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t()
+    close(out, torch.nn.functional.silu(g) * u, torch.bfloat16, "fused SwiGLU", bf16_tol=1e-2)
+    # more tokens than the fused kernel takes: product, then the SwiGLU kernel
+    xb = rand((40, K), torch.bfloat16, 59)
+    outb = torch.empty((40, I), dtype=torch.bfloat16, device="cuda")
+    ops.gated_linear(xb, w, outb)
+    gb, ub = xb.float() @ w[:I].float().t(), xb.float() @ w[I:].float().t()
+    close(outb, torch.nn.functional.silu(gb.bfloat16().float()) * ub.bfloat16().float(), torch.bfloat16,
+          "unfused SwiGLU", bf16_tol=2e-2)
 
 
 @pytest.mark.parametrize("V,R", [(151936, 3), (301, 5), (32, 1), (4099, 64)])
