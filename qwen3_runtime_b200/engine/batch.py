@@ -112,7 +112,7 @@ class BatchBuilder:
         # section offsets inside the int32 buffer (each 4-int aligned => 16-byte aligned)
         off, sections = 0, {}
         for name, size in (("ids", T), ("pos", T), ("seq", T), ("cu", B + 1), ("kv", B), ("slot", B),
-                           ("rows", T), *[(f"bt{g}", B * width) for g in range(n_paged)]):
+                           ("rows", T), ("single", B), *[(f"bt{g}", B * width) for g in range(n_paged)]):
             sections[name] = (off, size)
             off += _round_up(size, 4)
         host, dev = self._buffers(off)
@@ -154,6 +154,8 @@ class BatchBuilder:
             slot[b] = scratch_slot
             for g in range(n_paged):
                 sec(f"bt{g}")[b * width:(b + 1) * width] = scratch_page
+        singles = [b for b, n in enumerate(lens) if n == 1] + list(range(B_real, B))
+        sec("single")[:len(singles)] = singles
         if all_rows:
             rows_np = np.arange(T, dtype=np.int32)
         else:
@@ -178,5 +180,6 @@ class BatchBuilder:
             logit_rows=dsec("rows", R), num_logit_rows=R,
             max_query_len=max(lens), max_kv_len=int(kv[:B].max()),
             decode_only=all(n == 1 for n in lens),
+            single_seqs=dsec("single", len(singles)), num_single=len(singles),
             host_cu_seqlens=[int(x) for x in cu], host_kv_lens=[int(x) for x in kv[:B]],
         )

@@ -67,6 +67,11 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_float, c_int, c_int, c_void_p],
     },
+    "attention_prefill": {
+        "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                       c_void_p],
+    },
     "gemm_f32": {
         "q3_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -181,6 +186,27 @@ class CudaOps:
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
                 max_kv_len=step.extras.get("captured_width", 0) * page_size or step.max_kv_len)
+        if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
+                and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
+            # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
+            group = num_heads // num_kv_heads
+            cu = step.host_cu_seqlens
+            qlens = [cu[b + 1] - cu[b] for b in range(step.num_seqs)]
+            work = sum(-(-n * group // 128) for n in qlens if n > 1)
+            if work:
+                self._call("attention_prefill", "q3_paged_attention_prefill", "paged_attention_prefill",
+                           _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                           block_table.shape[1], _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out),
+                           step.num_seqs, work, num_heads, num_kv_heads, head_dim, page_size, float(scale),
+                           int(window or 0), 1)
+            if step.num_single:
+                longest = max(kv for kv, n in zip(step.host_kv_lens, qlens) if n == 1)
+                self.paged_attention_decode(
+                    q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                    k_pages=k_pages, v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens,
+                    cu_seqlens=step.cu_seqlens, out=out, page_size=page_size, scale=scale, window=window,
+                    num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs)
+            return out
         self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,

@@ -60,6 +60,8 @@ class StepContext:
     max_query_len: int  # host copies of batch extremes, for kernel choice
     max_kv_len: int
     decode_only: bool  # every sequence brings exactly one token
+    single_seqs: torch.Tensor | None = None  # [num_single] sequences that bring exactly one token
+    num_single: int = 0
     # host copies (lists) for parts that need them without a device read
     host_cu_seqlens: list[int] = field(default_factory=list)
     host_kv_lens: list[int] = field(default_factory=list)

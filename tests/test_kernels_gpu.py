@@ -237,6 +237,73 @@ def test_attention_ignores_what_lies_beyond_a_sequence(ops, dtype):
     close(out, ref, dtype, "attention with poisoned free slots", f32_tol=1e-5, bf16_tol=1e-2)
 
 
+def step_for(lens, qlens):
+    """The fields of a StepContext that the attention wrapper reads."""
+    from types import SimpleNamespace
+
+    cu = [0]
+    for n in qlens:
+        cu.append(cu[-1] + n)
+    singles = [b for b, n in enumerate(qlens) if n == 1]
+    return SimpleNamespace(
+        decode_only=all(n == 1 for n in qlens), num_seqs=len(lens), host_cu_seqlens=cu, host_kv_lens=list(lens),
+        kv_lens=torch.tensor(lens, dtype=torch.int32).cuda(), cu_seqlens=torch.tensor(cu, dtype=torch.int32).cuda(),
+        single_seqs=torch.tensor(singles, dtype=torch.int32).cuda(), num_single=len(singles),
+        max_kv_len=max(lens), extras={})
+
+
+@pytest.mark.parametrize("nq,nkv,D,ps,window", [(32, 8, 128, 16, None), (8, 8, 64, 8, None), (6, 2, 128, 3, None),
+                                                 (16, 1, 64, 32, 50), (14, 2, 128, 16, 129), (4, 4, 128, 64, 1)])
+def test_prefill_attention_tensor_cores(ops, nq, nkv, D, ps, window):
+    """Whole prompts, portions after cached tokens, tiny portions and single tokens in one batch."""
+    lens = [300, 1, 77, 700, 64, 130, 2, 333]
+    qlens = [1, 1, 77, 200, 2, 130, 2, 33]
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, torch.bfloat16, 90)
+    want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16, window)
+    out = torch.full((pr["T"], nq * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D, k_pages=pr["k"],
+                        v_pages=pr["v"], block_table=pr["bt"], token_seq=pr["seq"], positions=pr["pos"], out=out,
+                        page_size=ps, scale=1 / math.sqrt(D), window=window, step=step_for(lens, qlens))
+    assert torch.isfinite(out).all(), "every row is written"
+    close(out, want, torch.bfloat16, "prefill attention", bf16_tol=1e-2)
+
+
+def test_prefill_attention_far_key_diagonal_and_poison(ops):
+    nq, nkv, D, ps = 8, 2, 128, 16
+    lens, qlens = [900, 257], [300, 257]
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, torch.bfloat16, 91)
+    used = torch.zeros(pr["k"].shape[0], ps, dtype=torch.bool)
+    for b, n in enumerate(lens):
+        for j in range(n):
+            used[int(pr["bt"][b, j // ps]), j % ps] = True
+    mask = (~used).cuda()[:, None, :, None].expand_as(pr["k"])
+    pr["k"][mask] = float("nan")
+    pr["v"][mask] = float("nan")
+    step = step_for(lens, qlens)
+
+    def run(p):
+        out = torch.zeros((p["T"], nq * D), dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(p["q"], p["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D, k_pages=p["k"],
+                            v_pages=p["v"], block_table=p["bt"], token_seq=p["seq"], positions=p["pos"], out=out,
+                            page_size=ps, scale=1 / math.sqrt(D), window=None, step=step)
+        return out
+
+    assert torch.isfinite(run(pr)).all()
+    # one key carries all the weight for every query that can see it, none for the others
+    for far in (0, 599, 600, 777, 899):
+        p2 = dict(pr, k=pr["k"] * 0.01, q=pr["q"].clone())
+        p2["q"][:300, : nq * D] = 4.0
+        page, off = int(pr["bt"][0, far // ps]), far % ps
+        p2["k"][page, :, off, :] = 4.0
+        out = run(p2)
+        want = p2["v"][page, :, off, :].float().repeat_interleave(nq // nkv, dim=0).reshape(-1)
+        sees = torch.arange(600, 900) >= far  # query i of the portion sits at position 600 + i
+        got = out[:300].float().cpu()
+        assert float((got[sees] - want.cpu()).abs().max()) <= 1e-6 * max(1.0, float(want.abs().max()))
+        if (~sees).any():
+            assert float((got[~sees] - want.cpu()).abs().max()) > 0.05
+
+
 def decode_problem(nq, nkv, D, ps, lens, seed):
     pr = attention_problem(nq, nkv, D, ps, lens, [1] * len(lens), torch.bfloat16, seed)
     pr["kv_lens"] = torch.tensor(lens, dtype=torch.int32).cuda()
