@@ -41,6 +41,54 @@ __global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restri
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>((vals[i] * rstd) * w[i]);
 }
 
+// The same with 16-byte accesses: H a multiple of 8 and every row 16-byte aligned.
+template <typename T>
+__global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __restrict__ resid,
+                                      const int* __restrict__ ids, const T* __restrict__ table,
+                                      const int* __restrict__ rows, const float* __restrict__ w,
+                                      T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+  extern __shared__ float vals[];
+  float* red = vals + H;
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  const T* trow = nullptr;
+  if (ids) {
+    int id = ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    trow = table + (long)id * H;
+  }
+  const T* prow = pending ? pending + src * H : nullptr;
+  float* rrow = resid ? resid + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8];
+    if (trow) load8(trow + i, v); else load8(rrow + i, v);
+    if (prow) {
+      float pv[8];
+      load8(prow + i, pv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += pv[e];
+    }
+    if (write_resid) store8(rrow + i, v);
+    store8(vals + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = rsqrtf(total / (float)H + eps);
+  T* orow = out + (long)r * H;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8], wv[8];
+    load8(vals + i, v);
+    load8(w + i, wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (v[e] * rstd) * wv[e];
+    store8(orow + i, v);
+  }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 template <typename T>
 static int launch_fused_norm(const void* pending, float* resid, const int* ids, const void* table,
                              const int* rows, const float* w, void* out, int num_rows, int H, float eps,
@@ -50,6 +98,17 @@ static int launch_fused_norm(const void* pending, float* resid, const int* ids, 
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(fused_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const bool vec = H % 8 == 0 && aligned16(pending) && aligned16(resid) && aligned16(table) && aligned16(w) &&
+                   aligned16(out);
+  if (vec) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(fused_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int threads = ((H / 8 + 31) / 32) * 32;
+    threads = threads > 1024 ? 1024 : threads;
+    fused_norm_vec_kernel<T><<<num_rows, threads, smem, stream>>>(
+        (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
+    return q3_launch_status();
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   fused_norm_kernel<T><<<num_rows, threads, smem, stream>>>(
       (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
@@ -86,11 +145,37 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
   out[idx] = from_f32<T>((g / (1.f + expf(-g))) * u);
 }
 
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long chunks, int I) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= chunks) return;
+  const int per_row = I / 8;
+  const long t = idx / per_row;
+  const int i = (int)(idx - t * per_row) * 8;
+  float g[8], u[8];
+  load8(gu + t * 2 * I + i, g);
+  load8(gu + t * 2 * I + I + i, u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) g[e] = (g[e] / (1.f + expf(-g[e]))) * u[e];
+  store8(out + t * I + i, g);
+}
+
 Q3_EXPORT int q3_silu_mul(int dtype, const void* gu, void* out, int num_rows, int I, cudaStream_t stream) {
   if (!gu || !out || I < 1) return Q3_ERR_ARGUMENT;
   const long total = (long)num_rows * I;
   if (total == 0) return Q3_OK;
   const int threads = 256;
+  if (I % 8 == 0 && aligned16(gu) && aligned16(out)) {
+    const long chunks = total / 8;
+    const unsigned vblocks = (unsigned)((chunks + threads - 1) / threads);
+    if (dtype == Q3_DTYPE_F32)
+      silu_mul_vec_kernel<float><<<vblocks, threads, 0, stream>>>((const float*)gu, (float*)out, chunks, I);
+    else if (dtype == Q3_DTYPE_BF16)
+      silu_mul_vec_kernel<bf16><<<vblocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, chunks, I);
+    else
+      return Q3_ERR_ARGUMENT;
+    return q3_launch_status();
+  }
   const long blocks = (total + threads - 1) / threads;
   if (dtype == Q3_DTYPE_F32)
     silu_mul_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I);

@@ -67,6 +67,92 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   }
 }
 
+// The same with 16-byte accesses, for head sizes 16, 32, 64, 128, 256 with the rotation over
+// the whole head (or none): D/16 threads per (token, head); a thread owns elements
+// [8c, 8c+8) and their rotation partners [8c + D/2, 8c + D/2 + 8).
+template <typename T>
+__global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_stride, int nq, int nkv, int D,
+                                              const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                              float eps, const float* __restrict__ cos_t,
+                                              const float* __restrict__ sin_t, int max_pos,
+                                              const int* __restrict__ positions,
+                                              const int* __restrict__ token_seq,
+                                              const int* __restrict__ block_table, int max_pages,
+                                              T* __restrict__ kpages, T* __restrict__ vpages, int ps,
+                                              int num_tokens, int write_kv) {
+  const int tph = D / 16;  // threads per head: a power of two, at most 16
+  const int heads = write_kv ? nq + 2 * nkv : nq;
+  const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long item = gid / tph;
+  const int c = (int)(gid - item * tph);
+  const bool live = item < (long)num_tokens * heads;
+  const int t = live ? (int)(item / heads) : 0;
+  const int hi = live ? (int)(item - (long)t * heads) : 0;
+  const int half = D / 2;
+  T* x = qkv + (long)t * row_stride + (long)hi * D;
+  int p = positions[t];
+  long cache_row = -1;
+  if (live && hi >= nq && p >= 0 && p / ps < max_pages) {
+    const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
+    const int page = block_table[(long)token_seq[t] * max_pages + p / ps];
+    if (page >= 0) cache_row = (((long)page * nkv + kvh) * ps + (p % ps)) * D;
+  }
+  float a[8], b[8];
+  if (live) {
+    load8(x + 8 * c, a);
+    load8(x + half + 8 * c, b);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = b[e] = 0.f;
+  }
+  const bool is_v = hi >= nq + nkv;
+  const float* w = hi < nq ? q_w : k_w;
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+  for (int o = tph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!live) return;
+  if (is_v) {
+    if (cache_row >= 0) {
+      store8(vpages + cache_row + 8 * c, a);
+      store8(vpages + cache_row + half + 8 * c, b);
+    }
+    return;
+  }
+  if (w) {
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    float wa[8], wb[8];
+    load8(w + 8 * c, wa);
+    load8(w + half + 8 * c, wb);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      a[e] = (a[e] * rstd) * wa[e];
+      b[e] = (b[e] * rstd) * wb[e];
+    }
+  }
+  if (cos_t) {
+    if (p >= max_pos) p = max_pos - 1;
+    float cs[8], sn[8];
+    load8(cos_t + (long)p * half + 8 * c, cs);
+    load8(sin_t + (long)p * half + 8 * c, sn);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ya = a[e], yb = b[e];
+      a[e] = ya * cs[e] - yb * sn[e];
+      b[e] = yb * cs[e] + ya * sn[e];
+    }
+  }
+  if (hi < nq) {
+    store8(x + 8 * c, a);
+    store8(x + half + 8 * c, b);
+  } else if (cache_row >= 0) {
+    store8(kpages + cache_row + 8 * c, a);
+    store8(kpages + cache_row + half + 8 * c, b);
+  }
+}
+
+static inline bool rk_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq, int nkv, int D,
                                     const float* q_w, const float* k_w, float eps, const float* cos_t,
                                     const float* sin_t, int rot_half, int max_pos, const int* positions,
@@ -76,6 +162,26 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
   if (write_kv && (!token_seq || !block_table || !kpages || !vpages || ps < 1)) return Q3_ERR_ARGUMENT;
   if (cos_t && (!sin_t || rot_half < 1 || 2 * rot_half > D)) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
+  const int tph = D / 16;
+  const bool vec = D % 16 == 0 && tph >= 1 && tph <= 16 && (tph & (tph - 1)) == 0 && row_stride % 8 == 0 &&
+                   (!cos_t || 2 * rot_half == D) && rk_aligned16(qkv) && rk_aligned16(kpages) &&
+                   rk_aligned16(vpages) && rk_aligned16(q_w) && rk_aligned16(k_w) && rk_aligned16(cos_t) &&
+                   rk_aligned16(sin_t);
+  if (vec) {
+    const long threads_total = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq) * tph;
+    const unsigned vblocks = (unsigned)((threads_total + 255) / 256);
+    if (dtype == Q3_DTYPE_F32)
+      qk_norm_rope_store_vec_kernel<float><<<vblocks, 256, 0, stream>>>(
+          (float*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
+          block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+    else if (dtype == Q3_DTYPE_BF16)
+      qk_norm_rope_store_vec_kernel<bf16><<<vblocks, 256, 0, stream>>>(
+          (bf16*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
+          block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+    else
+      return Q3_ERR_ARGUMENT;
+    return q3_launch_status();
+  }
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * D * sizeof(float);
   if (smem > 48 * 1024) return Q3_ERR_UNSUPPORTED;
