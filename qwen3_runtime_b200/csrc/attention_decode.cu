@@ -343,3 +343,73 @@ Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void*
   }
 #undef Q3_DECODE_CASE
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that may not allocate: the slices' partial results live in
+// a fixed array inside this library.  See no_alloc.h for who needs this and for the rules
+// (shared array, first call outside stream capture, overlapping calls race).
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) float q3_no_alloc_scratch[Q3_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+float* g_no_alloc_ptr[NO_ALLOC_MAX_DEVICES];  // device address of the array, per device, once known
+std::mutex g_no_alloc_mutex;
+thread_local char g_no_alloc_error[256] = "";
+
+// In host code `q3_no_alloc_scratch` is only a handle for the runtime, not an address a kernel
+// can use; the address on the current device comes from cudaGetSymbolAddress.
+int no_alloc_scratch(float** ptr) {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NO_ALLOC_MAX_DEVICES) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "no current CUDA device (or device index above %d)",
+             NO_ALLOC_MAX_DEVICES - 1);
+    return Q3_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+  if (!g_no_alloc_ptr[device]) {
+    void* address = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&address, q3_no_alloc_scratch);
+    if (err != cudaSuccess || !address) {
+      snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "cudaGetSymbolAddress failed on device %d: %s", device,
+               cudaGetErrorString(err));
+      return Q3_ERR_LAUNCH;
+    }
+    g_no_alloc_ptr[device] = static_cast<float*>(address);
+  }
+  *ptr = g_no_alloc_ptr[device];
+  return Q3_OK;
+}
+}  // namespace
+
+Q3_EXPORT const char* q3_no_alloc_last_error(void) { return g_no_alloc_error; }
+
+Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, const void* kpages, const void* vpages,
+                                                 const int* block_table, int max_pages, const int* kv_lens,
+                                                 const int* cu_seqlens, const int* seq_list, void* out, int num_seqs,
+                                                 int nq, int nkv, int D, int ps, float scale, int window,
+                                                 int num_splits, cudaStream_t stream) {
+  g_no_alloc_error[0] = '\0';
+  if (num_seqs < 0 || nq < 1 || D < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
+  const long long partials = (long long)num_seqs * nq * num_splits;
+  const long long need = partials * ((long long)D + 1);
+  if (need > Q3_NO_ALLOC_SCRATCH_FLOATS) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error,
+             "decode attention without allocation: %d sequences x %d heads x %d slices x (%d + 1) = %lld floats "
+             "of scratch, but the fixed array holds %d; use fewer slices or the allocating entry point",
+             num_seqs, nq, num_splits, D, need, Q3_NO_ALLOC_SCRATCH_FLOATS);
+    return Q3_ERR_SCRATCH_TOO_SMALL;
+  }
+  float* scratch = nullptr;
+  const int status = no_alloc_scratch(&scratch);
+  if (status != Q3_OK) return status;
+  float* mid_o = scratch;                  // [num_seqs, nq, num_splits, D]
+  float* mid_lse = scratch + partials * D; // [num_seqs, nq, num_splits]
+  return q3_paged_attention_decode(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens,
+                                   seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window,
+                                   num_splits, stream);
+}
