@@ -115,3 +115,117 @@ Q3_EXPORT int q3_sample(const float* logits, int num_rows, int V, const float* t
   sample_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, uniform, token, logprob);
   return q3_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Logit processors, in place on one fp32 row per block, in the reference's order
+// (qwen3_runtime/sampling.py:120-135): logit bias -> repetition / presence / frequency
+// penalties -> (greedy stops) -> divide by temperature -> min_p -> top_k -> top_p.
+// ---------------------------------------------------------------------------------------------
+
+// Order-preserving map from float to unsigned: a > b  <=>  key(a) > key(b).
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Bias and penalties (sampling.py:36-72).  counts: scratch of V ints for this row.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+bias_penalty_kernel(float* __restrict__ row, int V, const int* __restrict__ bias_ids,
+                    const float* __restrict__ bias_vals, int n_bias, const int* __restrict__ seen_ids, int n_seen,
+                    int* __restrict__ counts, float repetition, float presence, float frequency) {
+  for (int i = threadIdx.x; i < n_bias; i += blockDim.x) {
+    const int id = bias_ids[i];
+    if (id >= 0 && id < V) atomicAdd(&row[id], bias_vals[i]);
+  }
+  if (n_seen == 0 || (repetition == 1.f && presence == 0.f && frequency == 0.f)) return;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_seen; i += blockDim.x) {
+    const int id = seen_ids[i];
+    if (id >= 0 && id < V) atomicAdd(&counts[id], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const int c = counts[i];
+    if (c == 0) continue;
+    float v = row[i];
+    if (repetition != 1.f) v = v > 0.f ? v / repetition : v * repetition;
+    v -= presence;
+    v -= frequency * (float)c;
+    row[i] = v;
+  }
+}
+
+// Smallest key k such that measure({i : key(x_i) > k}) <= limit, by bisection on the 32-bit key.
+// count_mode: measure = number of elements; else measure = sum of exp(x_i - mx) / z.
+__device__ unsigned cutoff_key(const float* row, int V, bool count_mode, float limit, float mx, float z, float* red) {
+  unsigned lo = 0u, hi = 0xffffffffu;
+  while (lo < hi) {
+    const unsigned mid = lo + ((hi - lo) >> 1);
+    float part = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      if (ordered_key(v) > mid) part += count_mode ? 1.f : expf(v - mx) / z;
+    }
+    const float total = block_sum(part, red);
+    if (total <= limit) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+filter_kernel(float* __restrict__ logits, int V, const float* __restrict__ temperature,
+              const float* __restrict__ min_p, const int* __restrict__ top_k, const float* __restrict__ top_p) {
+  __shared__ float red[33];
+  float* row = logits + (long)blockIdx.x * V;
+  const float temp = temperature[blockIdx.x];
+  const float mp = min_p[blockIdx.x], tp = top_p[blockIdx.x];
+  const int tk = top_k[blockIdx.x];
+  const float lowest = -3.4028234663852886e38f;  // finfo(float32).min, the reference's mask value
+  if (temp != 1.f)
+    for (int i = threadIdx.x; i < V; i += blockDim.x) row[i] = row[i] / temp;
+  __syncthreads();
+  if (mp > 0.f) {  // drop tokens whose probability is below min_p times the largest (sampling.py:75-81)
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = block_max(mx, red);
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (expf(row[i] - mx) < mp) row[i] = -INFINITY;
+    __syncthreads();
+  }
+  if (tk > 0 && tk < V) {  // keep the k largest, ties with the k-th included (sampling.py:96-99)
+    const unsigned cut = cutoff_key(row, V, true, (float)(tk - 1), 0.f, 1.f, red);
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (ordered_key(row[i]) < cut) row[i] = lowest;
+    __syncthreads();
+  }
+  if (tp > 0.f && tp < 1.f) {  // nucleus: keep a token iff the mass ranked before it is <= top_p (:100-108)
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = block_max(mx, red);
+    float s = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(row[i] - mx);
+    const float z = block_sum(s, red);
+    const unsigned cut = cutoff_key(row, V, false, tp, mx, z, red);
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (ordered_key(row[i]) < cut) row[i] = lowest;
+  }
+}
+
+Q3_EXPORT int q3_bias_penalty(float* row, int V, const int* bias_ids, const float* bias_vals, int n_bias,
+                              const int* seen_ids, int n_seen, int* counts, float repetition, float presence,
+                              float frequency, cudaStream_t stream) {
+  if (!row || V < 1 || (n_bias > 0 && (!bias_ids || !bias_vals)) || (n_seen > 0 && (!seen_ids || !counts)))
+    return Q3_ERR_ARGUMENT;
+  bias_penalty_kernel<<<1, SAMPLE_THREADS, 0, stream>>>(row, V, bias_ids, bias_vals, n_bias, seen_ids, n_seen, counts,
+                                                       repetition, presence, frequency);
+  return q3_launch_status();
+}
+
+Q3_EXPORT int q3_filter(float* logits, int num_rows, int V, const float* temperature, const float* min_p,
+                        const int* top_k, const float* top_p, cudaStream_t stream) {
+  if (!logits || !temperature || !min_p || !top_k || !top_p || V < 1) return Q3_ERR_ARGUMENT;
+  if (num_rows == 0) return Q3_OK;
+  filter_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, min_p, top_k, top_p);
+  return q3_launch_status();
+}

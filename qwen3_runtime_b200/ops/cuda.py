@@ -81,6 +81,9 @@ _SIGNATURES = {
     "sampling": {
         "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "q3_bias_penalty": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
+                            c_float, c_void_p],
+        "q3_filter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
 }
 
@@ -307,6 +310,36 @@ class CudaOps:
         self._call("sampling", "q3_sample", "sample",
                    _ptr(logits), R, V, _ptr(temperature), _ptr(uniform), _ptr(token), _ptr(logprob))
         return token, logprob
+
+
+    def bias_penalty_row(self, row, *, logit_bias, seen_ids, repetition_penalty, presence_penalty,
+                         frequency_penalty):
+        """Logit bias and repetition / presence / frequency penalties, in place on one fp32 row
+        (qwen3_runtime/sampling.py:36-72)."""
+        V = row.numel()
+        dev = row.device
+        bias_ids = bias_vals = seen = counts = None
+        n_bias = n_seen = 0
+        if logit_bias:
+            n_bias = len(logit_bias)
+            bias_ids = torch.tensor([int(k) for k in logit_bias], dtype=torch.int32, device=dev)
+            bias_vals = torch.tensor([float(v) for v in logit_bias.values()], dtype=torch.float32, device=dev)
+        if seen_ids and not (repetition_penalty == 1.0 and presence_penalty == 0.0 and frequency_penalty == 0.0):
+            n_seen = len(seen_ids)
+            seen = torch.tensor(seen_ids, dtype=torch.int32, device=dev)
+            counts = torch.empty(V, dtype=torch.int32, device=dev)
+        self._call("sampling", "q3_bias_penalty", "bias_penalty", _ptr(row), V, _ptr(bias_ids), _ptr(bias_vals),
+                   n_bias, _ptr(seen), n_seen, _ptr(counts), float(repetition_penalty), float(presence_penalty),
+                   float(frequency_penalty))
+        return row
+
+    def filter_rows(self, logits, temperature, min_p, top_k, top_p):
+        """Divide by the temperature, then min_p, top_k and top_p masks, in place on fp32 rows
+        (qwen3_runtime/sampling.py:75-109, 130-135).  The four arguments are per-row device tensors."""
+        R, V = logits.shape
+        self._call("sampling", "q3_filter", "filter", _ptr(logits), R, V, _ptr(temperature), _ptr(min_p),
+                   _ptr(top_k), _ptr(top_p))
+        return logits
 
 
 def default_scale(head_dim: int) -> float:

@@ -30,33 +30,58 @@ class Sampler:
         if logits.shape[0] != R:
             raise ValueError(f"logits rows {logits.shape[0]} must equal {R} sampling requests")
         params: list[SamplingParams] = [r.sampling for r in requests]
-        if any(p.logit_bias or p.has_penalties() or (not p.is_greedy() and p.needs_filter()) for p in params):
-            logits = self._process(logits, requests)
         want_lp = any(p.logprobs for p in params)
         greedy = [i for i, p in enumerate(params) if p.is_greedy()]
+        touched = [i for i, p in enumerate(params)
+                   if p.logit_bias or p.has_penalties() or (not p.is_greedy() and p.needs_filter())]
+        if touched:
+            logits = self._process(logits, requests, touched)
         if len(greedy) == R:
             tok, lp = self.ops.argmax(logits, want_lp)
             return tok.tolist(), (lp.tolist() if want_lp else [None] * R)
-        temps = torch.tensor([p.temperature if not p.is_greedy() else 1.0 for p in params], dtype=torch.float32)
-        unis = torch.tensor([0.0 if p.is_greedy() else draw_uniform(r.rng) for p, r in zip(params, requests)],
-                            dtype=torch.float32)
-        host = torch.stack([temps, unis]).pin_memory() if logits.is_cuda else torch.stack([temps, unis])
-        dev = host.to(self.device, non_blocking=True)
+        # rows that went through the filters are already divided by their temperature
+        filtered = {i for i in touched if not params[i].is_greedy() and params[i].needs_filter()}
+        temps = [1.0 if (p.is_greedy() or i in filtered) else p.temperature for i, p in enumerate(params)]
+        unis = [0.0 if p.is_greedy() else draw_uniform(r.rng) for p, r in zip(params, requests)]
+        dev = self._to_device(torch.tensor([temps, unis], dtype=torch.float32))
         tok_s, lp_s = self.ops.sample(logits, dev[0], dev[1], want_lp)
         if greedy:
             tok_g, lp_g = self.ops.argmax(logits, want_lp)
             mask = torch.zeros(R, dtype=torch.bool)
             mask[greedy] = True
-            mask = mask.to(self.device, non_blocking=True)
+            mask = self._to_device(mask)
             tok_s = torch.where(mask, tok_g, tok_s)
             if want_lp:
                 lp_s = torch.where(mask, lp_g, lp_s)
         return tok_s.tolist(), (lp_s.tolist() if want_lp else [None] * R)
 
-    def _process(self, logits: torch.Tensor, requests: list) -> torch.Tensor:
+    def _to_device(self, host: torch.Tensor) -> torch.Tensor:
+        if torch.device(self.device).type == "cuda":
+            host = host.pin_memory()
+        return host.to(self.device, non_blocking=True)
+
+    def _process(self, logits: torch.Tensor, requests: list, touched: list[int]) -> torch.Tensor:
+        """Processor chain on a copy of the rows that need it (qwen3_runtime/sampling.py:120-135):
+        bias and penalties per row, then one launch that divides by the temperature and applies
+        min_p, top_k and top_p to the non-greedy rows."""
         out = logits.clone()
-        for i, req in enumerate(requests):
-            p: SamplingParams = req.sampling
-            if p.logit_bias or p.has_penalties() or (not p.is_greedy() and p.needs_filter()):
-                self.ops.process_logits_row(out[i], p, req.token_ids)
+        for i in touched:
+            p: SamplingParams = requests[i].sampling
+            if p.logit_bias or p.has_penalties():
+                self.ops.bias_penalty_row(out[i], logit_bias=p.logit_bias, seen_ids=list(requests[i].token_ids),
+                                          repetition_penalty=p.repetition_penalty,
+                                          presence_penalty=p.presence_penalty, frequency_penalty=p.frequency_penalty)
+        rows = [i for i in touched if not requests[i].sampling.is_greedy() and requests[i].sampling.needs_filter()]
+        if rows:
+            ps = [requests[i].sampling for i in rows]
+            f = self._to_device(torch.tensor([[p.temperature for p in ps], [p.min_p for p in ps],
+                                              [p.top_p for p in ps]], dtype=torch.float32))
+            k = self._to_device(torch.tensor([p.top_k for p in ps], dtype=torch.int32))
+            if len(rows) == logits.shape[0]:
+                self.ops.filter_rows(out, f[0], f[1], k, f[2])
+            else:
+                idx = self._to_device(torch.tensor(rows, dtype=torch.long))
+                sub = out.index_select(0, idx).contiguous()
+                self.ops.filter_rows(sub, f[0], f[1], k, f[2])
+                out.index_copy_(0, idx, sub)
         return out

@@ -127,3 +127,40 @@ class TorchOps:
         if want_logprob:
             lp = torch.log(probs.gather(1, idx[:, None])[:, 0].clamp_min(1e-30))
         return idx.to(torch.int32), lp
+
+    def bias_penalty_row(self, row, *, logit_bias, seen_ids, repetition_penalty, presence_penalty,
+                         frequency_penalty):
+        for tok, val in (logit_bias or {}).items():
+            row[int(tok)] += float(val)
+        if seen_ids and not (repetition_penalty == 1.0 and presence_penalty == 0.0 and frequency_penalty == 0.0):
+            V = row.numel()
+            counts = torch.bincount(torch.tensor([t for t in seen_ids if 0 <= t < V], dtype=torch.long), minlength=V)
+            counts = counts.to(row.device)
+            seen = counts > 0
+            rep = torch.where(row > 0, row / repetition_penalty, row * repetition_penalty)
+            row.copy_(torch.where(seen, rep, row) - presence_penalty * seen.float() - frequency_penalty * counts.float())
+        return row
+
+    def filter_rows(self, logits, temperature, min_p, top_k, top_p):
+        lowest = torch.finfo(torch.float32).min
+        for r in range(logits.shape[0]):
+            x = logits[r] / temperature[r]
+            if float(min_p[r]) > 0:
+                p = torch.softmax(x, -1)
+                x = torch.where(p < float(min_p[r]) * p.max(), torch.full_like(x, float("-inf")), x)
+            k = int(top_k[r])
+            if 0 < k < x.numel():
+                kth = torch.topk(x, k).values[-1]
+                x = torch.where(x < kth, torch.full_like(x, lowest), x)
+            tp = float(top_p[r])
+            if 0 < tp < 1:
+                p = torch.softmax(x, -1)
+                order = torch.argsort(x, descending=True, stable=True)
+                before = p[order].cumsum(0) - p[order]  # mass ranked before each token
+                keep = torch.zeros_like(x, dtype=torch.bool)
+                keep[order] = before <= tp
+                # tokens tied with a kept one are kept as well (the kernel cuts by value)
+                keep |= x >= x[keep].min()
+                x = torch.where(keep, x, torch.full_like(x, lowest))
+            logits[r] = x
+        return logits
