@@ -1,0 +1,328 @@
+// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory (TMEM), operands staged in shared
+// memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), completion tracked by mbarriers.
+// This is the matrix product of prompt portions (more tokens than the weight-streaming
+// kernel of gemm_small_m.cu takes); the reference uses the library's product here
+// (qwen3_runtime/models/qwen3.py:76-77, 134-135).
+//
+// One block computes one 128 x 256 output tile (128 tokens x 256 features), K in slices of
+// 64, through a 4-stage ring of shared-memory tiles.  Six warps, three roles:
+//   warp 0, one lane : TMA producer   - waits for a free stage, arms its "full" barrier with
+//                                       the byte count, issues the loads of the A and B tiles;
+//   warp 1, one lane : MMA issuer     - waits for "full", issues 4 tcgen05.mma (K = 16 each)
+//                                       per stage, tcgen05.commit frees the stage; a final
+//                                       commit signals the epilogue;  warp 1 also owns TMEM;
+//   warps 2..5       : epilogue       - each reads its 32-lane quarter of TMEM with
+//                                       tcgen05.ld, converts and stores.
+// Epilogues: bf16 out; fp32 out; SwiGLU -- the block loads the gate rows and the up rows of
+// the same 128 features as two B tiles, accumulates them in two TMEM column ranges and writes
+// silu(gate) * up (models/qwen3.py:137-138), so the [M, 2I] intermediate never exists.
+//
+// Every wait on an mbarrier is bounded (about a second of SM clock): on expiry the waiter
+// raises the block's abort flag and a global error word, every role leaves its loop, TMEM is
+// freed and the block returns; the host reports the error.  No load uses cluster multicast.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_SWIGLU = 2 };
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  False: gave up (this or another role raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile [rows][64] bf16 written by TMA with the
+// 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t tile_addr) {
+  uint64_t d = (uint64_t)((tile_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                                // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: next group of 8 rows
+  d |= (uint64_t)1 << 46;                                // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+// BN: features per MMA (N of the instruction).  NB: B tiles per stage (2 for SwiGLU: gate, up).
+template <int BN, int NB, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int up_row_offset,
+                    int* __restrict__ error_word) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
+  constexpr int TMEM_COLS = BN * NB;  // 128 or 256: a power of two >= 32
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[STAGES]), done_bar = smem_addr(&bars[2 * STAGES]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(done_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM allocation is a warp-wide instruction; the same warp frees it at the end
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer -------------------------------------------------------
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t phase = (kb / STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1, &abort_flag)) break;
+        const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(a_dst, &tmap_a, full0 + 8 * s, kb * BK, m0);
+        tma_load_2d(a_dst + A_BYTES, &tmap_w, full0 + 8 * s, kb * BK, n0);
+        if (NB == 2) tma_load_2d(a_dst + A_BYTES + B_BYTES, &tmap_w, full0 + 8 * s, kb * BK, up_row_offset + n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer ---------------------------------------------------------
+      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t phase = (kb / STAGES) & 1;
+        ok = mbar_wait(full0 + 8 * s, phase, &abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+        const uint64_t a_desc = umma_desc(a_addr);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const uint64_t b_desc = umma_desc(a_addr + A_BYTES + j * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes = 2 descriptor units along K
+            umma_bf16(tmem_base + j * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
+      }
+      if (ok) umma_commit(done_bar);  // arrives when every MMA has written TMEM
+    }
+  } else {  // ---- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 ---------------------------
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(done_bar, 0, &abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;  // (uniform)
+        uint32_t acc[32];
+        tmem_load32(lane_addr + c0, acc);
+        float v[32];
+        if (MODE == OUT_SWIGLU) {
+          uint32_t up[32];
+          tmem_load32(lane_addr + BN + c0, up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = __uint_as_float(acc[i]);
+            v[i] = (g / (1.f + expf(-g))) * __uint_as_float(up[i]);
+          }
+        } else {
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+        }
+        if (row < M) {
+          const int col = n0 + c0;
+          if (MODE == OUT_F32) {
+            float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
+            if (col + 32 <= N && (ldo & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+              for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = v[i];
+            }
+          } else {
+            bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
+            if (col + 32 <= N && (ldo & 7) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                float chunk[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) chunk[e] = v[i + e];
+                store8(dst + i, chunk);
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_word) atomicExch(error_word, 1);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// A row-major [rows, cols] bf16 matrix with row stride `ld` elements, read in boxes of
+// [box_rows, 64] with the 128-byte swizzle; out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int NB, int MODE>
+int launch(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K, int up_offset,
+           int* error_word, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, NB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_tcgen05_kernel<BN, NB, MODE><<<grid, THREADS, smem, stream>>>(ta, tw, out, ldo, M, N, K, up_offset, error_word);
+  return q3_launch_status();
+}
+
+}  // namespace
+
+// mode 0: out bf16 [M, N]; 1: out fp32 [M, N]; 2: W is [2 * N, K] (gate rows, then up rows from
+// row N), out bf16 [M, N] = silu(x W_gate^T) * (x W_up^T).  x, W bf16 with 16-byte aligned bases
+// and row strides (elements) that are multiples of 8.  error_word: device int, set to 1 if a
+// wait inside the kernel expired (may be null).
+Q3_EXPORT int q3_gemm_tcgen05(int mode, const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M,
+                              int N, int K, int* error_word, cudaStream_t stream) {
+  if (!x || !W || !out || N < 1 || K < 1 || M < 0) return Q3_ERR_ARGUMENT;
+  if (ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return Q3_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return Q3_ERR_UNSUPPORTED;
+  if (M == 0) return Q3_OK;
+  if ((M + BM - 1) / BM > 65535) return Q3_ERR_UNSUPPORTED;
+  CUtensorMap ta, tw;
+  const int bn = mode == OUT_SWIGLU ? 128 : 256;
+  const long w_rows = mode == OUT_SWIGLU ? 2L * N : N;
+  if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, bn)) return Q3_ERR_LAUNCH;
+  if (mode == OUT_BF16) return launch<256, 1, OUT_BF16>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
+  if (mode == OUT_F32) return launch<256, 1, OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
+  if (mode == OUT_SWIGLU) return launch<128, 2, OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
+  return Q3_ERR_ARGUMENT;
+}

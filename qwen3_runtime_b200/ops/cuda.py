@@ -78,6 +78,10 @@ _SIGNATURES = {
     "gemm_small_m": {
         "q3_gemm_small_m": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
+    "gemm_tcgen05": {
+        "q3_gemm_tcgen05": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                            c_void_p],
+    },
     "sampling": {
         "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -275,6 +279,43 @@ class CudaOps:
         if out is None:
             return torch.mm(x, weight.t())
         return torch.mm(x, weight.t(), out=out)
+
+    def _tcgen05_ok(self, x, weight) -> bool:
+        return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def _error_word(self, device) -> torch.Tensor:
+        if getattr(self, "_err", None) is None:
+            self._err = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._err
+
+    def raise_if_kernel_error(self) -> None:
+        """A bounded wait inside a kernel expired (it gave up and returned).  Reads one int from
+        the device, so call it where the host waits for the device anyway."""
+        err = getattr(self, "_err", None)
+        if err is not None and int(err.item()) != 0:
+            err.zero_()
+            raise KernelError("a wait inside gemm_tcgen05 expired: the kernel gave up and its output is invalid")
+
+    def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None):
+        """``x @ weight^T`` on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).  ``mode=2``: SwiGLU with
+        ``weight = [W_gate; W_up]``, ``out`` is ``[M, I]``."""
+        M, K = x.shape
+        if not self._tcgen05_ok(x, weight):
+            raise KernelError("gemm_tcgen05: bfloat16 operands with 16-byte aligned rows (K multiple of 8) only")
+        if mode == 2:
+            N = weight.shape[0] // 2
+            odt = x.dtype
+        else:
+            N = weight.shape[0]
+            odt = out_dtype or x.dtype
+            mode = 1 if odt == torch.float32 else 0
+        if out is None:
+            out = torch.empty((M, N), dtype=odt, device=x.device)
+        self._call("gemm_tcgen05", "q3_gemm_tcgen05", "gemm_tcgen05", mode, _ptr(x), x.stride(0), _ptr(weight),
+                   weight.stride(0), _ptr(out), out.stride(0), M, N, K, _ptr(self._error_word(x.device)))
+        return out
 
     SMALL_M = 16
 

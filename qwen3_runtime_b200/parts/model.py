@@ -57,7 +57,7 @@ class DecoderModel:
         self.loaded = True
 
     def kernel_groups(self) -> list[str]:
-        groups = {"norm", "sampling"}
+        groups = {"norm"}
         for part in [*self.blocks, self.final_norm]:
             groups.update(part.kernel_groups())
         return sorted(groups)
