@@ -5,8 +5,10 @@
 // kernel of gemm_small_m.cu takes); the reference uses the library's product here
 // (qwen3_runtime/models/qwen3.py:76-77, 134-135).
 //
-// One block computes one 128 x 256 output tile (128 tokens x 256 features), K in slices of
-// 64, through a 4-stage ring of shared-memory tiles.  Six warps, three roles:
+// A block computes 128 x 256 output tiles (128 tokens x 256 features), K in slices of 64,
+// through a 4-stage ring of shared-memory tiles; it is persistent (one block per SM walks the
+// tiles) and keeps two accumulators in TMEM so that the epilogue of a tile overlaps the MMAs
+// of the next.  Six warps, three roles:
 //   warp 0, one lane : TMA producer   - waits for a free stage, arms its "full" barrier with
 //                                       the byte count, issues the loads of the A and B tiles;
 //   warp 1, one lane : MMA issuer     - waits for "full", issues 4 tcgen05.mma (K = 16 each)
@@ -113,6 +115,8 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // BN: features per MMA (N of the instruction).  NB: B tiles per stage (2 for SwiGLU: gate, up).
+// Persistent: block b computes tiles b, b + gridDim.x, ...; the accumulator is double-buffered
+// in TMEM (2 x 256 columns) so that the epilogue of one tile overlaps the MMAs of the next.
 template <int BN, int NB, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -121,17 +125,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
-  constexpr int TMEM_COLS = BN * NB;  // 128 or 256: a power of two >= 32
+  constexpr int ACC_COLS = 256;          // columns per accumulator buffer (BN * NB of them are used)
+  constexpr int TMEM_COLS = 2 * ACC_COLS;  // 512: the whole tensor memory of the SM
+  static_assert(BN * NB <= ACC_COLS && BN % 32 == 0, "tile width");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
-  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[STAGES]), done_bar = smem_addr(&bars[2 * STAGES]);
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[STAGES]);
+  const uint32_t acc_full0 = smem_addr(&bars[2 * STAGES]), acc_empty0 = smem_addr(&bars[2 * STAGES + 2]);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -139,7 +147,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(done_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // TMEM allocation is a warp-wide instruction; the same warp frees it at the end
@@ -155,93 +166,119 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer -------------------------------------------------------
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t phase = (kb / STAGES) & 1;
-        if (!mbar_wait(empty0 + 8 * s, phase ^ 1, &abort_flag)) break;
-        const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        tma_load_2d(a_dst, &tmap_a, full0 + 8 * s, kb * BK, m0);
-        tma_load_2d(a_dst + A_BYTES, &tmap_w, full0 + 8 * s, kb * BK, n0);
-        if (NB == 2) tma_load_2d(a_dst + A_BYTES + B_BYTES, &tmap_w, full0 + 8 * s, kb * BK, up_row_offset + n0);
+      int g = 0;  // k-slices issued so far, over all tiles of this block
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;  // token tiles fastest: a weight tile stays in L2
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % STAGES;
+          const uint32_t phase = (g / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, phase ^ 1, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, full0 + 8 * s, kb * BK, m0);
+          tma_load_2d(a_dst + A_BYTES, &tmap_w, full0 + 8 * s, kb * BK, n0);
+          if (NB == 2) tma_load_2d(a_dst + A_BYTES + B_BYTES, &tmap_w, full0 + 8 * s, kb * BK, up_row_offset + n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ---------------------------------------------------------
       constexpr uint32_t idesc = umma_idesc(BM, BN);
+      int g = 0, i = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t phase = (kb / STAGES) & 1;
-        ok = mbar_wait(full0 + 8 * s, phase, &abort_flag);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+        const int buf = i & 1;
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_flag);  // epilogue has drained it
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-        const uint64_t a_desc = umma_desc(a_addr);
+        const uint32_t acc = tmem_base + buf * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % STAGES;
+          const uint32_t phase = (g / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, phase, &abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr);
 #pragma unroll
-        for (int j = 0; j < NB; ++j) {
-          const uint64_t b_desc = umma_desc(a_addr + A_BYTES + j * B_BYTES);
+          for (int j = 0; j < NB; ++j) {
+            const uint64_t b_desc = umma_desc(a_addr + A_BYTES + j * B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes = 2 descriptor units along K
-            umma_bf16(tmem_base + j * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes = 2 descriptor units along K
+              umma_bf16(acc + j * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
         }
-        umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
+        if (ok) umma_commit(acc_full0 + 8 * buf);  // arrives when the tile's MMAs have written TMEM
       }
-      if (ok) umma_commit(done_bar);  // arrives when every MMA has written TMEM
     }
   } else {  // ---- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 ---------------------------
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    const bool ok = mbar_wait(done_bar, 0, &abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int i = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;  // token tiles fastest: a weight tile stays in L2
+      const int buf = i & 1;
+      const int row = m0 + quarter * 32 + lane;
+      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, &abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= N) break;  // (uniform)
-        uint32_t acc[32];
-        tmem_load32(lane_addr + c0, acc);
-        float v[32];
-        if (MODE == OUT_SWIGLU) {
-          uint32_t up[32];
-          tmem_load32(lane_addr + BN + c0, up);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const bool last = c0 + 32 >= BN || n0 + c0 + 32 >= N;
+        if (n0 + c0 < N) {  // (uniform)
+          uint32_t acc[32];
+          tmem_load32(lane_addr + c0, acc);
+          float v[32];
+          if (MODE == OUT_SWIGLU) {
+            uint32_t up[32];
+            tmem_load32(lane_addr + BN + c0, up);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float g = __uint_as_float(acc[i]);
-            v[i] = (g / (1.f + expf(-g))) * __uint_as_float(up[i]);
-          }
-        } else {
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
-        }
-        if (row < M) {
-          const int col = n0 + c0;
-          if (MODE == OUT_F32) {
-            float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
-            if (col + 32 <= N && (ldo & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-              for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = v[i];
+            for (int e = 0; e < 32; ++e) {
+              const float gate = __uint_as_float(acc[e]);
+              v[e] = (gate / (1.f + expf(-gate))) * __uint_as_float(up[e]);
             }
           } else {
-            bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
-            if (col + 32 <= N && (ldo & 7) == 0) {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                float chunk[8];
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(acc[e]);
+          }
+          if (last) {  // everything of this buffer is in registers: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+          }
+          if (row < M) {
+            const int col = n0 + c0;
+            if (MODE == OUT_F32) {
+              float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
+              if (col + 32 <= N && (ldo & 3) == 0) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) chunk[e] = v[i + e];
-                store8(dst + i, chunk);
+                for (int e = 0; e < 32; e += 4)
+                  *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+              } else {
+                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = v[e];
               }
             } else {
-              for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+              bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
+              if (col + 32 <= N && (ldo & 7) == 0) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                  float chunk[8];
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) chunk[x] = v[e + x];
+                  store8(dst + e, chunk);
+                }
+              } else {
+                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+              }
             }
           }
         }
+        if (last) break;
       }
     }
   }
@@ -299,7 +336,15 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int
       return Q3_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms < 1)
+      num_sms = 148;
+  }
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int grid = tiles < num_sms ? tiles : num_sms;  // one persistent block per SM
   gemm_tcgen05_kernel<BN, NB, MODE><<<grid, THREADS, smem, stream>>>(ta, tw, out, ldo, M, N, K, up_offset, error_word);
   return q3_launch_status();
 }
@@ -316,13 +361,35 @@ Q3_EXPORT int q3_gemm_tcgen05(int mode, const void* x, int ldx, const void* W, i
   if (ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return Q3_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)W) & 15) return Q3_ERR_UNSUPPORTED;
   if (M == 0) return Q3_OK;
-  if ((M + BM - 1) / BM > 65535) return Q3_ERR_UNSUPPORTED;
   CUtensorMap ta, tw;
-  const int bn = mode == OUT_SWIGLU ? 128 : 256;
+  int bn = 128;
+  if (mode != OUT_SWIGLU) {
+    // tile width: the one that needs the fewest rounds of one-tile-per-SM, counted in columns
+    // (+24 for what a tile costs beyond its MMAs); narrow outputs get narrower tiles
+    const int tiles_m = (M + BM - 1) / BM;
+    long best = -1;
+    for (int cand : {256, 192, 160, 128}) {
+      const long tiles = (long)tiles_m * ((N + cand - 1) / cand);
+      const long cost = ((tiles + 147) / 148) * (cand + 24);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
   const long w_rows = mode == OUT_SWIGLU ? 2L * N : N;
   if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, bn)) return Q3_ERR_LAUNCH;
-  if (mode == OUT_BF16) return launch<256, 1, OUT_BF16>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
-  if (mode == OUT_F32) return launch<256, 1, OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
   if (mode == OUT_SWIGLU) return launch<128, 2, OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
+#define Q3_TC_CASE(BN_)                                                                                   \
+  if (bn == BN_)                                                                                          \
+    return mode == OUT_F32 ? launch<BN_, 1, OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream)    \
+                           : launch<BN_, 1, OUT_BF16>(ta, tw, out, ldo, M, N, K, 0, error_word, stream)
+  if (mode == OUT_BF16 || mode == OUT_F32) {
+    Q3_TC_CASE(256);
+    Q3_TC_CASE(192);
+    Q3_TC_CASE(160);
+    Q3_TC_CASE(128);
+  }
+#undef Q3_TC_CASE
   return Q3_ERR_ARGUMENT;
 }

@@ -98,7 +98,14 @@ class CudaOps:
 
     name = "cuda-sm100a"
 
-    def __init__(self, groups: list[str] | None = None):
+    def __init__(self, groups: list[str] | None = None, large_gemm: str = "auto"):
+        """``large_gemm`` picks the bfloat16 product for more than 16 tokens: ``"tcgen05"`` -- this
+        engine's tcgen05/TMEM kernel for every such product; ``"library"`` -- the library's;
+        ``"auto"`` (default) -- the tcgen05 kernel where it is at least as fast as the library
+        on a B200 (the fused SwiGLU product of prompt-sized batches), the library elsewhere."""
+        if large_gemm not in ("auto", "tcgen05", "library"):
+            raise ValueError("large_gemm must be auto, tcgen05 or library")
+        self.large_gemm = large_gemm
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -274,6 +281,8 @@ class CudaOps:
             self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m", 1 if odt == torch.float32 else 0,
                        _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K)
             return out
+        if self.large_gemm == "tcgen05" and self._tcgen05_ok(x, weight):
+            return self.linear_tcgen05(x, weight, out=out, out_dtype=out_dtype)
         if out_dtype is not None and out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         if out is None:
@@ -333,6 +342,10 @@ class CudaOps:
             self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m(swiglu)", 2, _ptr(x), x.stride(0),
                        _ptr(gate_up_weight), gate_up_weight.stride(0), _ptr(out), out.stride(0), M, I, K)
             return out
+        if self.large_gemm != "library" and self._tcgen05_ok(x, gate_up_weight):
+            tiles = -(-M // 128) * -(-I // 128)
+            if self.large_gemm == "tcgen05" or tiles >= 2 * self.SM_COUNT:
+                return self.linear_tcgen05(x, gate_up_weight, out=out, mode=2)
         return self.silu_mul(self.linear(x, gate_up_weight), out)
 
     # ---- sampling ---------------------------------------------------------------------

@@ -76,6 +76,8 @@ def main(argv: list[str] | None = None) -> int:
             logits = rt.runner.run(entries)
             if logits is not None:
                 arr = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+                if hasattr(model.ops, "raise_if_kernel_error"):
+                    model.ops.raise_if_kernel_error()
                 np.ascontiguousarray(arr).tofile(out_dir / f"{step}.f32")
         for rid in record.get("end", []):
             rc = live.pop(rid, None)

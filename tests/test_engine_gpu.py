@@ -47,3 +47,13 @@ def test_greedy_generation(tmp_path, ops, name, dtype, cuda_graph):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_temperature_sampling(tmp_path, ops, dtype):
     ec.case_temperature_sampling(tmp_path, "B", dtype, ops, "cuda")
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_four_schedules_with_every_large_product_on_tcgen05(tmp_path, name):
+    """The whole model with this engine's tcgen05/TMEM kernel for every product of more than 16 tokens."""
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    forced = CudaOps(large_gemm="tcgen05")
+    ec.case_four_schedules(tmp_path, name, "bfloat16", forced, "cuda", lengths=(400, 37, 257, 150))
+    forced.raise_if_kernel_error()
