@@ -39,12 +39,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // NT: token tiles of 8 (1 or 2).  MODE: epilogue.  SETS: 2 for SwiGLU (gate and up), else 1.
-template <int NT, int MODE>
-__global__ void __launch_bounds__(MAX_WARPS * 32)
+// WARPS_ x MINB_ is chosen so that the register cap is 64: two 16-warp blocks or four 8-warp
+// blocks per SM, which lets every shape of the model run as a single wave of blocks.
+template <int NT, int MODE, int WARPS_, int MINB_>
+__global__ void __launch_bounds__(WARPS_ * 32, MINB_)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw,
                     void* __restrict__ out, int ldo, int M, int N, int K, int KS, int kper, int up_offset) {
   constexpr int SETS = MODE == OUT_SWIGLU ? 2 : 1;
-  constexpr int U = 4;  // k-blocks of 32 in flight per thread
+  constexpr int U = 2;  // k-blocks of 32 in flight per thread (64 registers: many warps instead)
   __shared__ float red[MAX_WARPS][SETS * NT * 4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -151,7 +153,11 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
   const int warps = KS > 8 ? 16 : 8;  // blocks of 8 warps balance better; 16 only to split K further
   const int MT = warps / KS;
   const int blocks = (tiles + MT - 1) / MT;
-  gemm_small_m_kernel<NT, MODE><<<blocks, warps * 32, 0, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, KS, kper,
+  if (warps == 16)
+    gemm_small_m_kernel<NT, MODE, 16, 2><<<blocks, 512, 0, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, KS, kper,
+                                                                     up_offset);
+  else
+    gemm_small_m_kernel<NT, MODE, 8, 4><<<blocks, 256, 0, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, KS, kper,
                                                                     up_offset);
   return q3_launch_status();
 }

@@ -230,14 +230,25 @@ class CudaOps:
     SM_COUNT = 148
     DECODE_MIN_KEYS_PER_SPLIT = 256
 
+    DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
+
     def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int) -> int:
-        """How many slices each sequence's keys are cut into: enough blocks to fill the GPU
-        about six times over (three blocks are resident per SM), but no slice shorter than 256 keys.  Depends only on sizes that
-        are fixed for a captured step (qwen3_runtime/kernels/triton_decode.py:122-133 has the
-        same shape of rule for an RTX 4090)."""
-        by_length = max(1, -(-max_kv_len // self.DECODE_MIN_KEYS_PER_SPLIT))
-        by_blocks = max(1, -(-6 * self.SM_COUNT // (num_seqs * num_kv_heads)))
-        return int(min(by_length, by_blocks, 64))
+        """How many slices each sequence's keys are cut into.  Blocks run in waves of
+        3 x 148; the cost of a choice is waves x (keys per slice + a fixed part worth about
+        128 keys), and the cheapest choice with slices of at least 256 keys wins (fewer slices
+        on ties).  Depends only on sizes that are fixed for a captured step.  The reference's
+        rule for an RTX 4090 has the same inputs (qwen3_runtime/kernels/triton_decode.py:122-133)."""
+        pairs = max(1, num_seqs * num_kv_heads)
+        slots = self.DECODE_BLOCKS_PER_SM * self.SM_COUNT
+        most = max(1, min(64, max_kv_len // self.DECODE_MIN_KEYS_PER_SPLIT))
+        best, best_cost = 1, None
+        for splits in range(1, most + 1):
+            per = -(-(-(-max_kv_len // splits)) // 64) * 64
+            waves = -(-pairs * splits // slots)
+            cost = waves * (per + 128)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = splits, cost
+        return best
 
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
