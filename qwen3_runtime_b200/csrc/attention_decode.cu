@@ -39,6 +39,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
   unsigned char* q_s = smem;                  // [16][D] bf16
   unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile)
 
+  pdl_wait();  // keys and values of the newest token come from the kernel before this one
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int slot = blockIdx.z;                // index into the partial buffers
   const int seq = seq_list ? seq_list[slot] : slot;
@@ -208,6 +209,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
   }
 
   // ---- merge the 4 warps ------------------------------------------------------------------
+  pdl_launch_dependents();
   cp_async_wait<0>();
   __syncthreads();
 #pragma unroll
@@ -263,6 +265,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
 __global__ void decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
                                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_list,
                                       bf16* __restrict__ out, int nq, int D, int num_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int slot = blockIdx.y, head = blockIdx.x;
   const int seq = seq_list ? seq_list[slot] : slot;
   const int tok = cu_seqlens[seq];
@@ -299,16 +303,17 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     configured = true;
   }
   dim3 grid(num_splits, nkv, num_seqs);
-  decode_attention_kernel<D><<<grid, THREADS, smem, stream>>>(
-      q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq,
-      nkv, ps, scale * 1.4426950408889634f, window, num_splits, stages);
-  if (q3_launch_status() != Q3_OK) return Q3_ERR_LAUNCH;
+  if (launch_pdl(decode_attention_kernel<D>, grid, dim3(THREADS), smem, stream, q, q_stride, kpages, vpages,
+                 block_table, max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps,
+                 scale * 1.4426950408889634f, window, num_splits, stages) != cudaSuccess)
+    return Q3_ERR_LAUNCH;
   if (num_splits > 1) {
     dim3 cgrid(nq, num_seqs);
-    decode_combine_kernel<<<cgrid, D < 128 ? D : 128, 0, stream>>>(mid_o, mid_lse, cu_seqlens, seq_list, out, nq, D,
-                                                                   num_splits);
+    if (launch_pdl(decode_combine_kernel, cgrid, dim3(D < 128 ? D : 128), 0, stream, (const float*)mid_o,
+                   (const float*)mid_lse, cu_seqlens, seq_list, out, nq, D, num_splits) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
   }
-  return q3_launch_status();
+  return Q3_OK;
 }
 
 }  // namespace

@@ -100,3 +100,38 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
   *reinterpret_cast<uint4*>(p) = raw;
 }
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A kernel launched with launch_pdl may start while the kernel before it in the stream is still
+// running.  It must call pdl_wait() before it touches anything that kernel writes (or writes
+// anything that kernel reads); what it does before that -- fetching weights -- overlaps the tail
+// of its predecessor.  pdl_launch_dependents() lets the *next* kernel start early in the same
+// way.  Both are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool q3_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("QWEN3_RUNTIME_B200_PDL");
+    enabled = (v && v[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = q3_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -80,8 +80,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       x_row[n] = x + (long)(x_ok[n] ? n * 8 + g : 0) * ldx;
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int k0 = k_lo; k0 < k_hi; k0 += 32 * U) {
-      uint4 wl[SETS][U], wh[SETS][U], xv[NT][U];
+    // The first weights are fetched before waiting for the kernel that produces x: weights do
+    // not depend on it, so this overlaps the predecessor's tail (programmatic dependent launch).
+    uint4 wl[SETS][U], wh[SETS][U], xv[NT][U];
+    auto load_w = [&](int k0) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int k = k0 + 32 * u + 8 * t;
@@ -91,6 +93,16 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
           wl[s][u] = ok ? ldg16(w_lo[s] + k) : zero;
           wh[s][u] = ok ? ldg16(w_hi[s] + k) : zero;
         }
+      }
+    };
+    load_w(k_lo);
+    pdl_wait();
+    for (int k0 = k_lo; k0 < k_hi; k0 += 32 * U) {
+      if (k0 != k_lo) load_w(k0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + 32 * u + 8 * t;
+        const bool ok = k < k_hi;
 #pragma unroll
         for (int n = 0; n < NT; ++n) xv[n][u] = (ok && x_ok[n]) ? ldg16_cached(x_row[n] + k) : zero;
       }
@@ -104,7 +116,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
             mma_bf16(acc[s][n], wl[s][u].z, wh[s][u].z, wl[s][u].w, wh[s][u].w, xv[n][u].z, xv[n][u].w);
           }
     }
+  } else {
+    pdl_wait();
   }
+  pdl_launch_dependents();
 
   // ---- sum the K slices of each tile, then the epilogue ---------------------------------------
   if (KS > 1) {
@@ -153,13 +168,14 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
   const int warps = KS > 8 ? 16 : 8;  // blocks of 8 warps balance better; 16 only to split K further
   const int MT = warps / KS;
   const int blocks = (tiles + MT - 1) / MT;
+  cudaError_t err;
   if (warps == 16)
-    gemm_small_m_kernel<NT, MODE, 16, 2><<<blocks, 512, 0, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, KS, kper,
-                                                                     up_offset);
+    err = launch_pdl(gemm_small_m_kernel<NT, MODE, 16, 2>, dim3(blocks), dim3(512), 0, stream, x, ldx, W, ldw, out,
+                     ldo, M, N, K, KS, kper, up_offset);
   else
-    gemm_small_m_kernel<NT, MODE, 8, 4><<<blocks, 256, 0, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, KS, kper,
-                                                                    up_offset);
-  return q3_launch_status();
+    err = launch_pdl(gemm_small_m_kernel<NT, MODE, 8, 4>, dim3(blocks), dim3(256), 0, stream, x, ldx, W, ldw, out,
+                     ldo, M, N, K, KS, kper, up_offset);
+  return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
 }  // namespace

@@ -17,6 +17,8 @@ __global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restri
                                   T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
   extern __shared__ float vals[];  // H floats, then 33 for the reduction
   float* red = vals + H;
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const long src = rows ? rows[r] : r;
   const T* trow = nullptr;
@@ -49,6 +51,8 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
                                       T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
   extern __shared__ float vals[];
   float* red = vals + H;
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const long src = rows ? rows[r] : r;
   const T* trow = nullptr;
@@ -105,9 +109,10 @@ static int launch_fused_norm(const void* pending, float* resid, const int* ids, 
       cudaFuncSetAttribute(fused_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int threads = ((H / 8 + 31) / 32) * 32;
     threads = threads > 1024 ? 1024 : threads;
-    fused_norm_vec_kernel<T><<<num_rows, threads, smem, stream>>>(
-        (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
-    return q3_launch_status();
+    return launch_pdl(fused_norm_vec_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending, resid,
+                      ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+               ? Q3_OK
+               : Q3_ERR_LAUNCH;
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   fused_norm_kernel<T><<<num_rows, threads, smem, stream>>>(

@@ -82,6 +82,8 @@ __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_strid
                                               int num_tokens, int write_kv) {
   const int tph = D / 16;  // threads per head: a power of two, at most 16
   const int heads = write_kv ? nq + 2 * nkv : nq;
+  pdl_wait();
+  pdl_launch_dependents();
   const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long item = gid / tph;
   const int c = (int)(gid - item * tph);
@@ -170,17 +172,18 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
   if (vec) {
     const long threads_total = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq) * tph;
     const unsigned vblocks = (unsigned)((threads_total + 255) / 256);
+    cudaError_t err;
     if (dtype == Q3_DTYPE_F32)
-      qk_norm_rope_store_vec_kernel<float><<<vblocks, 256, 0, stream>>>(
-          (float*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-          block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+      err = launch_pdl(qk_norm_rope_store_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (float*)qkv,
+                       row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
+                       block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
     else if (dtype == Q3_DTYPE_BF16)
-      qk_norm_rope_store_vec_kernel<bf16><<<vblocks, 256, 0, stream>>>(
-          (bf16*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-          block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+      err = launch_pdl(qk_norm_rope_store_vec_kernel<bf16>, dim3(vblocks), dim3(256), 0, stream, (bf16*)qkv,
+                       row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
+                       block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
     else
       return Q3_ERR_ARGUMENT;
-    return q3_launch_status();
+    return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
   }
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * D * sizeof(float);
