@@ -96,6 +96,13 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       }
     };
     load_w(k_lo);
+    // ... and the rest of this warp's weight slice is requested into L2, one 128-byte line per
+    // request, so that HBM keeps streaming while the predecessor finishes
+    for (int s = 0; s < SETS; ++s) {
+      const bf16* row = W + (long)min(row0 + s * up_offset + (lane & 15), N + s * up_offset - 1) * ldw;
+      for (int k = k_lo + 32 * U + 64 * (lane >> 4); k < k_hi; k += 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(row + k));
+    }
     pdl_wait();
     for (int k0 = k_lo; k0 < k_hi; k0 += 32 * U) {
       if (k0 != k_lo) load_w(k0);
