@@ -24,6 +24,8 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 FREED = -1  # block-table entry of a page that a window has passed
 
 
@@ -121,6 +123,23 @@ class RequestCache:
     num_reserved: int = 0  # tokens for which pages are reserved (>= num_computed)
     needs_state_reset: bool = True  # its slot must be zeroed before its next step
     closed: bool = field(default=False, repr=False)
+    # int32 copies of ``tables`` kept in step with them, so that a step's block tables are
+    # filled with array copies instead of per-element conversions
+    table_arrays: list = field(default_factory=list, repr=False)
+
+    def table_array(self, paged_index: int) -> np.ndarray:
+        """The block table of one paged group as an int32 array (a view; do not keep it)."""
+        return self.table_arrays[paged_index][: len(self.tables[paged_index])]
+
+    def _append_page(self, paged_index: int, page: int) -> None:
+        table = self.tables[paged_index]
+        arr = self.table_arrays[paged_index]
+        if len(table) >= arr.size:
+            grown = np.empty(max(16, 2 * arr.size), dtype=np.int32)
+            grown[: arr.size] = arr
+            self.table_arrays[paged_index] = arr = grown
+        arr[len(table)] = page
+        table.append(page)
 
 
 class CacheManager:
@@ -174,6 +193,7 @@ class CacheManager:
         if request_id in self.live:
             raise CacheError(f"request {request_id!r} is already open")
         rc = RequestCache(request_id, self.slots.allocate(), [[] for _ in self.paged_groups])
+        rc.table_arrays = [np.empty(16, dtype=np.int32) for _ in self.paged_groups]
         self.live[request_id] = rc
         return rc
 
@@ -186,9 +206,9 @@ class CacheManager:
             raise CacheError("page pool exhausted")
         end = rc.num_computed + num_tokens
         need = self.pages_for(end)
-        for table, alloc in zip(rc.tables, self.allocators):
+        for pi, (table, alloc) in enumerate(zip(rc.tables, self.allocators)):
             while len(table) < need:
-                table.append(alloc.allocate())
+                rc._append_page(pi, alloc.allocate())
         rc.num_reserved = max(rc.num_reserved, end)
 
     def commit(self, rc: RequestCache, num_tokens: int) -> None:
@@ -208,6 +228,7 @@ class CacheManager:
                 if table[idx] != FREED:
                     alloc.release(table[idx])
                     table[idx] = FREED
+                    rc.table_arrays[self.paged_groups.index(gi)][idx] = FREED
 
     def reset(self, rc: RequestCache) -> None:
         """Give back every page and forget what was computed (preemption by recompute)."""

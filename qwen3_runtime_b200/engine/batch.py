@@ -129,22 +129,28 @@ class BatchBuilder:
         sec("ids")[:T_real] = ids_np
         sec("ids")[T_real:] = 0
         pos, seq, cu, kv, slot = sec("pos"), sec("seq"), sec("cu"), sec("kv"), sec("slot")
+        starts = np.fromiter((e.cache.num_computed for e in entries), dtype=np.int32, count=B_real)
+        lens_np = np.asarray(lens, dtype=np.int32)
         cu[0] = 0
-        t = 0
-        for b, (e, n) in enumerate(zip(entries, lens)):
-            start = e.cache.num_computed
-            pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
-            seq[t:t + n] = b
-            rows.extend(t + w for w in e.want)
-            t += n
-            cu[b + 1] = t
-            kv[b] = start + n
-            slot[b] = e.cache.slot
-            for g in range(n_paged):
-                bt = sec(f"bt{g}")[b * width:(b + 1) * width]
-                table = e.cache.tables[g]
-                bt[:len(table)] = table
-                bt[len(table):] = scratch_page
+        np.cumsum(lens_np, out=cu[1:B_real + 1])
+        kv[:B_real] = starts + lens_np
+        slot[:B_real] = np.fromiter((e.cache.slot for e in entries), dtype=np.int32, count=B_real)
+        if T_real == B_real:  # every entry brings one token
+            pos[:T_real] = starts
+            seq[:T_real] = np.arange(B_real, dtype=np.int32)
+        else:
+            seq[:T_real] = np.repeat(np.arange(B_real, dtype=np.int32), lens_np)
+            pos[:T_real] = np.arange(T_real, dtype=np.int32) - np.repeat(cu[:B_real] - starts, lens_np)
+        for e, first in zip(entries, cu[:B_real].tolist()):
+            if e.want:
+                rows.extend(first + w for w in e.want)
+        for g in range(n_paged):
+            bt = sec(f"bt{g}").reshape(B, width)
+            bt[:] = scratch_page
+            for b, e in enumerate(entries):
+                arr = e.cache.table_array(g)
+                bt[b, : arr.size] = arr
+        t = T_real
         for b in range(B_real, B):  # padding rows: one token at position 0 of the scratch page
             pos[t] = 0
             seq[t] = b
@@ -152,8 +158,6 @@ class BatchBuilder:
             cu[b + 1] = t
             kv[b] = 1
             slot[b] = scratch_slot
-            for g in range(n_paged):
-                sec(f"bt{g}")[b * width:(b + 1) * width] = scratch_page
         singles = [b for b, n in enumerate(lens) if n == 1] + list(range(B_real, B))
         sec("single")[:len(singles)] = singles
         if all_rows:
