@@ -44,7 +44,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 template <int NT, int MODE, int WARPS_, int MINB_>
 __global__ void __launch_bounds__(WARPS_ * 32, MINB_)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int KS, int kper, int up_offset) {
+                    void* __restrict__ out, int ldo, int M, int N, int K, int KS, int kper, int up_offset,
+                    int prefetch_l2) {
   constexpr int SETS = MODE == OUT_SWIGLU ? 2 : 1;
   constexpr int U = 2;  // k-blocks of 32 in flight per thread (64 registers: many warps instead)
   __shared__ float red[MAX_WARPS][SETS * NT * 4][32];
@@ -97,8 +98,9 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     };
     load_w(k_lo);
     // ... and the rest of this warp's weight slice is requested into L2, one 128-byte line per
-    // request, so that HBM keeps streaming while the predecessor finishes
-    for (int s = 0; s < SETS; ++s) {
+    // request, so that HBM keeps streaming while the predecessor finishes (only for weights
+    // that fit in L2 with room to spare: requested too far ahead, lines are evicted again)
+    for (int s = 0; s < SETS && prefetch_l2; ++s) {
       const bf16* row = W + (long)min(row0 + s * up_offset + (lane & 15), N + s * up_offset - 1) * ldw;
       for (int k = k_lo + 32 * U + 64 * (lane >> 4); k < k_hi; k += 128)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(row + k));
@@ -176,12 +178,13 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
   const int MT = warps / KS;
   const int blocks = (tiles + MT - 1) / MT;
   cudaError_t err;
+  const int prefetch_l2 = (long)N * K * 2 * (MODE == OUT_SWIGLU ? 2 : 1) <= (64L << 20);
   if (warps == 16)
     err = launch_pdl(gemm_small_m_kernel<NT, MODE, 16, 2>, dim3(blocks), dim3(512), 0, stream, x, ldx, W, ldw, out,
-                     ldo, M, N, K, KS, kper, up_offset);
+                     ldo, M, N, K, KS, kper, up_offset, prefetch_l2);
   else
     err = launch_pdl(gemm_small_m_kernel<NT, MODE, 8, 4>, dim3(blocks), dim3(256), 0, stream, x, ldx, W, ldw, out,
-                     ldo, M, N, K, KS, kper, up_offset);
+                     ldo, M, N, K, KS, kper, up_offset, prefetch_l2);
   return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
