@@ -1,0 +1,480 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation tensor
+// cores: S = Q K^T and O += P V are tcgen05.mma with accumulators in tensor memory, Q, K and V
+// tiles arrive by TMA (128-byte swizzle) straight from the QKV buffer and the cache pages.
+// bfloat16, head_dim 128, group size a divisor of 128, page size 8/16/32/64, no window; the
+// mma.sync kernel of attention_prefill.cu serves everything else.
+//
+// Work item: (sequence, kv head, block of 128 rows); rows are the (query token, head of the
+// group) pairs in token-major order, so one 3-D TMA box [128/G tokens, G heads, 64] is the Q
+// tile and the group's heads share every K/V tile.  Keys come in tiles of 64 (64/page_size
+// pages, one TMA box per page and half of D).  Six warps:
+//   warp 0, one lane : TMA producer (Q once, then K and V tiles through 2-stage rings);
+//   warp 1, one lane : MMA issuer.  Order: S_0, S_1, then per tile j: P_j ready -> PV_j,
+//                      S_{j+2}.  S has two TMEM buffers, so the tensor core computes S_{j+1}
+//                      and PV_{j-1} while the softmax warps work on tile j;
+//   warps 2..5       : softmax, one thread per row: reads S from TMEM, masks, online softmax
+//                      in fp32 (exp2, scale folded in), writes P (bf16) to shared memory (two
+//                      buffers) in the swizzled K-major layout that the PV MMA reads, keeps O in registers and
+//                      folds each PV tile in (O = O * correction + PV), finally stores O / l.
+// V is the B operand of PV in MN-major form (rows = keys): descriptor with the halves of D
+// 8 KB apart (leading offset) and 8-key groups 1 KB apart (stride offset); 16 keys = 2 KB.
+// Keys past a block's last position are zeroed in shared memory before PV (stale or poisoned
+// page contents must not meet a zero probability).  Every mbarrier wait is bounded; on expiry
+// the block raises its abort flag and the global error word, frees TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 128;
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 64;
+constexpr int THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
+constexpr int Q_BYTES = BLOCK_M * D * 2;        // 32 KB: two halves of [128 rows][128 B]
+constexpr int KV_BYTES = BLOCK_N * D * 2;       // 16 KB: two halves of [64 rows][128 B]
+constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB: [128 rows][128 B]
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 1024;
+constexpr int TMEM_COLS = 256;                  // S0 [0,64), S1 [64,128), PV [128,256)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// K-major tile [rows][64] bf16, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (rows = K index, 64 contiguous N per 128-byte row), 128-byte swizzle:
+// leading offset = distance between 64-wide blocks of N, stride offset = 8 rows of K.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t n_block_bytes) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(n_block_bytes >> 4) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+enum { BAR_Q = 0, BAR_K_FULL = 1, BAR_K_EMPTY = 3, BAR_V_FULL = 5, BAR_V_EMPTY = 7, BAR_S_FULL = 9, BAR_P_FULL = 11,
+       BAR_PV_FULL = 12, NUM_BARS = 13 };
+
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                            const __grid_constant__ CUtensorMap tmap_v, const int* __restrict__ block_table,
+                            int max_pages, const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
+                            bf16* __restrict__ out, int num_seqs, int num_work, int nq, int nkv, int ps,
+                            float scale_log2, int skip_single, int* __restrict__ error_word) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = base;                         // [2 halves][128 rows][128 B]
+  unsigned char* k_s = q_s + Q_BYTES;                // 2 stages x [2 halves][64 rows][128 B]
+  unsigned char* v_s = k_s + 2 * KV_BYTES;           // 2 stages x [2 halves][64 rows][128 B]
+  unsigned char* p_s = v_s + 2 * KV_BYTES;           // 2 buffers x [128 rows][128 B]
+  __shared__ __align__(8) unsigned long long bars[NUM_BARS];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_flag;
+  __shared__ int s_item[2];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.y;
+  const int G = nq / nkv;
+  const uint32_t bar0 = smem_addr(&bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    // heavy blocks (late rows of long prompts) first: walk the work list from its end
+    int acc = 0, found = -1, rb = 0;
+    const int w = num_work - 1 - (int)blockIdx.x;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int ql = cu_seqlens[s + 1] - cu_seqlens[s];
+      if (ql <= 0 || (skip_single && ql == 1)) continue;
+      const int nb = (ql * G + BLOCK_M - 1) / BLOCK_M;
+      if (w < acc + nb) {
+        found = s;
+        rb = w - acc;
+        break;
+      }
+      acc += nb;
+    }
+    s_item[0] = found;
+    s_item[1] = rb;
+    mbar_init(bar(BAR_Q), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_K_FULL + i), 1);
+      mbar_init(bar(BAR_K_EMPTY + i), 1);
+      mbar_init(bar(BAR_V_FULL + i), 1);
+      mbar_init(bar(BAR_V_EMPTY + i), 1);
+      mbar_init(bar(BAR_S_FULL + i), 1);
+    }
+    mbar_init(bar(BAR_P_FULL), 128);
+    mbar_init(bar(BAR_PV_FULL), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const int seq = s_item[0];
+
+  if (seq >= 0) {
+    const int row0 = s_item[1] * BLOCK_M;
+    const int tok0 = cu_seqlens[seq];
+    const int q_len = cu_seqlens[seq + 1] - tok0;
+    const int kv_len = kv_lens[seq];
+    const int rows = q_len * G;
+    const int base_pos = kv_len - q_len;
+    const int last_row = min(rows, row0 + BLOCK_M) - 1;
+    const int p_max = base_pos + last_row / G;
+    const int num_tiles = p_max / BLOCK_N + 1;
+    const int* bt = block_table + (long)seq * max_pages;
+    const int pages_per_tile = BLOCK_N / ps;
+
+    if (warp == 0) {
+      if (lane == 0) {  // ---- TMA producer ---------------------------------------------------------
+        mbar_expect_tx(bar(BAR_Q), Q_BYTES);
+        tma_load_3d(smem_addr(q_s), &tmap_q, bar(BAR_Q), 0, kvh * G, tok0 + row0 / G);
+        tma_load_3d(smem_addr(q_s) + Q_BYTES / 2, &tmap_q, bar(BAR_Q), 64, kvh * G, tok0 + row0 / G);
+        bool ok = true;
+        for (int j = 0; j < num_tiles && ok; ++j) {
+          const int st = j & 1;
+          const uint32_t phase = (j >> 1) & 1;
+          // pages of this tile that exist in the block table (the rest of the tile is masked)
+          int page_ids[8];
+          int n_valid = 0;
+          for (int i = 0; i < pages_per_tile; ++i) {
+            const int pi = j * pages_per_tile + i;
+            const int first_key = pi * ps;
+            page_ids[i] = (pi < max_pages && first_key <= p_max) ? bt[pi] : -1;
+            if (page_ids[i] >= 0) ++n_valid;
+          }
+          const uint32_t bytes = (uint32_t)n_valid * (uint32_t)ps * 256u;
+          // keys
+          ok = mbar_wait(bar(BAR_K_EMPTY + st), phase ^ 1, &abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar(BAR_K_FULL + st), bytes);
+          for (int i = 0; i < pages_per_tile; ++i) {
+            if (page_ids[i] < 0) continue;
+            const uint32_t dst = smem_addr(k_s) + st * KV_BYTES + i * ps * 128;
+            const int y = (page_ids[i] * nkv + kvh) * ps;
+            tma_load_2d(dst, &tmap_k, bar(BAR_K_FULL + st), 0, y);
+            tma_load_2d(dst + KV_BYTES / 2, &tmap_k, bar(BAR_K_FULL + st), 64, y);
+          }
+          // values
+          ok = mbar_wait(bar(BAR_V_EMPTY + st), phase ^ 1, &abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar(BAR_V_FULL + st), bytes);
+          for (int i = 0; i < pages_per_tile; ++i) {
+            if (page_ids[i] < 0) continue;
+            const uint32_t dst = smem_addr(v_s) + st * KV_BYTES + i * ps * 128;
+            const int y = (page_ids[i] * nkv + kvh) * ps;
+            tma_load_2d(dst, &tmap_v, bar(BAR_V_FULL + st), 0, y);
+            tma_load_2d(dst + KV_BYTES / 2, &tmap_v, bar(BAR_V_FULL + st), 64, y);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {  // ---- MMA issuer -----------------------------------------------------------
+        constexpr uint32_t idesc_s = idesc_bf16(BLOCK_M, BLOCK_N, 0);   // S = Q K^T: N = 64 keys
+        constexpr uint32_t idesc_pv = idesc_bf16(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
+        const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s);
+        auto issue_s = [&](int j) -> bool {  // S_j into TMEM buffer j & 1
+          const int st = j & 1;
+          if (!mbar_wait(bar(BAR_K_FULL + st), (j >> 1) & 1, &abort_flag)) return false;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t k_addr = smem_addr(k_s) + st * KV_BYTES;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t half = (k >> 2), sub = (k & 3) * 2;  // 4 steps of 32 bytes per 64-wide half
+            umma(tmem + st * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
+                 desc_kmajor(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
+          }
+          umma_commit(bar(BAR_K_EMPTY + st));  // the key tile may be overwritten
+          umma_commit(bar(BAR_S_FULL + st));   // S_j is in TMEM
+          return true;
+        };
+        bool ok = mbar_wait(bar(BAR_Q), 0, &abort_flag);
+        if (ok) ok = issue_s(0);
+        if (ok && num_tiles > 1) ok = issue_s(1);
+        for (int j = 0; j < num_tiles && ok; ++j) {
+          const int st = j & 1;
+          ok = mbar_wait(bar(BAR_P_FULL), j & 1, &abort_flag);  // P_j written, S_j and PV_{j-1} consumed
+          if (!ok) break;
+          ok = mbar_wait(bar(BAR_V_FULL + st), (j >> 1) & 1, &abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
+            umma(tmem + 2 * BLOCK_N, desc_kmajor(p_addr + st * P_BYTES) + 2 * k,
+                 desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2),
+                 idesc_pv, k > 0 ? 1u : 0u);
+          umma_commit(bar(BAR_V_EMPTY + st));
+          umma_commit(bar(BAR_PV_FULL));
+          if (j + 2 < num_tiles) ok = issue_s(j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
+        }
+      }
+    } else {  // ---- softmax: one thread per row ------------------------------------------------------
+      const int quarter = warp & 3;
+      const int r = quarter * 32 + lane;  // row of the tile = TMEM lane
+      const int R = row0 + r;
+      const bool row_ok = R < rows;
+      const int pos = row_ok ? base_pos + R / G : -1;
+      const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+      float o[D];
+#pragma unroll
+      for (int d = 0; d < D; ++d) o[d] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;
+      bool ok = true;
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(bar(BAR_S_FULL + st), (j >> 1) & 1, &abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t sa[32], sb[32];
+        tmem_load32(lane_base + st * BLOCK_N, sa);
+        tmem_load32(lane_base + st * BLOCK_N + 32, sb);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int key0 = j * BLOCK_N;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float a = __uint_as_float(sa[c]), b = __uint_as_float(sb[c]);
+          if (key0 + c > pos) a = -INFINITY;
+          if (key0 + 32 + c > pos) b = -INFINITY;
+          sa[c] = __float_as_uint(a);
+          sb[c] = __float_as_uint(b);
+          mx = fmaxf(mx, fmaxf(a, b));
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = exp2f((m_run - m_use) * scale_log2);
+        m_run = m_new;
+        float sum = 0.f;
+        // probabilities, rounded to bf16 as the MMA will see them, into the swizzled P tile
+        unsigned char* p_row = p_s + st * P_BYTES + r * 128;  // P_j goes to buffer j & 1: PV_{j-1} may still read the other
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = ch * 8 + 2 * e;
+            const float x0 = exp2f((__uint_as_float(c < 32 ? sa[c] : sb[c - 32]) - m_use) * scale_log2);
+            const float x1 = exp2f((__uint_as_float(c + 1 < 32 ? sa[c + 1] : sb[c + 1 - 32]) - m_use) * scale_log2);
+            sum += x0 + x1;
+            w[e] = pack2(x0, x1);
+          }
+          *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l_run = l_run * corr + sum;
+        // fold the previous tile's PV into O (it also frees P and the PV accumulator), then rescale
+        if (j > 0) {
+          ok = mbar_wait(bar(BAR_PV_FULL), (j - 1) & 1, &abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t pv[32];
+            tmem_load32(lane_base + 2 * BLOCK_N + c0, pv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c0 + c] = (o[c0 + c] + __uint_as_float(pv[c])) * corr;
+          }
+        }
+        // keys of this tile past the block's last position: zero their value rows before PV reads them
+        if (key0 + BLOCK_N - 1 > p_max) {
+          ok = mbar_wait(bar(BAR_V_FULL + st), (j >> 1) & 1, &abort_flag);
+          if (!ok) break;
+          const int vrow = r & 63, half = r >> 6;
+          if (key0 + vrow > p_max) {
+            uint4* dst = reinterpret_cast<uint4*>(v_s + st * KV_BYTES + half * (KV_BYTES / 2) + vrow * 128);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) dst[ch] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V) visible to the MMA
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(bar(BAR_P_FULL));
+      }
+      if (ok) ok = mbar_wait(bar(BAR_PV_FULL), (num_tiles - 1) & 1, &abort_flag);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = 1.f / l_run;
+        bf16* dst = row_ok ? out + ((long)(tok0 + R / G) * nq + kvh * G + R % G) * D : nullptr;
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t pv[32];
+          tmem_load32(lane_base + 2 * BLOCK_N + c0, pv);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              float v8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v8[e] = (o[c0 + c + e] + __uint_as_float(pv[c + e])) * inv;
+              store8(dst + c0 + c, v8);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+  if (tid == 0 && abort_flag && error_word) atomicExch(error_word, 2);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+}  // namespace
+
+// q: the QKV buffer, [num_tokens, *] bf16 with row stride q_stride (elements), head h at column
+// h * 128.  kpages / vpages: [num_rows_kv / (nkv * ps), nkv, ps, 128] bf16 of one layer, num_rows_kv
+// rows of 128 in all.  num_work = sum over served sequences of ceil(q_len * (nq / nkv) / 128).
+// Returns Q3_ERR_UNSUPPORTED for shapes this kernel does not take (the caller then uses the
+// mma.sync kernel).  error_word: device int set to 2 if a wait inside the kernel expired.
+Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num_tokens, const void* kpages,
+                                            const void* vpages, long num_rows_kv, const int* block_table,
+                                            int max_pages, const int* kv_lens, const int* cu_seqlens, void* out,
+                                            int num_seqs, int num_work, int nq, int nkv, int head_dim, int ps,
+                                            float scale, int skip_single, int* error_word, cudaStream_t stream) {
+  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
+  if (nq < 1 || nkv < 1 || nq % nkv) return Q3_ERR_ARGUMENT;
+  const int G = nq / nkv;
+  if (head_dim != D || BLOCK_M % G || (ps != 8 && ps != 16 && ps != 32 && ps != 64) || q_stride % 8 ||
+      nkv > 65535 || (((uintptr_t)q | (uintptr_t)kpages | (uintptr_t)vpages) & 15))
+    return Q3_ERR_UNSUPPORTED;
+  if (num_work == 0) return Q3_OK;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return Q3_ERR_LAUNCH;
+  CUtensorMap tq, tk, tv;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)num_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(BLOCK_M / G)};
+    const cuuint32_t es[3] = {1, 1, 1};
+    if (fn(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return Q3_ERR_LAUNCH;
+  }
+  for (int which = 0; which < 2; ++which) {
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_rows_kv};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)ps};
+    const cuuint32_t es[2] = {1, 1};
+    if (fn(which ? &tv : &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? vpages : kpages), dims,
+           strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return Q3_ERR_LAUNCH;
+  }
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid(num_work, nkv);
+  prefill_attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, block_table, max_pages, kv_lens,
+                                                                    cu_seqlens, (bf16*)out, num_seqs, num_work, nq,
+                                                                    nkv, ps, scale * 1.4426950408889634f,
+                                                                    skip_single, error_word);
+  return q3_launch_status();
+}

@@ -72,6 +72,11 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                        c_void_p],
     },
+    "attention_prefill_tc": {
+        "q3_paged_attention_prefill_tc": [c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_long, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, c_int, c_void_p, c_void_p],
+    },
     "gemm_f32": {
         "q3_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -106,6 +111,7 @@ class CudaOps:
         if large_gemm not in ("auto", "tcgen05", "library"):
             raise ValueError("large_gemm must be auto, tcgen05 or library")
         self.large_gemm = large_gemm
+        self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -207,7 +213,22 @@ class CudaOps:
             cu = step.host_cu_seqlens
             qlens = [cu[b + 1] - cu[b] for b in range(step.num_seqs)]
             work = sum(-(-n * group // 128) for n in qlens if n > 1)
-            if work:
+            done = False
+            if (work and head_dim == 128 and not window and 128 % group == 0 and page_size in (8, 16, 32, 64)
+                    and self.prefill_attention == "tcgen05"):
+                # tcgen05/TMEM kernel; it answers "unsupported" for what it does not take
+                self.launches += 1
+                code = self._get("attention_prefill_tc", "q3_paged_attention_prefill_tc")(
+                    _ptr(q), q_stride, q.shape[0], _ptr(k_pages), _ptr(v_pages),
+                    k_pages.shape[0] * num_kv_heads * page_size, _ptr(block_table), block_table.shape[1],
+                    _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), step.num_seqs, work, num_heads,
+                    num_kv_heads, head_dim, page_size, float(scale), 1, _ptr(self._error_word(out.device)),
+                    self._stream())
+                if code == 0:
+                    done = True
+                elif code != 1:
+                    _check(code, "paged_attention_prefill_tc")
+            if work and not done:
                 self._call("attention_prefill", "q3_paged_attention_prefill", "paged_attention_prefill",
                            _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                            block_table.shape[1], _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out),
@@ -316,7 +337,8 @@ class CudaOps:
         err = getattr(self, "_err", None)
         if err is not None and int(err.item()) != 0:
             err.zero_()
-            raise KernelError("a wait inside gemm_tcgen05 expired: the kernel gave up and its output is invalid")
+            raise KernelError("a bounded wait inside a tcgen05 kernel expired: the kernel gave up and its output "
+                              "is invalid")
 
     def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None):
         """``x @ weight^T`` on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).  ``mode=2``: SwiGLU with

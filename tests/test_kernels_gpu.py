@@ -268,6 +268,33 @@ def test_prefill_attention_tensor_cores(ops, nq, nkv, D, ps, window):
     close(out, want, torch.bfloat16, "prefill attention", bf16_tol=1e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,ps", [(32, 8, 16), (8, 8, 8), (16, 1, 64), (8, 2, 32), (32, 8, 16)])
+def test_prefill_attention_tcgen05_matches_mma_kernel(ops, nq, nkv, ps):
+    """head_dim 128 without a window takes the tcgen05/TMEM kernel; the mma.sync kernel and the
+    plain statement are the references."""
+    D = 128
+    lens = [300, 1, 77, 700, 64, 130, 2, 1333, 128]
+    qlens = [1, 1, 77, 200, 2, 130, 2, 1333, 128]
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, torch.bfloat16, 92)
+    step = step_for(lens, qlens)
+
+    def run(which):
+        ops.prefill_attention = which
+        out = torch.full((pr["T"], nq * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D, k_pages=pr["k"],
+                            v_pages=pr["v"], block_table=pr["bt"], token_seq=pr["seq"], positions=pr["pos"], out=out,
+                            page_size=ps, scale=1 / math.sqrt(D), window=None, step=step)
+        ops.prefill_attention = "tcgen05"
+        return out
+
+    tc, mma = run("tcgen05"), run("mma")
+    ops.raise_if_kernel_error()
+    assert torch.isfinite(tc).all(), "every row is written"
+    want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16)
+    close(mma, want, torch.bfloat16, "mma.sync prefill", bf16_tol=1e-2)
+    close(tc, want, torch.bfloat16, "tcgen05 prefill", bf16_tol=1e-2)
+
+
 def test_prefill_attention_far_key_diagonal_and_poison(ops):
     nq, nkv, D, ps = 8, 2, 128, 16
     lens, qlens = [900, 257], [300, 257]
