@@ -8,14 +8,16 @@
 // group) pairs in token-major order, so one 3-D TMA box [128/G tokens, G heads, 64] is the Q
 // tile and the group's heads share every K/V tile.  Keys come in tiles of 64 (64/page_size
 // pages, one TMA box per page and half of D).  Six warps:
-//   warp 0, one lane : TMA producer (Q once, then K and V tiles through 2-stage rings);
+//   warp 0           : TMA producer (Q once, then K and V tiles through 4-stage rings; the
+//                      lanes issue a tile's page boxes side by side);
 //   warp 1, one lane : MMA issuer.  Order: S_0, S_1, then per tile j: P_j ready -> PV_j,
 //                      S_{j+2}.  S has two TMEM buffers, so the tensor core computes S_{j+1}
 //                      and PV_{j-1} while the softmax warps work on tile j;
 //   warps 2..5       : softmax, one thread per row: reads S from TMEM, masks, online softmax
 //                      in fp32 (exp2, scale folded in), writes P (bf16) to shared memory (two
-//                      buffers) in the swizzled K-major layout that the PV MMA reads, keeps O in registers and
-//                      folds each PV tile in (O = O * correction + PV), finally stores O / l.
+//                      buffers) in the swizzled K-major layout that the PV MMA reads; O stays in
+//                      TMEM (the MMAs accumulate into it) and is rescaled there only when a
+//                      row's maximum has grown by more than 2^8; finally stores O / l.
 // V is the B operand of PV in MN-major form (rows = keys): descriptor with the halves of D
 // 8 KB apart (leading offset) and 8-key groups 1 KB apart (stride offset); 16 keys = 2 KB.
 // Keys past a block's last position are zeroed in shared memory before PV (stale or poisoned
@@ -35,7 +37,8 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 32 KB: two halves of [128 rows][128 B]
 constexpr int KV_BYTES = BLOCK_N * D * 2;       // 16 KB: two halves of [64 rows][128 B]
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB: [128 rows][128 B]
-constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 1024;
+constexpr int KV_STAGES = 4;                    // key tiles and value tiles in flight
+constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 2 * P_BYTES + 1024;
 constexpr int TMEM_COLS = 256;                  // S0 [0,64), S1 [64,128), PV [128,256)
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -126,8 +129,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-enum { BAR_Q = 0, BAR_K_FULL = 1, BAR_K_EMPTY = 3, BAR_V_FULL = 5, BAR_V_EMPTY = 7, BAR_S_FULL = 9, BAR_P_FULL = 11,
-       BAR_PV_FULL = 12, NUM_BARS = 13 };
+enum { BAR_Q = 0, BAR_K_FULL = 1, BAR_K_EMPTY = BAR_K_FULL + KV_STAGES, BAR_V_FULL = BAR_K_EMPTY + KV_STAGES,
+       BAR_V_EMPTY = BAR_V_FULL + KV_STAGES, BAR_S_FULL = BAR_V_EMPTY + KV_STAGES, BAR_P_FULL = BAR_S_FULL + 2,
+       BAR_PV_FULL = BAR_P_FULL + 1, NUM_BARS = BAR_PV_FULL + 1 };
 
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -138,9 +142,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                         // [2 halves][128 rows][128 B]
-  unsigned char* k_s = q_s + Q_BYTES;                // 2 stages x [2 halves][64 rows][128 B]
-  unsigned char* v_s = k_s + 2 * KV_BYTES;           // 2 stages x [2 halves][64 rows][128 B]
-  unsigned char* p_s = v_s + 2 * KV_BYTES;           // 2 buffers x [128 rows][128 B]
+  unsigned char* k_s = q_s + Q_BYTES;                // KV_STAGES x [2 halves][64 rows][128 B]
+  unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;   // KV_STAGES x [2 halves][64 rows][128 B]
+  unsigned char* p_s = v_s + KV_STAGES * KV_BYTES;   // 2 buffers x [128 rows][128 B]
   __shared__ __align__(8) unsigned long long bars[NUM_BARS];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
@@ -171,13 +175,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     s_item[0] = found;
     s_item[1] = rb;
     mbar_init(bar(BAR_Q), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(bar(BAR_K_FULL + i), 1);
       mbar_init(bar(BAR_K_EMPTY + i), 1);
       mbar_init(bar(BAR_V_FULL + i), 1);
       mbar_init(bar(BAR_V_EMPTY + i), 1);
-      mbar_init(bar(BAR_S_FULL + i), 1);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(bar(BAR_S_FULL + i), 1);
     mbar_init(bar(BAR_P_FULL), 128);
     mbar_init(bar(BAR_PV_FULL), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -207,48 +211,45 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     const int* bt = block_table + (long)seq * max_pages;
     const int pages_per_tile = BLOCK_N / ps;
 
-    if (warp == 0) {
-      if (lane == 0) {  // ---- TMA producer ---------------------------------------------------------
+    if (warp == 0) {  // ---- TMA producer: lane 0 waits and arms the barriers, the lanes share the loads ----
+      if (lane == 0) {
         mbar_expect_tx(bar(BAR_Q), Q_BYTES);
         tma_load_3d(smem_addr(q_s), &tmap_q, bar(BAR_Q), 0, kvh * G, tok0 + row0 / G);
         tma_load_3d(smem_addr(q_s) + Q_BYTES / 2, &tmap_q, bar(BAR_Q), 64, kvh * G, tok0 + row0 / G);
-        bool ok = true;
-        for (int j = 0; j < num_tiles && ok; ++j) {
-          const int st = j & 1;
-          const uint32_t phase = (j >> 1) & 1;
-          // pages of this tile that exist in the block table (the rest of the tile is masked)
-          int page_ids[8];
-          int n_valid = 0;
-          for (int i = 0; i < pages_per_tile; ++i) {
-            const int pi = j * pages_per_tile + i;
-            const int first_key = pi * ps;
-            page_ids[i] = (pi < max_pages && first_key <= p_max) ? bt[pi] : -1;
-            if (page_ids[i] >= 0) ++n_valid;
-          }
-          const uint32_t bytes = (uint32_t)n_valid * (uint32_t)ps * 256u;
-          // keys
-          ok = mbar_wait(bar(BAR_K_EMPTY + st), phase ^ 1, &abort_flag);
-          if (!ok) break;
-          mbar_expect_tx(bar(BAR_K_FULL + st), bytes);
-          for (int i = 0; i < pages_per_tile; ++i) {
-            if (page_ids[i] < 0) continue;
-            const uint32_t dst = smem_addr(k_s) + st * KV_BYTES + i * ps * 128;
-            const int y = (page_ids[i] * nkv + kvh) * ps;
-            tma_load_2d(dst, &tmap_k, bar(BAR_K_FULL + st), 0, y);
-            tma_load_2d(dst + KV_BYTES / 2, &tmap_k, bar(BAR_K_FULL + st), 64, y);
-          }
-          // values
-          ok = mbar_wait(bar(BAR_V_EMPTY + st), phase ^ 1, &abort_flag);
-          if (!ok) break;
-          mbar_expect_tx(bar(BAR_V_FULL + st), bytes);
-          for (int i = 0; i < pages_per_tile; ++i) {
-            if (page_ids[i] < 0) continue;
-            const uint32_t dst = smem_addr(v_s) + st * KV_BYTES + i * ps * 128;
-            const int y = (page_ids[i] * nkv + kvh) * ps;
-            tma_load_2d(dst, &tmap_v, bar(BAR_V_FULL + st), 0, y);
-            tma_load_2d(dst + KV_BYTES / 2, &tmap_v, bar(BAR_V_FULL + st), 64, y);
-          }
+      }
+      // a tile is 64 / ps pages x 2 halves of D: one box per lane (small boxes are slow to issue
+      // one after another from a single thread)
+      const int my_page = lane >> 1, my_half = lane & 1;
+      int ok = 1;
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t phase = (j / KV_STAGES) & 1;
+        // pages of this tile that exist in the block table (the rest of the tile is masked)
+        int page = -1;
+        if (my_page < pages_per_tile) {
+          const int pi = j * pages_per_tile + my_page;
+          if (pi < max_pages && pi * ps <= p_max) page = bt[pi];
         }
+        const uint32_t boxes = __popc(__ballot_sync(0xffffffffu, page >= 0));
+        const uint32_t bytes = boxes * (uint32_t)ps * 128u;
+        const int y = (page * nkv + kvh) * ps;
+        const uint32_t off = st * KV_BYTES + my_half * (KV_BYTES / 2) + my_page * ps * 128;
+        // keys
+        if (lane == 0) {
+          ok = mbar_wait(bar(BAR_K_EMPTY + st), phase ^ 1, &abort_flag);
+          if (ok) mbar_expect_tx(bar(BAR_K_FULL + st), bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (page >= 0) tma_load_2d(smem_addr(k_s) + off, &tmap_k, bar(BAR_K_FULL + st), my_half * 64, y);
+        // values
+        if (lane == 0) {
+          ok = mbar_wait(bar(BAR_V_EMPTY + st), phase ^ 1, &abort_flag);
+          if (ok) mbar_expect_tx(bar(BAR_V_FULL + st), bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (page >= 0) tma_load_2d(smem_addr(v_s) + off, &tmap_v, bar(BAR_V_FULL + st), my_half * 64, y);
       }
     } else if (warp == 1) {
       if (lane == 0) {  // ---- MMA issuer -----------------------------------------------------------
@@ -256,36 +257,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         constexpr uint32_t idesc_pv = idesc_bf16(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
         const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s);
         auto issue_s = [&](int j) -> bool {  // S_j into TMEM buffer j & 1
-          const int st = j & 1;
-          if (!mbar_wait(bar(BAR_K_FULL + st), (j >> 1) & 1, &abort_flag)) return false;
+          const int st = j % KV_STAGES, sbuf = j & 1;
+          if (!mbar_wait(bar(BAR_K_FULL + st), (j / KV_STAGES) & 1, &abort_flag)) return false;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t k_addr = smem_addr(k_s) + st * KV_BYTES;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t half = (k >> 2), sub = (k & 3) * 2;  // 4 steps of 32 bytes per 64-wide half
-            umma(tmem + st * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
+            umma(tmem + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
                  desc_kmajor(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
           }
           umma_commit(bar(BAR_K_EMPTY + st));  // the key tile may be overwritten
-          umma_commit(bar(BAR_S_FULL + st));   // S_j is in TMEM
+          umma_commit(bar(BAR_S_FULL + sbuf)); // S_j is in TMEM
           return true;
         };
         bool ok = mbar_wait(bar(BAR_Q), 0, &abort_flag);
         if (ok) ok = issue_s(0);
         if (ok && num_tiles > 1) ok = issue_s(1);
         for (int j = 0; j < num_tiles && ok; ++j) {
-          const int st = j & 1;
+          const int st = j % KV_STAGES, pbuf = j & 1;
           ok = mbar_wait(bar(BAR_P_FULL), j & 1, &abort_flag);  // P_j written, S_j and PV_{j-1} consumed
           if (!ok) break;
-          ok = mbar_wait(bar(BAR_V_FULL + st), (j >> 1) & 1, &abort_flag);
+          ok = mbar_wait(bar(BAR_V_FULL + st), (j / KV_STAGES) & 1, &abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
 #pragma unroll
           for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
-            umma(tmem + 2 * BLOCK_N, desc_kmajor(p_addr + st * P_BYTES) + 2 * k,
+            umma(tmem + 2 * BLOCK_N, desc_kmajor(p_addr + pbuf * P_BYTES) + 2 * k,
                  desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2),
-                 idesc_pv, k > 0 ? 1u : 0u);
+                 idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(bar(BAR_V_EMPTY + st));
           umma_commit(bar(BAR_PV_FULL));
           if (j + 2 < num_tiles) ok = issue_s(j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
@@ -298,13 +299,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const bool row_ok = R < rows;
       const int pos = row_ok ? base_pos + R / G : -1;
       const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-      float o[D];
-#pragma unroll
-      for (int d = 0; d < D; ++d) o[d] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f;
+      const uint32_t o_addr = lane_base + 2 * BLOCK_N;
+      // O stays in TMEM and the MMAs accumulate into it.  The reference point of the exponentials
+      // (m_ref) is only moved when a row's maximum exceeds it by more than 2^8 after scaling; then
+      // O and l are rescaled.  Probabilities may therefore reach 2^8, which bf16 and fp32 hold easily,
+      // and the final O / l is unchanged.
+      const float slack = 8.f / scale_log2;
+      float m_ref = -INFINITY, l_run = 0.f;
       bool ok = true;
       for (int j = 0; j < num_tiles && ok; ++j) {
-        const int st = j & 1;
+        const int st = j & 1;             // S buffer and P buffer of this tile
+        const int vst = j % KV_STAGES;    // its value tile
         ok = mbar_wait(bar(BAR_S_FULL + st), (j >> 1) & 1, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -314,57 +319,83 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int key0 = j * BLOCK_N;
         float mx = -INFINITY;
+        if (key0 + BLOCK_N - 1 > pos) {  // the tile crosses this row's diagonal
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float a = __uint_as_float(sa[c]), b = __uint_as_float(sb[c]);
-          if (key0 + c > pos) a = -INFINITY;
-          if (key0 + 32 + c > pos) b = -INFINITY;
-          sa[c] = __float_as_uint(a);
-          sb[c] = __float_as_uint(b);
-          mx = fmaxf(mx, fmaxf(a, b));
+          for (int c = 0; c < 32; ++c) {
+            if (key0 + c > pos) sa[c] = 0xff800000u;       // -inf
+            if (key0 + 32 + c > pos) sb[c] = 0xff800000u;
+          }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = exp2f((m_run - m_use) * scale_log2);
-        m_run = m_new;
-        float sum = 0.f;
+        {  // eight independent running maxima: a single chain of 64 would expose its latency
+          float part[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) part[c] = fmaxf(__uint_as_float(sa[c]), __uint_as_float(sb[c]));
+#pragma unroll
+          for (int c = 8; c < 32; ++c)
+            part[c & 7] = fmaxf(part[c & 7], fmaxf(__uint_as_float(sa[c]), __uint_as_float(sb[c])));
+          mx = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
+                     fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+        }
+        float corr = 1.f;
+        if (mx > m_ref + slack || (m_ref == -INFINITY && mx > -INFINITY)) {
+          corr = m_ref == -INFINITY ? 0.f : exp2f((m_ref - mx) * scale_log2);
+          m_ref = mx;
+        }
+        const bool rescale = __any_sync(0xffffffffu, corr != 1.f) && j > 0;
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        float sums[4] = {0.f, 0.f, 0.f, 0.f};
         // probabilities, rounded to bf16 as the MMA will see them, into the swizzled P tile
-        unsigned char* p_row = p_s + st * P_BYTES + r * 128;  // P_j goes to buffer j & 1: PV_{j-1} may still read the other
+        unsigned char* p_row = p_s + st * P_BYTES + r * 128;  // buffer j & 1: PV_{j-1} may still read the other
+        const float neg = -m_use * scale_log2;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = ch * 8 + 2 * e;
-            const float x0 = exp2f((__uint_as_float(c < 32 ? sa[c] : sb[c - 32]) - m_use) * scale_log2);
-            const float x1 = exp2f((__uint_as_float(c + 1 < 32 ? sa[c + 1] : sb[c + 1 - 32]) - m_use) * scale_log2);
-            sum += x0 + x1;
+            const float x0 = exp2f(fmaf(__uint_as_float(c < 32 ? sa[c] : sb[c - 32]), scale_log2, neg));
+            const float x1 = exp2f(fmaf(__uint_as_float(c + 1 < 32 ? sa[c + 1] : sb[c + 1 - 32]), scale_log2, neg));
+            sums[e] += x0 + x1;
             w[e] = pack2(x0, x1);
           }
           *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        l_run = l_run * corr + sum;
-        // fold the previous tile's PV into O (it also frees P and the PV accumulator), then rescale
+        l_run = l_run * corr + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+        // PV_{j-1} must be finished before P_j is signalled: it keeps this barrier from running a
+        // phase ahead of the waiters, and O must be at rest if it has to be rescaled
         if (j > 0) {
           ok = mbar_wait(bar(BAR_PV_FULL), (j - 1) & 1, &abort_flag);
           if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (rescale) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ov[32];
+              tmem_load32(o_addr + c0, ov);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t pv[32];
-            tmem_load32(lane_base + 2 * BLOCK_N + c0, pv);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c0 + c] = (o[c0 + c] + __uint_as_float(pv[c])) * corr;
+              for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
+              asm volatile(
+                  "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                  "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                  ::"r"(o_addr + c0), "r"(ov[0]), "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]),
+                  "r"(ov[6]), "r"(ov[7]), "r"(ov[8]), "r"(ov[9]), "r"(ov[10]), "r"(ov[11]), "r"(ov[12]), "r"(ov[13]),
+                  "r"(ov[14]), "r"(ov[15]), "r"(ov[16]), "r"(ov[17]), "r"(ov[18]), "r"(ov[19]), "r"(ov[20]),
+                  "r"(ov[21]), "r"(ov[22]), "r"(ov[23]), "r"(ov[24]), "r"(ov[25]), "r"(ov[26]), "r"(ov[27]),
+                  "r"(ov[28]), "r"(ov[29]), "r"(ov[30]), "r"(ov[31])
+                  : "memory");
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           }
         }
         // keys of this tile past the block's last position: zero their value rows before PV reads them
         if (key0 + BLOCK_N - 1 > p_max) {
-          ok = mbar_wait(bar(BAR_V_FULL + st), (j >> 1) & 1, &abort_flag);
+          ok = mbar_wait(bar(BAR_V_FULL + vst), (j / KV_STAGES) & 1, &abort_flag);
           if (!ok) break;
           const int vrow = r & 63, half = r >> 6;
           if (key0 + vrow > p_max) {
-            uint4* dst = reinterpret_cast<uint4*>(v_s + st * KV_BYTES + half * (KV_BYTES / 2) + vrow * 128);
+            uint4* dst = reinterpret_cast<uint4*>(v_s + vst * KV_BYTES + half * (KV_BYTES / 2) + vrow * 128);
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) dst[ch] = make_uint4(0, 0, 0, 0);
           }
@@ -378,17 +409,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = 1.f / l_run;
         bf16* dst = row_ok ? out + ((long)(tok0 + R / G) * nq + kvh * G + R % G) * D : nullptr;
-#pragma unroll
+#pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t pv[32];
-          tmem_load32(lane_base + 2 * BLOCK_N + c0, pv);
+          uint32_t ov[32];
+          tmem_load32(o_addr + c0, ov);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (row_ok) {
 #pragma unroll
             for (int c = 0; c < 32; c += 8) {
               float v8[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v8[e] = (o[c0 + c + e] + __uint_as_float(pv[c + e])) * inv;
+              for (int e = 0; e < 8; ++e) v8[e] = __uint_as_float(ov[c + e]) * inv;
               store8(dst + c0 + c, v8);
             }
           }
