@@ -21,25 +21,46 @@
 
 namespace {
 
+// What the fused variant needs to make q, k and v of the newest token itself, from the raw
+// output of the q/k/v projection (row layout: nq q heads, nkv k heads, nkv v heads of D):
+// per-head RMSNorm weights (null: no norm), rotation tables [max_pos, D/2] (null: none).
+struct NewToken {
+  const float* q_w;
+  const float* k_w;
+  const float* cos_t;
+  const float* sin_t;
+  bf16* kpages;   // the same pages the kernel reads, writable
+  bf16* vpages;
+  float eps;
+  int max_pos;
+};
+
 constexpr int TILE = 64;     // keys per pipeline stage
 constexpr int WARPS = 4;     // each takes 16 keys of a tile
 constexpr int THREADS = WARPS * 32;
 
-template <int D>
+// FUSED: `q` is the raw q/k/v projection; the block norms and rotates its own queries, and the
+// block whose slice holds the newest position also makes that token's key and value, writes
+// them to their page and patches them into its tile (q/k/v math as in rope_kv.cu, same order of
+// operations, so both ways give the same bits).  Nothing the block reads before pdl_wait() is
+// written by a kernel of the same step, so the first key tiles are in flight while the
+// projection before this kernel is still finishing.
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
-decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpages,
-                        const bf16* __restrict__ vpages, const int* __restrict__ block_table, int max_pages,
+decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kpages,
+                        const bf16* vpages, const int* __restrict__ block_table, int max_pages,
                         const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
-                        int num_splits, int stages) {
+                        int num_splits, int stages, NewToken nt) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                  // [16][D] bf16
-  unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile)
+  unsigned char* new_s = smem + 16 * D * 2;   // FUSED: the newest key, then the newest value, [2][D] bf16
+  unsigned char* kv_s = new_s + (FUSED ? 2 * D * 2 : 0);    // stages x (K tile, V tile)
 
-  pdl_wait();  // keys and values of the newest token come from the kernel before this one
+  if (!FUSED) pdl_wait();  // keys and values of the newest token come from the kernel before this one
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int slot = blockIdx.z;                // index into the partial buffers
   const int seq = seq_list ? seq_list[slot] : slot;
@@ -62,13 +83,21 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
       mid_lse[((long)slot * nq + kvh * G + tid) * num_splits + split] = -INFINITY;
     return;
   }
+  // FUSED: position p is not in the cache yet; its row is left out of the copies and patched in
+  const bool owner = FUSED && p >= k_begin && p < k_end;
+  const int skip = FUSED ? p : -1;
 
   // ---- the group's queries: rows 0..G-1 of a 16-row tile, the rest zero -----------------
-  for (int c = tid; c < 16 * CHUNKS; c += THREADS) {
-    const int row = c / CHUNKS, chunk = c % CHUNKS;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < G) v = *reinterpret_cast<const uint4*>(q + (long)tok * q_stride + (long)(kvh * G + row) * D + chunk * 8);
-    *reinterpret_cast<uint4*>(q_s + swz<D>(row, chunk)) = v;
+  if (!FUSED) {
+    for (int c = tid; c < 16 * CHUNKS; c += THREADS) {
+      const int row = c / CHUNKS, chunk = c % CHUNKS;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < G) v = *reinterpret_cast<const uint4*>(q + (long)tok * q_stride + (long)(kvh * G + row) * D + chunk * 8);
+      *reinterpret_cast<uint4*>(q_s + swz<D>(row, chunk)) = v;
+    }
+  } else {
+    for (int c = tid; c < (16 - G) * CHUNKS; c += THREADS)
+      *reinterpret_cast<uint4*>(q_s + swz<D>(G + c / CHUNKS, c % CHUNKS)) = make_uint4(0, 0, 0, 0);
   }
 
   const int num_tiles = (k_end - k_begin + TILE - 1) / TILE;
@@ -92,7 +121,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + i;
-          const bool valid = j >= lo && j < k_end;
+          const bool valid = j >= lo && j < k_end && j != skip;
           const int off = swz<D>(r0 + i, chunk);
           cp_async16(smem_u32(k_dst + off), kpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
           cp_async16(smem_u32(v_dst + off), vpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
@@ -100,7 +129,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
       } else {
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + i;
-          const bool valid = j >= lo && j < k_end;
+          const bool valid = j >= lo && j < k_end && j != skip;
           long src = 0;
           if (valid) {
             const int page = bt[j / ps];
@@ -118,7 +147,80 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     if (s < num_tiles) load_tile(s, s);
     cp_async_commit();
   }
-  __syncthreads();  // q_s is complete
+  if (FUSED) {
+    pdl_wait();  // the q/k/v projection of this step
+    // D/16 threads per head; a thread owns elements [8c, 8c+8) and their rotation partners
+    // [8c + D/2, 8c + D/2 + 8).  Items: the group's q heads, then (owner only) the k and v head.
+    constexpr int TPH = D / 16, HALF = D / 2, PER_PASS = THREADS / TPH;
+    const int items = G + (owner ? 2 : 0);
+    const bf16* row = q + (long)tok * q_stride;
+    long cache_row = -1;
+    if (owner && p / ps < max_pages) {
+      const int page = bt[p / ps];
+      if (page >= 0) cache_row = (((long)page * nkv + kvh) * ps + (p % ps)) * D;
+    }
+    const int pc = p >= nt.max_pos ? nt.max_pos - 1 : p;
+    for (int base = 0; base < items; base += PER_PASS) {
+      const int item = base + tid / TPH, c = tid % TPH;
+      const bool live = item < items;
+      const bool is_q = item < G, is_v = item == G + 1;
+      const bf16* x = row + (is_q ? (long)(kvh * G + item) * D
+                                  : (long)(nq + (is_v ? nkv : 0) + kvh) * D);
+      float a[8], b[8];
+      if (live) {
+        load8(x + 8 * c, a);
+        load8(x + HALF + 8 * c, b);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = b[e] = 0.f;
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+      for (int o = TPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!live) continue;
+      if (!is_v) {
+        const float* w = is_q ? nt.q_w : nt.k_w;
+        if (w) {
+          const float rstd = rsqrtf(ss / (float)D + nt.eps);
+          float wa[8], wb[8];
+          load8(w + 8 * c, wa);
+          load8(w + HALF + 8 * c, wb);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            a[e] = (a[e] * rstd) * wa[e];
+            b[e] = (b[e] * rstd) * wb[e];
+          }
+        }
+        if (nt.cos_t) {
+          float cs[8], sn[8];
+          load8(nt.cos_t + (long)pc * HALF + 8 * c, cs);
+          load8(nt.sin_t + (long)pc * HALF + 8 * c, sn);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float ya = a[e], yb = b[e];
+            a[e] = ya * cs[e] - yb * sn[e];
+            b[e] = yb * cs[e] + ya * sn[e];
+          }
+        }
+      }
+      if (is_q) {
+        store8(reinterpret_cast<bf16*>(q_s + swz<D>(item, c)), a);
+        store8(reinterpret_cast<bf16*>(q_s + swz<D>(item, CHUNKS / 2 + c)), b);
+      } else {
+        bf16* side = reinterpret_cast<bf16*>(new_s) + (is_v ? D : 0);
+        store8(side + 8 * c, a);
+        store8(side + HALF + 8 * c, b);
+        if (cache_row >= 0) {
+          bf16* dst = (is_v ? nt.vpages : nt.kpages) + cache_row;
+          store8(dst + 8 * c, a);
+          store8(dst + HALF + 8 * c, b);
+        }
+      }
+    }
+  }
+  __syncthreads();  // q_s (and the newest key and value) are complete
 
   uint32_t qa[D / 16][4];
 #pragma unroll
@@ -139,8 +241,17 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
       if (nxt < num_tiles) load_tile(nxt, nxt % stages);
       cp_async_commit();
     }
-    const unsigned char* k_t = kv_s + (size_t)(tile % stages) * 2 * TILE_BYTES;
-    const unsigned char* v_t = k_t + TILE_BYTES;
+    unsigned char* k_t = kv_s + (size_t)(tile % stages) * 2 * TILE_BYTES;
+    unsigned char* v_t = k_t + TILE_BYTES;
+    if (FUSED && owner && tile == (p - k_begin) / TILE) {  // (uniform over the block)
+      const int r = p - k_begin - tile * TILE;
+      for (int c = tid; c < 2 * CHUNKS; c += THREADS) {
+        const int chunk = c % CHUNKS;
+        const uint4 v = *reinterpret_cast<const uint4*>(new_s + (c / CHUNKS) * D * 2 + chunk * 16);
+        *reinterpret_cast<uint4*>((c < CHUNKS ? k_t : v_t) + swz<D>(r, chunk)) = v;
+      }
+      __syncthreads();
+    }
     const int key0 = k_begin + tile * TILE + warp * 16;  // this warp's 16 keys
     if (key0 >= k_end) continue;                          // (uniform per warp)
 
@@ -286,26 +397,26 @@ __global__ void decode_combine_kernel(const float* __restrict__ mid_o, const flo
   }
 }
 
-template <int D>
+template <int D, bool FUSED>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
-                  int num_splits, cudaStream_t stream) {
+                  int num_splits, const NewToken& nt, cudaStream_t stream) {
   const int stages = 2;
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
   const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
-  const size_t smem = 16 * D * 2 + (pipe > merge ? pipe : merge);
+  const size_t smem = 16 * D * 2 + (FUSED ? 2 * D * 2 : 0) + (pipe > merge ? pipe : merge);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
       return Q3_ERR_LAUNCH;
     configured = true;
   }
   dim3 grid(num_splits, nkv, num_seqs);
-  if (launch_pdl(decode_attention_kernel<D>, grid, dim3(THREADS), smem, stream, q, q_stride, kpages, vpages,
+  if (launch_pdl(decode_attention_kernel<D, FUSED>, grid, dim3(THREADS), smem, stream, q, q_stride, kpages, vpages,
                  block_table, max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps,
-                 scale * 1.4426950408889634f, window, num_splits, stages) != cudaSuccess)
+                 scale * 1.4426950408889634f, window, num_splits, stages, nt) != cudaSuccess)
     return Q3_ERR_LAUNCH;
   if (num_splits > 1) {
     dim3 cgrid(nq, num_seqs);
@@ -314,6 +425,32 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
       return Q3_ERR_LAUNCH;
   }
   return Q3_OK;
+}
+
+template <bool FUSED>
+int dispatch_decode(const void* q, int q_stride, const void* kpages, const void* vpages, const int* block_table,
+                    int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
+                    float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
+                    int window, int num_splits, const NewToken& nt, cudaStream_t stream) {
+  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
+  if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
+  if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
+  if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
+  if (num_seqs == 0) return Q3_OK;
+  if (num_seqs > 65535 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
+#define Q3_DECODE_CASE(DIM)                                                                                     \
+  case DIM:                                                                                                     \
+    return launch_decode<DIM, FUSED>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages,        \
+                                     block_table, max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o,  \
+                                     mid_lse, num_seqs, nq, nkv, ps, scale, window, num_splits, nt, stream)
+  switch (D) {
+    Q3_DECODE_CASE(64);
+    Q3_DECODE_CASE(128);
+    Q3_DECODE_CASE(256);
+    default:
+      return Q3_ERR_UNSUPPORTED;
+  }
+#undef Q3_DECODE_CASE
 }
 
 }  // namespace
@@ -328,25 +465,30 @@ Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void*
                                         const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                         float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
                                         int window, int num_splits, cudaStream_t stream) {
-  if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
-  if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
-  if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
-  if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
-  if (num_seqs == 0) return Q3_OK;
-  if (num_seqs > 65535 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
-#define Q3_DECODE_CASE(DIM)                                                                                       \
-  case DIM:                                                                                                       \
-    return launch_decode<DIM>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,  \
-                              max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs, nq, \
-                              nkv, ps, scale, window, num_splits, stream)
-  switch (D) {
-    Q3_DECODE_CASE(64);
-    Q3_DECODE_CASE(128);
-    Q3_DECODE_CASE(256);
-    default:
-      return Q3_ERR_UNSUPPORTED;
-  }
-#undef Q3_DECODE_CASE
+  return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
+                                out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
+                                stream);
+}
+
+// The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the
+// q/k/v projection (rows of nq + 2*nkv heads); each sequence's newest position is
+// kv_lens[seq] - 1.  q_w / k_w (per-head RMSNorm weights, fp32 [D]) and cos_t / sin_t
+// ([max_pos, D/2], rotation over the whole head) may be null.  The key and value of the newest
+// token are written to their pages; q is not written back.
+Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, void* kpages, void* vpages,
+                                              const int* block_table, int max_pages, const int* kv_lens,
+                                              const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
+                                              float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
+                                              float scale, int window, int num_splits, const float* q_w,
+                                              const float* k_w, float eps, const float* cos_t, const float* sin_t,
+                                              int max_pos, cudaStream_t stream) {
+  if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w)) return Q3_ERR_ARGUMENT;
+  const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
+                         (uintptr_t)cos_t | (uintptr_t)sin_t;
+  if (bits & 15) return Q3_ERR_UNSUPPORTED;
+  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos};
+  return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
+                               out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

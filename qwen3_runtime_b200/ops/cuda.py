@@ -66,6 +66,10 @@ _SIGNATURES = {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_float, c_int, c_int, c_void_p],
+        "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                            c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
+                                            c_void_p, c_void_p, c_int, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -112,6 +116,7 @@ class CudaOps:
             raise ValueError("large_gemm must be auto, tcgen05 or library")
         self.large_gemm = large_gemm
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
+        self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -271,10 +276,21 @@ class CudaOps:
                 best, best_cost = splits, cost
         return best
 
+    def decode_new_token_ok(self, qkv, *, num_heads, num_kv_heads, head_dim, cos, q_weight, k_weight) -> bool:
+        """Whether the split-KV kernel can make q, k and v of the newest token itself (per-head
+        norm, rotation, cache write) for a step in which every sequence brings one token."""
+        return (self.fuse_decode_new_token and qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
+                and num_heads // num_kv_heads <= 16 and qkv.stride(0) % 8 == 0
+                and (cos is None or 2 * cos.shape[1] == head_dim)
+                and (q_weight is None) == (k_weight is None))
+
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
-                               max_kv_len, seq_list=None, num_splits=None):
-        """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu)."""
+                               max_kv_len, seq_list=None, num_splits=None, new_token=None):
+        """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
+        ``new_token`` (q_weight, k_weight, eps, cos, sin): ``q`` is the raw q/k/v projection and
+        the kernel also does the work of :meth:`qk_norm_rope_store` for the newest position of
+        each sequence, ``kv_lens - 1``."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
         if window:
@@ -285,6 +301,15 @@ class CudaOps:
             mid_o = torch.empty((num_seqs, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
             mid_lse = torch.empty((num_seqs, num_heads, splits), dtype=torch.float32, device=out.device)
         self.launches += 1 if splits > 1 else 0  # the merge kernel
+        if new_token is not None:
+            cos, sin = new_token["cos"], new_token["sin"]
+            self._call("attention_decode", "q3_paged_attention_decode_fused", "paged_attention_decode_fused",
+                       _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                       _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
+                       num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+                       splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
+                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0)
+            return out
         self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),

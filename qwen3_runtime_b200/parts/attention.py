@@ -81,13 +81,28 @@ class PagedAttention(Part):
         tables = self.position.rotation_tables()
         cos, sin = tables if tables is not None else (None, None)
         block_table = step.block_tables[cache.paged_index]
+        ctx_out = torch.empty((T, self.q_size), dtype=h.dtype, device=h.device)
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        fusable = getattr(ops, "decode_new_token_ok", None)
+        if (fusable is not None and step.decode_only and cache.writes
+                and fusable(qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                            cos=cos, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight)):
+            # one kernel: norm and rotation of the newest q and k, cache write, split-KV attention
+            width = step.extras.get("captured_width", 0)
+            ops.paged_attention_decode(
+                qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,
+                kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens, out=ctx_out, page_size=cache.page_size,
+                scale=self.scale, window=self.window, num_seqs=step.num_seqs,
+                max_kv_len=width * cache.page_size or step.max_kv_len,
+                new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin))
+            return ops.linear(ctx_out, self.o_weight)
         ops.qk_norm_rope_store(
             qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
-            eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos=cos, sin=sin,
+            eps=eps, cos=cos, sin=sin,
             positions=step.positions, token_seq=step.token_seq, block_table=block_table,
             k_pages=cache.k_pages, v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
-        ctx_out = torch.empty((T, self.q_size), dtype=h.dtype, device=h.device)
         ops.paged_attention(
             qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
             head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,

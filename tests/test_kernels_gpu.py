@@ -363,6 +363,44 @@ def test_decode_attention_split_kv(ops, nq, nkv, D, ps, splits):
         close(got, want, torch.bfloat16, f"decode attention window={window} splits={splits}", bf16_tol=1e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 64), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
+                                          (14, 2, 64, 3)])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False), (False, False)])
+def test_decode_attention_makes_the_newest_token_itself(ops, nq, nkv, D, ps, norm, rotate):
+    """One kernel (per-head norm, rotation, cache write, attention) against the two kernels it
+    replaces: the same bits in the output and in the pages, for every split count and window."""
+    lens = [1, 63, 64, 65, 700, 129, 2, 1000]
+    g = torch.Generator().manual_seed(5)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if norm else None
+    cos = sin = None
+    if rotate:
+        inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+        cos, sin = ops.rope_table(inv.cuda(), 1024)
+    assert ops.decode_new_token_ok(torch.empty((1, (nq + 2 * nkv) * D), dtype=torch.bfloat16, device="cuda"),
+                                   num_heads=nq, num_kv_heads=nkv, head_dim=D, cos=cos, q_weight=qw, k_weight=kw)
+    for splits, window in [(None, None), (1, None), (3, None), (8, 100), (2, 1), (5, 64)]:
+        pr = decode_problem(nq, nkv, D, ps, lens, 90)
+        two = dict(pr, q=pr["q"].clone(), k=pr["k"].clone(), v=pr["v"].clone())
+        ops.qk_norm_rope_store(two["q"], num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=qw, k_weight=kw,
+                               eps=1e-6, cos=cos, sin=sin, positions=pr["pos"], token_seq=pr["seq"],
+                               block_table=pr["bt"], k_pages=two["k"], v_pages=two["v"], page_size=ps, write_kv=True)
+        want = run_decode(ops, two, nq, nkv, D, ps, lens, window=window, splits=splits)
+        one = dict(pr, q=pr["q"].clone(), k=pr["k"].clone(), v=pr["v"].clone())
+        raw = one["q"].clone()
+        got = torch.zeros_like(want)
+        ops.paged_attention_decode(one["q"], one["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D,
+                                   k_pages=one["k"], v_pages=one["v"], block_table=pr["bt"], kv_lens=pr["kv_lens"],
+                                   cu_seqlens=pr["cu"], out=got, page_size=ps, scale=1 / math.sqrt(D), window=window,
+                                   num_seqs=len(lens), max_kv_len=max(lens), num_splits=splits,
+                                   new_token=dict(q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin))
+        what = f"splits={splits} window={window}"
+        assert torch.equal(got, want), what
+        assert torch.equal(one["k"], two["k"]) and torch.equal(one["v"], two["v"]), what
+        assert torch.equal(one["q"], raw), "the projection's output is read only"
+        assert not torch.equal(one["k"], pr["k"])
+
+
 def test_decode_attention_far_key_poison_and_subset(ops):
     nq, nkv, D, ps = 32, 8, 128, 16
     lens = [900, 333, 64]
