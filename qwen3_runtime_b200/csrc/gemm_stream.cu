@@ -1,0 +1,420 @@
+// out[M, N] = x[M, K] * W[N, K]^T for at most 16 tokens, bfloat16 in, fp32 accumulate: the
+// matrix products of a decode step, built as a stream over the weights.
+//
+// With so few tokens the product is memory bound, and what decides its speed is how many
+// bytes of W each SM keeps in flight.  Registers cannot hold enough, so the weights go
+// through shared memory: one producer lane per row issues bulk asynchronous copies
+// (cp.async.bulk, completion counted on an mbarrier) of whole row segments into a ring of
+// stages that fills most of the SM's shared memory (about 160-190 KB in flight per SM), and
+// 16 consumer warps feed them to mma.sync.  One block per SM, persistent over its units.
+//
+// Work: W is cut into panels of 8 rows (4 gate rows and the 4 up rows of the same features
+// for the SwiGLU product) and K into `parts` (1, 2, 4 or 8) equal ranges; a unit is one panel x one range and fills one
+// stage.  Block b always has range b % parts, so the tokens' values for that range live in
+// registers for the whole kernel: consumer warp w owns the 32-wide k-blocks w, w+16, ... of
+// the range.  The MMA is m16n8k16 with the tokens as its 16 rows and the panel's 8 weight
+// rows as its 8 columns; a thread pairs 8 consecutive k-values of its weight row (one
+// 16-byte shared-memory read, conflict free because the row pitch is 64 mod 128 bytes) with
+// the same 8 k-values of its token rows, which is a valid contraction because both operands
+// use the same permutation of k.  After a stage the 16 warps' partial tiles are summed
+// through shared memory in warp order.
+//
+// parts > 1: the blocks that share a panel form a thread-block cluster (block rank = range).
+// For unit u the block of rank u % parts leads: the others store their [16 tokens x 8 rows]
+// partial into a slot of the leader's shared memory (st.shared::cluster) and arrive on the
+// slot's mbarrier there; the leader adds the partials in range order and runs the epilogue.
+// A slot is used once, so nobody ever waits for a slot to become free.
+//
+// Every mbarrier wait is bounded; on expiry the waiter sets the error word and carries on
+// (the result is then invalid, and the host raises), so no barrier is ever abandoned.
+#include "common.cuh"
+
+namespace {
+
+enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_SWIGLU = 2 };
+constexpr int CONSUMER_WARPS = 16;
+constexpr int CONSUMERS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMERS + 32;
+constexpr int MAX_STAGES = 8;
+constexpr int MAX_LED = 16;                // units a block may lead in a cluster (slots are used once)
+constexpr int SMEM_LIMIT = 226 * 1024;     // dynamic; the barriers are static
+constexpr int RED_BYTES = 2 * CONSUMER_WARPS * 4 * 32 * 4;  // two buffers of the warps' tiles
+constexpr long long WAIT_LIMIT_CYCLES = 400000000ll;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; on expiry records `code` in the error word and returns (the caller carries on).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* error_word, int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      atomicExch(error_word, code);
+      return;
+    }
+  }
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct Plan {
+  int parts;       // ranges of K
+  int range;       // k-values per range (multiple of 32; the last range may be shorter)
+  int pitch;       // bytes between rows of a stage, 64 mod 128
+  int stages;
+  int blocks;      // multiple of parts
+  int panels;
+  int led;         // slots for the units a block leads (parts > 1)
+};
+
+// k-blocks of 32 per consumer warp: what its registers hold of the tokens' values
+template <bool HI> struct Blocks { static constexpr int value = 5; };
+
+// MODE: epilogue.  HI: tokens 8..15 exist (M > 8).
+template <int MODE, bool HI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw, void* __restrict__ out,
+                   int ldo, int M, int N, int K, int up_offset, Plan plan, int* __restrict__ error_word) {
+  constexpr int ROWS = 8;
+  constexpr int XB = Blocks<HI>::value;
+  constexpr int FPP = MODE == OUT_SWIGLU ? 4 : 8;  // output features per panel
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + MAX_LED];
+  const int stage_bytes = ROWS * plan.pitch;
+  float* red = reinterpret_cast<float*>(smem + (size_t)plan.stages * stage_bytes);  // [2][warps][4][32]
+  float* slots = red + RED_BYTES / 4;                                                // [led][parts - 1][128]
+  const uint32_t slot_bar0 = smem_addr(bars + 2 * MAX_STAGES);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + MAX_STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = blockIdx.x % plan.parts;
+  const int k_lo = part * plan.range, k_hi = min(K, k_lo + plan.range);
+  const int klen = k_hi - k_lo;                        // > 0 by construction
+  const int first_panel = blockIdx.x / plan.parts, panel_step = plan.blocks / plan.parts;
+  const int my_units = first_panel < plan.panels ? (plan.panels - 1 - first_panel) / panel_step + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < plan.stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
+    }
+    for (int i = 0; i < plan.led; ++i) mbar_init(slot_bar0 + 8 * i, 128 * (plan.parts - 1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (K & 31) {  // the tail of the last k-block is read but never copied: keep it finite
+    for (int i = threadIdx.x * 16; i < plan.stages * stage_bytes; i += THREADS * 16)
+      *reinterpret_cast<uint4*>(smem + i) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  if (plan.parts > 1) cluster_sync_all();  // every block of the cluster has its barriers ready
+
+  if (warp == CONSUMER_WARPS) {
+    // ---- producer: weights do not depend on the kernel before this one, so it starts at once ----
+    const uint32_t bytes_row = (uint32_t)klen * 2;
+    for (int u = 0; u < my_units; ++u) {
+      const int s = u % plan.stages;
+      if (u >= plan.stages) mbar_wait(empty0 + 8 * s, ((u / plan.stages) & 1) ^ 1, error_word, 1);
+      const int row0 = (first_panel + u * panel_step) * FPP;
+      const int rows_live = min(FPP, N - row0);  // per half for SwiGLU: gate rows, then up rows
+      if (lane == 0) mbar_expect_tx(full0 + 8 * s, bytes_row * rows_live * (ROWS / FPP));
+      __syncwarp();
+      if (lane < ROWS && (lane % FPP) < rows_live) {
+        const long row = row0 + (lane % FPP) + (lane / FPP) * up_offset;
+        bulk_copy(smem_addr(smem + (size_t)s * stage_bytes + lane * plan.pitch), W + row * ldw + k_lo, bytes_row,
+                  full0 + 8 * s);
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----------------------------------------------------------------------------------
+  const int g = lane >> 2, t = lane & 3;
+  pdl_wait();  // x comes from the kernel before this one
+  uint4 xg[XB], xh[XB];
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int i = 0; i < XB; ++i) {
+    const int k = 32 * (warp + CONSUMER_WARPS * i) + 8 * t;
+    const bool ok = k < klen;
+    xg[i] = (ok && g < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long)g * ldx + k_lo + k)) : zero;
+    xh[i] = (HI && ok && g + 8 < M) ? __ldg(reinterpret_cast<const uint4*>(x + (long)(g + 8) * ldx + k_lo + k)) : zero;
+  }
+  const int my_blocks = (klen + 31) / 32;  // k-blocks of this range; this warp has w, w+16, ...
+
+  for (int u = 0; u < my_units; ++u) {
+    const int s = u % plan.stages;
+    const int panel = first_panel + u * panel_step;
+    mbar_wait(full0 + 8 * s, (u / plan.stages) & 1, error_word, 2);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const unsigned char* base = smem + (size_t)s * stage_bytes + g * plan.pitch + 16 * t;
+#pragma unroll
+    for (int i = 0; i < XB; ++i) {
+      const int b = warp + CONSUMER_WARPS * i;
+      if (b < my_blocks) {
+        const uint4 w = *reinterpret_cast<const uint4*>(base + 64 * b);
+        mma_bf16(acc, xg[i].x, xh[i].x, xg[i].y, xh[i].y, w.x, w.y);
+        mma_bf16(acc, xg[i].z, xh[i].z, xg[i].w, xh[i].w, w.z, w.w);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);  // the stage may be refilled
+
+    // sum the warps' tiles (warp order), two buffers so that one barrier per unit is enough
+    float* rbuf = red + (size_t)(u & 1) * CONSUMER_WARPS * 4 * 32;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) rbuf[(warp * 4 + e) * 32 + lane] = acc[e];
+    consumer_sync();
+    if (threadIdx.x < 128) {  // thread = (e, lane) of the tile: token g + 8 * (e >> 1), row 2t + (e & 1)
+      const int e = threadIdx.x >> 5;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < CONSUMER_WARPS; ++w) v += rbuf[(w * 4 + e) * 32 + lane];
+      bool emit = true;
+      if (plan.parts > 1) {
+        const int leader = u % plan.parts, li = u / plan.parts;
+        if (part != leader) {
+          const int idx = part < leader ? part : part - 1;
+          const uint32_t dst = map_to_rank(smem_addr(slots + ((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x),
+                                           leader);
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(v) : "memory");
+          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                           map_to_rank(slot_bar0 + 8 * li, leader))
+                       : "memory");
+          emit = false;
+        } else {
+          const uint32_t bar = slot_bar0 + 8 * li;
+          if (!mbar_try_wait_cluster(bar, 0)) {
+            const long long start = clock64();
+            while (!mbar_try_wait_cluster(bar, 0)) {
+              if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                atomicExch(error_word, 3);
+                break;
+              }
+            }
+          }
+          const float own = v;
+          v = 0.f;
+          for (int p = 0; p < plan.parts; ++p) {
+            const int idx = p < leader ? p : p - 1;
+            v += p == leader ? own : slots[((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x];
+          }
+        }
+      }
+      // SwiGLU: rows 0..3 of the panel are gate rows, rows 4..7 the up rows of the same features,
+      // held two lanes further on
+      const float up = MODE == OUT_SWIGLU ? __shfl_down_sync(0xffffffffu, v, 2) : 0.f;
+      const int token = g + 8 * (e >> 1);
+      const int feature = panel * FPP + 2 * t + (e & 1);
+      if (emit && token < M && feature < N && (MODE != OUT_SWIGLU || t < 2)) {
+        float r = v;
+        if (MODE == OUT_SWIGLU) r = (r / (1.f + expf(-r))) * up;
+        if (MODE == OUT_F32)
+          reinterpret_cast<float*>(out)[(long)token * ldo + feature] = r;
+        else
+          reinterpret_cast<bf16*>(out)[(long)token * ldo + feature] = __float2bfloat16_rn(r);
+      }
+    }
+  }
+  // only now: a successor that starts earlier requests its own weights into L2 while this
+  // kernel is still streaming through it, and loses them again before it can use them
+  pdl_launch_dependents();
+}
+
+cudaError_t launch_stream(const void* kernel, int blocks, int cluster, size_t smem, cudaStream_t stream, void** args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (q3_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelExC(&cfg, kernel, args);
+}
+
+// How many clusters of `cluster` blocks (one block per SM, all of its shared memory) the device
+// runs at once; clusters live inside one GPC, so this can be less than SMs / cluster.
+int resident_clusters(const void* kernel, int cluster, int sm_count) {
+  if (cluster == 1) return sm_count;
+  static int cached[9] = {0};
+  if (!cached[cluster]) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count / cluster * cluster);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_LIMIT;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = -1;
+    }
+    cached[cluster] = n;
+  }
+  return cached[cluster];
+}
+
+// Ranges of K: as few as keep a range within what a warp's registers hold and the ring at two
+// stages or more; more only while that shortens the longest block's work (units x (range +
+// a fixed part worth 256 k-values)).
+bool make_plan(const void* kernel, int N, int K, int features_per_panel, int max_range, int sm_count, Plan* plan) {
+  const int panels = (N + features_per_panel - 1) / features_per_panel;
+  long best_cost = 0;
+  plan->parts = 0;
+  for (int parts = 1; parts <= 8; parts *= 2) {
+    int range = (K + parts - 1) / parts;
+    range = (range + 31) & ~31;
+    if (range > max_range) continue;
+    if ((long)(parts - 1) * range >= K) continue;  // an empty range
+    const int clusters = resident_clusters(kernel, parts, sm_count);
+    if (clusters < 1) continue;
+    const int groups = clusters < panels ? clusters : panels;  // clusters launched
+    const int units = (panels + groups - 1) / groups;
+    const int led = parts > 1 ? (units + parts - 1) / parts : 0;
+    if (led > MAX_LED) continue;
+    const int pitch = ((range * 2 + 127) & ~127) + 64;
+    int stages = (SMEM_LIMIT - RED_BYTES - led * (parts - 1) * 512) / (8 * pitch);
+    if (stages < 2) continue;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    const long cost = (long)units * (range + 256);
+    if (!plan->parts || cost < best_cost) {
+      best_cost = cost;
+      plan->parts = parts;
+      plan->range = range;
+      plan->pitch = pitch;
+      plan->stages = stages;
+      plan->blocks = groups * parts;
+      plan->panels = panels;
+      plan->led = led;
+    }
+  }
+  return plan->parts != 0;
+}
+
+template <int MODE, bool HI>
+int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, int M, int N, int K, int up_offset,
+           int sm_count, int only_large, int* error_word, cudaStream_t stream) {
+  const void* kernel = (const void*)gemm_stream_kernel<MODE, HI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    configured = true;
+  }
+  Plan plan;
+  if (!make_plan(kernel, N, K, MODE == OUT_SWIGLU ? 4 : 8, CONSUMER_WARPS * 32 * Blocks<HI>::value, sm_count, &plan))
+    return Q3_ERR_UNSUPPORTED;
+  // A block owns its SM, so kernels do not overlap at their ends: short products (few units
+  // per block) and products that need the exchange between blocks are faster on the kernel
+  // that streams through registers.
+  if (only_large && (plan.parts > 1 || plan.panels < 8 * plan.blocks)) return Q3_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)plan.stages * 8 * plan.pitch + RED_BYTES + (size_t)plan.led * (plan.parts - 1) * 512;
+  void* args[] = {&x, &ldx, &W, &ldw, &out, &ldo, &M, &N, &K, &up_offset, &plan, &error_word};
+  return launch_stream(kernel, plan.blocks, plan.parts, smem, stream, args) == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+int sm_count_of_current_device() {
+  static int count = 0;
+  if (!count) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count < 8)
+      count = 0;
+  }
+  return count;
+}
+
+}  // namespace
+
+// mode 0: out bf16 [M, N]; 1: out fp32 [M, N]; 2: W is [2 * N, K] with gate rows first and up
+// rows from row `N`, out bf16 [M, N] = silu(x W_gate^T) * (x W_up^T).
+// M <= 16; K a multiple of 8 and at most 40960 (20480 when M > 8); leading dimensions in
+// elements (ldx, ldw multiples of 8); x and W 16-byte aligned; anything else is refused as
+// unsupported.  only_large != 0: also refuse the products for which q3_gemm_small_m is the
+// faster kernel on a B200.  `error_word` is set non-zero if a bounded wait expired.
+Q3_EXPORT int q3_gemm_stream(int mode, const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M,
+                             int N, int K, int only_large, int* error_word, cudaStream_t stream) {
+  if (!x || !W || !out || !error_word || N < 1 || K < 1 || M < 0 || mode < 0 || mode > 2) return Q3_ERR_ARGUMENT;
+  if (M > 16 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return Q3_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return Q3_ERR_UNSUPPORTED;
+  if (M == 0) return Q3_OK;
+  const int sms = sm_count_of_current_device();
+  if (!sms) return Q3_ERR_LAUNCH;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  const int up = mode == OUT_SWIGLU ? N : 0;
+#define Q3_STREAM_CASE(MODE)                                                                                  \
+  return M > 8 ? launch<MODE, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, error_word, stream)          \
+               : launch<MODE, false>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, error_word, stream)
+  if (mode == OUT_BF16) Q3_STREAM_CASE(OUT_BF16);
+  if (mode == OUT_F32) Q3_STREAM_CASE(OUT_F32);
+  Q3_STREAM_CASE(OUT_SWIGLU);
+#undef Q3_STREAM_CASE
+}

@@ -87,6 +87,10 @@ _SIGNATURES = {
     "gemm_small_m": {
         "q3_gemm_small_m": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
+    "gemm_stream": {
+        "q3_gemm_stream": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p],
+    },
     "gemm_tcgen05": {
         "q3_gemm_tcgen05": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                             c_void_p],
@@ -117,6 +121,10 @@ class CudaOps:
         self.large_gemm = large_gemm
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
+        # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
+        # large ones, the register stream (csrc/gemm_small_m.cu) for the rest; "stream" -- the first
+        # for everything it supports; "registers" -- always the second
+        self.small_gemm = "auto"
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -335,8 +343,7 @@ class CudaOps:
             odt = out_dtype or x.dtype
             if out is None:
                 out = torch.empty((M, N), dtype=odt, device=x.device)
-            self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m", 1 if odt == torch.float32 else 0,
-                       _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K)
+            self._small_product(1 if odt == torch.float32 else 0, x, weight, out, M, N, K)
             return out
         if self.large_gemm == "tcgen05" and self._tcgen05_ok(x, weight):
             return self.linear_tcgen05(x, weight, out=out, out_dtype=out_dtype)
@@ -362,8 +369,8 @@ class CudaOps:
         err = getattr(self, "_err", None)
         if err is not None and int(err.item()) != 0:
             err.zero_()
-            raise KernelError("a bounded wait inside a tcgen05 kernel expired: the kernel gave up and its output "
-                              "is invalid")
+            raise KernelError("a bounded wait inside a kernel expired (tcgen05 product or attention, or the "
+                              "streaming product): the kernel gave up and its output is invalid")
 
     def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None):
         """``x @ weight^T`` on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).  ``mode=2``: SwiGLU with
@@ -386,6 +393,22 @@ class CudaOps:
 
     SMALL_M = 16
 
+    def _small_product(self, mode: int, x, weight, out, M, N, K) -> None:
+        """A product of at most 16 tokens: the streaming kernel (csrc/gemm_stream.cu), or the
+        register-streaming one (csrc/gemm_small_m.cu) for what the first refuses."""
+        if self.small_gemm != "registers":
+            self.launches += 1
+            code = self._get("gemm_stream", "q3_gemm_stream")(
+                mode, _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
+                int(self.small_gemm == "auto"), _ptr(self._error_word(x.device)), self._stream())
+            if code == 0:
+                return
+            self.launches -= 1
+            if code != 1:
+                _check(code, "gemm_stream")
+        self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m", mode, _ptr(x), x.stride(0), _ptr(weight),
+                   weight.stride(0), _ptr(out), out.stride(0), M, N, K)
+
     def _small_m_ok(self, x, weight) -> bool:
         return (x.dtype == torch.bfloat16 and x.shape[0] <= self.SMALL_M and x.shape[1] % 8 == 0
                 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1
@@ -397,8 +420,7 @@ class CudaOps:
         M, K = x.shape
         I = out.shape[1]
         if self._small_m_ok(x, gate_up_weight):
-            self._call("gemm_small_m", "q3_gemm_small_m", "gemm_small_m(swiglu)", 2, _ptr(x), x.stride(0),
-                       _ptr(gate_up_weight), gate_up_weight.stride(0), _ptr(out), out.stride(0), M, I, K)
+            self._small_product(2, x, gate_up_weight, out, M, I, K)
             return out
         if self.large_gemm != "library" and self._tcgen05_ok(x, gate_up_weight):
             tiles = -(-M // 128) * -(-I // 128)

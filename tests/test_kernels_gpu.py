@@ -465,10 +465,21 @@ def test_linear_bf16(ops, M, N, K):
     close(f32, want, torch.float32, "linear bf16 -> f32", f32_tol=1e-4)
 
 
+@pytest.fixture(params=["stream", "registers", "auto"])
+def small_gemm(ops, request):
+    """Both kernels for products of at most 16 tokens: the shared-memory stream and the older
+    register stream (which also takes what the first refuses)."""
+    before = ops.small_gemm
+    ops.small_gemm = request.param
+    yield request.param
+    ops.small_gemm = before
+    ops.raise_if_kernel_error()
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(2560, 2560), (6144, 2560), (2560, 9728), (2560, 4096), (301, 80), (160, 96),
-                                 (151936, 64), (24, 8), (17, 4096)])
-def test_gemm_small_m(ops, M, N, K):
+                                 (151936, 64), (24, 8), (17, 4096), (40, 20480), (40, 20488), (1000, 5128), (64, 40960), (8, 40968)])
+def test_gemm_small_m(ops, small_gemm, M, N, K):
     x = rand((M, K), torch.bfloat16, 54)
     w = rand((N, K), torch.bfloat16, 55, scale=0.05)
     assert ops._small_m_ok(x, w)
@@ -479,11 +490,28 @@ def test_gemm_small_m(ops, M, N, K):
     wide = rand((M, K + 8), torch.bfloat16, 56)
     close(ops.linear(wide[:, :K], w[: max(1, N // 2)]), wide[:, :K].float() @ w[: max(1, N // 2)].float().t(),
           torch.bfloat16, "strided", bf16_tol=1e-2)
+    # the same bits every time
+    first = ops.linear(x, w, out_dtype=torch.float32)
+    for _ in range(3):
+        assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), first)
+
+
+def test_gemm_stream_rows_do_not_depend_on_the_other_tokens(ops):
+    """A token's result is the same bits alone, among 8 and among 16 tokens."""
+    for N, K in [(2560, 2560), (2560, 9728), (304, 96)]:
+        x = rand((16, K), torch.bfloat16, 66)
+        w = rand((N, K), torch.bfloat16, 67, scale=0.05)
+        ops.small_gemm = "stream"
+        full = ops.linear(x, w, out_dtype=torch.float32)
+        for m in (1, 5, 8, 9):
+            assert torch.equal(ops.linear(x[:m], w, out_dtype=torch.float32), full[:m]), (N, K, m)
+    ops.small_gemm = "auto"
+    ops.raise_if_kernel_error()
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
-@pytest.mark.parametrize("I,K", [(9728, 2560), (112, 80), (160, 96), (24, 4096)])
-def test_gated_linear_small_m(ops, M, I, K):
+@pytest.mark.parametrize("I,K", [(9728, 2560), (112, 80), (160, 96), (24, 4096), (301, 2560), (6, 9728)])
+def test_gated_linear_small_m(ops, small_gemm, M, I, K):
     x = rand((M, K), torch.bfloat16, 57)
     w = rand((2 * I, K), torch.bfloat16, 58, scale=0.05)
     out = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
