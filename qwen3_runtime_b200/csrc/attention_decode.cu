@@ -16,10 +16,61 @@
 // to scratch (mid_o [seqs, nq, splits, D] fp32, mid_lse [seqs, nq, splits]); a second
 // kernel merges the splits (triton_decode.py:447-501).  Slices are cut at multiples of 64
 // keys counted from the first visible key, so an empty slice writes lse = -inf.
+#include <cuda.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
 namespace {
+
+// ---- TMA variant: page boxes instead of 16-byte copies ------------------------------------------
+// A 64-key tile of K (and of V) is fetched as boxes of [rows of one page] x [64 dims] through a
+// tensor map with the 128-byte swizzle, issued by the lanes of warp 0 in parallel and counted on
+// one mbarrier per stage.  A box asks memory for whole 128-byte lines of a page at once, which
+// keeps DRAM far busier than 16-byte copies spread over threads.  Tile layout: D/64 slabs of
+// [64 keys][128 bytes]; chunk c of key r of slab h sits at h*8192 + r*128 + ((c ^ (r & 7)) * 16).
+constexpr int MAX_STAGES = 4;
+constexpr long long WAIT_LIMIT_CYCLES = 400000000ll;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded; on expiry the error word is set and the caller carries on with whatever is there.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* error_word) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      if (error_word) atomicExch(error_word, 4);
+      return;
+    }
+  }
+}
+__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+template <int D, bool TMA> __device__ __forceinline__ int kv_off(int row, int chunk) {
+  if (TMA) return (chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+  return swz<D>(row, chunk);
+}
 
 // What the fused variant needs to make q, k and v of the newest token itself, from the raw
 // output of the q/k/v projection (row layout: nq q heads, nkv k heads, nkv v heads of D):
@@ -39,27 +90,81 @@ constexpr int TILE = 64;     // keys per pipeline stage
 constexpr int WARPS = 4;     // each takes 16 keys of a tile
 constexpr int THREADS = WARPS * 32;
 
+// ---- merge of the slices inside a thread-block cluster ---------------------------------------------
+// With `cluster_merge` the blocks of one (sequence, kv head) -- its slices -- are one cluster.
+// Each leaves its normalised partial result [G][D] and its log-sum-exp [G] in its own shared
+// memory; after a cluster barrier block r merges the r-th share of the G x D outputs, reading
+// every block's partials through distributed shared memory in slice order (the arithmetic of
+// decode_combine_kernel, so the bits are the same), and a second barrier keeps every block's
+// shared memory alive until all have read it.
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* local, uint32_t rank) {
+  uint32_t addr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+template <int D>
+__device__ __forceinline__ void cluster_merge_slices(const float* part_o, const float* part_lse, int G, int rank,
+                                                     int num_splits, bf16* __restrict__ out_row) {
+  cluster_barrier();
+  const int total = G * D;
+  const int share = (total + num_splits - 1) / num_splits;
+  const int hi = min(total, (rank + 1) * share);
+  for (int idx = rank * share + threadIdx.x; idx < hi; idx += blockDim.x) {
+    const int g = idx / D;
+    float mx = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, ld_cluster(part_lse + g, s));
+    float acc = 0.f, wsum = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ls = ld_cluster(part_lse + g, s);
+      if (ls == -INFINITY) continue;
+      const float w = exp2f(ls - mx);
+      wsum += w;
+      acc += w * ld_cluster(part_o + idx, s);
+    }
+    out_row[idx] = __float2bfloat16_rn(acc / wsum);
+  }
+  cluster_barrier();
+}
+
 // FUSED: `q` is the raw q/k/v projection; the block norms and rotates its own queries, and the
 // block whose slice holds the newest position also makes that token's key and value, writes
 // them to their page and patches them into its tile (q/k/v math as in rope_kv.cu, same order of
 // operations, so both ways give the same bits).  Nothing the block reads before pdl_wait() is
 // written by a kernel of the same step, so the first key tiles are in flight while the
 // projection before this kernel is still finishing.
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool TMA>
 __global__ void __launch_bounds__(THREADS)
 decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kpages,
                         const bf16* vpages, const int* __restrict__ block_table, int max_pages,
                         const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
-                        int num_splits, int stages, NewToken nt) {
+                        int num_splits, int stages, NewToken nt, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, int* __restrict__ error_word, int cluster_merge) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   unsigned char* q_s = smem;                  // [16][D] bf16
-  unsigned char* new_s = smem + 16 * D * 2;   // FUSED: the newest key, then the newest value, [2][D] bf16
-  unsigned char* kv_s = new_s + (FUSED ? 2 * D * 2 : 0);    // stages x (K tile, V tile)
+  unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile); 1024-byte aligned
+  unsigned char* new_s = kv_s + (size_t)stages * 2 * TILE_BYTES;  // FUSED: the newest key, then value, [2][D]
+  // after the last tile the ring is reused: the warps' results [WARPS][16][D] + [WARPS][16][2],
+  // then (cluster_merge) this slice's partial [16][D] and its log-sum-exp [16]
+  float* part_o = reinterpret_cast<float*>(kv_s) + WARPS * 16 * D + WARPS * 16 * 2;
+  float* part_lse = part_o + 16 * D;
 
+  if (TMA) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < stages; ++i) mbar_init(smem_u32(full_bar + i), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
   if (!FUSED) pdl_wait();  // keys and values of the newest token come from the kernel before this one
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int slot = blockIdx.z;                // index into the partial buffers
@@ -79,6 +184,13 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   const int* bt = block_table + (long)seq * max_pages;
 
   if (k_begin >= k_end) {  // nothing visible in this slice
+    if (cluster_merge) {
+      pdl_launch_dependents();
+      if (tid < G) part_lse[tid] = -INFINITY;
+      if (FUSED) pdl_wait();
+      cluster_merge_slices<D>(part_o, part_lse, G, split, num_splits, out + ((long)tok * nq + kvh * G) * D);
+      return;
+    }
     if (num_splits > 1 && tid < G)
       mid_lse[((long)slot * nq + kvh * G + tid) * num_splits + split] = -INFINITY;
     return;
@@ -109,6 +221,36 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     unsigned char* k_dst = kv_s + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* v_dst = k_dst + TILE_BYTES;
     const int base = k_begin + tile * TILE;
+    if (TMA) {
+      if (warp != 0) return;
+      // boxes of this tile: (page part j, slab h, K or V); a box holds `box_rows` keys of one page
+      const int box_rows = ps < TILE ? ps : TILE;
+      const int parts = TILE / box_rows;
+      const int boxes = parts * (D / 64) * 2;
+      const uint32_t bar = smem_u32(full_bar + stage);
+      int live_total = 0;
+      for (int b0 = 0; b0 < boxes; b0 += 32) {
+        const int b = b0 + lane;
+        const int j0 = base + (b / (2 * (D / 64))) * box_rows;
+        const bool live = b < boxes && j0 < k_end && j0 + box_rows > lo && bt[j0 / ps] >= 0;
+        live_total += __popc(__ballot_sync(0xffffffffu, live));
+      }
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)live_total * box_rows * 128);
+      __syncwarp();
+      for (int b0 = 0; b0 < boxes; b0 += 32) {
+        const int b = b0 + lane;
+        if (b >= boxes) break;
+        const int which = b & 1, h = (b >> 1) % (D / 64), j = b / (2 * (D / 64));
+        const int j0 = base + j * box_rows;
+        if (!(j0 < k_end && j0 + box_rows > lo)) continue;
+        const int page = bt[j0 / ps];
+        if (page < 0) continue;
+        const int y = (page * nkv + kvh) * ps + (j0 % ps);
+        unsigned char* dst = (which ? v_dst : k_dst) + h * (TILE * 128) + j * box_rows * 128;
+        tma_box(smem_u32(dst), which ? &map_v : &map_k, bar, h * 64, y);
+      }
+      return;
+    }
     const int chunk = tid % CHUNKS;
     for (int r0 = (tid / CHUNKS) * 8; r0 < TILE; r0 += ROWS_PER_PASS) {
       const int j0 = base + r0;
@@ -122,7 +264,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + i;
           const bool valid = j >= lo && j < k_end && j != skip;
-          const int off = swz<D>(r0 + i, chunk);
+          const int off = kv_off<D, false>(r0 + i, chunk);
           cp_async16(smem_u32(k_dst + off), kpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
           cp_async16(smem_u32(v_dst + off), vpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
         }
@@ -234,7 +376,11 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
 
   for (int tile = 0; tile < num_tiles; ++tile) {
-    if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
+    if (TMA) {
+      mbar_wait(smem_u32(full_bar + tile % stages), (tile / stages) & 1, error_word);
+    } else {
+      if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
+    }
     __syncthreads();
     {
       const int nxt = tile + stages - 1;
@@ -243,14 +389,31 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     }
     unsigned char* k_t = kv_s + (size_t)(tile % stages) * 2 * TILE_BYTES;
     unsigned char* v_t = k_t + TILE_BYTES;
-    if (FUSED && owner && tile == (p - k_begin) / TILE) {  // (uniform over the block)
-      const int r = p - k_begin - tile * TILE;
-      for (int c = tid; c < 2 * CHUNKS; c += THREADS) {
-        const int chunk = c % CHUNKS;
-        const uint4 v = *reinterpret_cast<const uint4*>(new_s + (c / CHUNKS) * D * 2 + chunk * 16);
-        *reinterpret_cast<uint4*>((c < CHUNKS ? k_t : v_t) + swz<D>(r, chunk)) = v;
+    {
+      const int base = k_begin + tile * TILE;
+      const bool patch = FUSED && owner && tile == (p - k_begin) / TILE;
+      // page boxes bring whole pages: values of keys outside [lo, k_end) are cleared, since a
+      // probability of zero does not silence a NaN (their scores are masked below)
+      const bool ragged = TMA && (base < lo || base + TILE > k_end);
+      if (patch || ragged) {  // (uniform over the block)
+        if (ragged) {
+          for (int c = tid; c < TILE * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, j = base + row;
+            if (j < lo || j >= k_end)
+              *reinterpret_cast<uint4*>(v_t + kv_off<D, TMA>(row, c % CHUNKS)) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        if (patch) {
+          const int r = p - base;
+          for (int c = tid; c < 2 * CHUNKS; c += THREADS) {
+            const int chunk = c % CHUNKS;
+            const uint4 v = *reinterpret_cast<const uint4*>(new_s + (c / CHUNKS) * D * 2 + chunk * 16);
+            *reinterpret_cast<uint4*>((c < CHUNKS ? k_t : v_t) + kv_off<D, TMA>(r, chunk)) = v;
+          }
+        }
+        if (TMA) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before the stage is refilled
+        __syncthreads();
       }
-      __syncthreads();
     }
     const int key0 = k_begin + tile * TILE + warp * 16;  // this warp's 16 keys
     if (key0 >= k_end) continue;                          // (uniform per warp)
@@ -262,7 +425,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t kb[4];
       const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-      ldmatrix_x4(kb, smem_u32(k_t + swz<D>(row, 2 * ks + ((lane >> 3) & 1))));
+      ldmatrix_x4(kb, smem_u32(k_t + kv_off<D, TMA>(row, 2 * ks + ((lane >> 3) & 1))));
       mma_bf16(s[0], qa[ks], kb[0], kb[1]);
       mma_bf16(s[1], qa[ks], kb[2], kb[3]);
     }
@@ -313,7 +476,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     for (int i = 0; i < D / 16; ++i) {
       uint32_t vb[4];
       const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-      ldmatrix_x4_trans(vb, smem_u32(v_t + swz<D>(row, 2 * i + (lane >> 4))));
+      ldmatrix_x4_trans(vb, smem_u32(v_t + kv_off<D, TMA>(row, 2 * i + (lane >> 4))));
       mma_bf16(o[2 * i], pa, vb[0], vb[1]);
       mma_bf16(o[2 * i + 1], pa, vb[2], vb[3]);
     }
@@ -321,7 +484,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
 
   // ---- merge the 4 warps ------------------------------------------------------------------
   pdl_launch_dependents();
-  cp_async_wait<0>();
+  if (!TMA) cp_async_wait<0>();
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -365,11 +528,15 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     const float val = acc / l;
     if (num_splits == 1) {
       out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(val);
+    } else if (cluster_merge) {
+      part_o[idx] = val;
+      if (d == 0) part_lse[g] = m * scale_log2 + log2f(l);
     } else {
       mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = val;
       if (d == 0) mid_lse[((long)slot * nq + head) * num_splits + split] = m * scale_log2 + log2f(l);
     }
   }
+  if (cluster_merge) cluster_merge_slices<D>(part_o, part_lse, G, split, num_splits, out + ((long)tok * nq + kvh * G) * D);
 }
 
 // out[token of seq, head, :] = sum_s w_s * mid_o[s] / sum_s w_s,  w_s = 2^(lse_s - max lse)
@@ -397,28 +564,98 @@ __global__ void decode_combine_kernel(const float* __restrict__ mid_o, const flo
   }
 }
 
-template <int D, bool FUSED>
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Pages as a matrix [rows of all pages and kv heads][D]; a box is [box_rows][64 dims], swizzled.
+bool page_map(CUtensorMap* map, const void* pages, long num_rows_kv, int D, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_rows_kv};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t es[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, bool FUSED, bool TMA>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
-                  int num_splits, const NewToken& nt, cudaStream_t stream) {
-  const int stages = 2;
+                  int num_splits, const NewToken& nt, long num_rows_kv, int* error_word, int cluster_merge,
+                  cudaStream_t stream) {
+  static int stages = 0;
+  if (!stages) {
+    const char* v = getenv("Q3_DECODE_STAGES");
+    stages = v ? atoi(v) : 2;
+    if (stages < 2 || stages > MAX_STAGES || (!TMA && stages > 3)) stages = 2;
+  }
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
-  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
+  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4 + 16 * D * 4 + 16 * 4;
   const size_t smem = 16 * D * 2 + (FUSED ? 2 * D * 2 : 0) + (pipe > merge ? pipe : merge);
+  if (smem > 227 * 1024) return Q3_ERR_UNSUPPORTED;
+  cluster_merge = cluster_merge && num_splits > 1 && num_splits <= 8;
+  if (num_splits > 1 && !cluster_merge && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return Q3_ERR_LAUNCH;
     configured = true;
   }
+  CUtensorMap map_k, map_v;
+  memset(&map_k, 0, sizeof map_k);
+  memset(&map_v, 0, sizeof map_v);
+  if (TMA) {
+    const int box_rows = ps < TILE ? ps : TILE;
+    if (!page_map(&map_k, kpages, num_rows_kv, D, box_rows) || !page_map(&map_v, vpages, num_rows_kv, D, box_rows))
+      return Q3_ERR_LAUNCH;
+  }
   dim3 grid(num_splits, nkv, num_seqs);
-  if (launch_pdl(decode_attention_kernel<D, FUSED>, grid, dim3(THREADS), smem, stream, q, q_stride, kpages, vpages,
-                 block_table, max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps,
-                 scale * 1.4426950408889634f, window, num_splits, stages, nt) != cudaSuccess)
-    return Q3_ERR_LAUNCH;
-  if (num_splits > 1) {
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_merge) {
+      attr[n].id = cudaLaunchAttributeClusterDimension;
+      attr[n].val.clusterDim.x = num_splits;
+      attr[n].val.clusterDim.y = 1;
+      attr[n].val.clusterDim.z = 1;
+      ++n;
+    }
+    if (q3_pdl_enabled()) {
+      attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n].val.programmaticStreamSerializationAllowed = 1;
+      ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED, TMA>, q, q_stride, kpages, vpages, block_table,
+                           max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps, scale_log2,
+                           window, num_splits, stages, nt, map_k, map_v, error_word, cluster_merge) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
+  }
+  if (num_splits > 1 && !cluster_merge) {
     dim3 cgrid(nq, num_seqs);
     if (launch_pdl(decode_combine_kernel, cgrid, dim3(D < 128 ? D : 128), 0, stream, (const float*)mid_o,
                    (const float*)mid_lse, cu_seqlens, seq_list, out, nq, D, num_splits) != cudaSuccess)
@@ -431,18 +668,29 @@ template <bool FUSED>
 int dispatch_decode(const void* q, int q_stride, const void* kpages, const void* vpages, const int* block_table,
                     int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
                     float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
-                    int window, int num_splits, const NewToken& nt, cudaStream_t stream) {
+                    int window, int num_splits, const NewToken& nt, long num_rows_kv, int* error_word,
+                    int cluster_merge, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
-  if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
   if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
   if (num_seqs == 0) return Q3_OK;
   if (num_seqs > 65535 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
-#define Q3_DECODE_CASE(DIM)                                                                                     \
-  case DIM:                                                                                                     \
-    return launch_decode<DIM, FUSED>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages,        \
-                                     block_table, max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o,  \
-                                     mid_lse, num_seqs, nq, nkv, ps, scale, window, num_splits, nt, stream)
+  // page boxes: pages of 8, 16, 32 keys or a multiple of 64, all rows addressable with an int
+  const bool tma = num_rows_kv > 0 && num_rows_kv < (1L << 31) && error_word &&
+                   (ps == 8 || ps == 16 || ps == 32 || ps % 64 == 0) &&
+                   (((uintptr_t)kpages | (uintptr_t)vpages) & 15) == 0;
+#define Q3_DECODE_CASE(DIM)                                                                                      \
+  case DIM:                                                                                                      \
+    return tma ? launch_decode<DIM, FUSED, true>((const bf16*)q, q_stride, (const bf16*)kpages,                  \
+                                                 (const bf16*)vpages, block_table, max_pages, kv_lens,           \
+                                                 cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs, nq, \
+                                                 nkv, ps, scale, window, num_splits, nt, num_rows_kv,            \
+                                                 error_word, cluster_merge, stream)                              \
+               : launch_decode<DIM, FUSED, false>((const bf16*)q, q_stride, (const bf16*)kpages,                 \
+                                                  (const bf16*)vpages, block_table, max_pages, kv_lens,          \
+                                                  cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs,    \
+                                                  nq, nkv, ps, scale, window, num_splits, nt, num_rows_kv,       \
+                                                  error_word, cluster_merge, stream)
   switch (D) {
     Q3_DECODE_CASE(64);
     Q3_DECODE_CASE(128);
@@ -459,15 +707,22 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
 // kv_lens / cu_seqlens / block_table rows), or sequences 0..num_seqs-1 when it is null.
 // Scratch: mid_o needs num_seqs*nq*num_splits*D floats and mid_lse num_seqs*nq*num_splits
 // floats when num_splits > 1 (both may be null otherwise).  head_dim 64, 128 or 256;
-// group size nq/nkv at most 16; bfloat16 only.
+// group size nq/nkv at most 16; bfloat16 only.  num_rows_kv: rows of D in each of kpages and
+// vpages (pages x kv heads x page size); when it is given (> 0) together with `error_word`
+// (a device int that is set non-zero if a bounded wait expires) and the page size is 8, 16, 32
+// or a multiple of 64, keys and values are fetched as page boxes by TMA, else by 16-byte copies.
+// cluster_merge != 0 and 2..8 slices: the slices of a sequence and kv head run as one thread-block
+// cluster and merge through distributed shared memory (mid_o / mid_lse are not used and may be
+// null); otherwise the merge is a second kernel over the scratch.
 Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void* kpages, const void* vpages,
                                         const int* block_table, int max_pages, const int* kv_lens,
                                         const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                         float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
-                                        int window, int num_splits, cudaStream_t stream) {
+                                        int window, int num_splits, long num_rows_kv, int* error_word,
+                                        int cluster_merge, cudaStream_t stream) {
   return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                 out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
-                                stream);
+                                num_rows_kv, error_word, cluster_merge, stream);
 }
 
 // The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the
@@ -481,14 +736,16 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
                                               float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
                                               float scale, int window, int num_splits, const float* q_w,
                                               const float* k_w, float eps, const float* cos_t, const float* sin_t,
-                                              int max_pos, cudaStream_t stream) {
+                                              int max_pos, long num_rows_kv, int* error_word, int cluster_merge,
+                                              cudaStream_t stream) {
   if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w)) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
                          (uintptr_t)cos_t | (uintptr_t)sin_t;
   if (bits & 15) return Q3_ERR_UNSUPPORTED;
   NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos};
   return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
-                               out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt, stream);
+                               out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
+                               num_rows_kv, error_word, cluster_merge, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -558,5 +815,5 @@ Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, co
   float* mid_lse = scratch + partials * D; // [num_seqs, nq, num_splits]
   return q3_paged_attention_decode(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens,
                                    seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window,
-                                   num_splits, stream);
+                                   num_splits, 0, nullptr, 0, stream);
 }

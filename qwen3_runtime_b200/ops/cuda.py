@@ -65,11 +65,11 @@ _SIGNATURES = {
     "attention_decode": {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_float, c_int, c_int, c_void_p],
+                                      c_float, c_int, c_int, ctypes.c_long, c_void_p, c_int, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
-                                            c_void_p, c_void_p, c_int, c_void_p],
+                                            c_void_p, c_void_p, c_int, ctypes.c_long, c_void_p, c_int, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -121,6 +121,10 @@ class CudaOps:
         self.large_gemm = large_gemm
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
+        # Two variants of the split-KV kernel that are correct and tested but measured slower inside a
+        # whole decode step on a B200 (batch 8, context 4096: 3.36 ms and 3.48 ms against 3.19 ms), so off:
+        self.decode_page_boxes = False      # True: keys and values as TMA page boxes instead of 16-byte copies
+        self.decode_cluster_merge = False   # True: up to 8 slices merge inside a thread-block cluster
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
         # large ones, the register stream (csrc/gemm_small_m.cu) for the rest; "stream" -- the first
         # for everything it supports; "registers" -- always the second
@@ -305,10 +309,14 @@ class CudaOps:
             max_kv_len = min(max_kv_len, int(window) + 63)
         splits = num_splits or self.decode_splits(num_seqs, num_kv_heads, max_kv_len)
         mid_o = mid_lse = None
-        if splits > 1:
+        cluster = int(self.decode_cluster_merge and 1 < splits <= 8)
+        if splits > 1 and not cluster:
             mid_o = torch.empty((num_seqs, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
             mid_lse = torch.empty((num_seqs, num_heads, splits), dtype=torch.float32, device=out.device)
-        self.launches += 1 if splits > 1 else 0  # the merge kernel
+        self.launches += 1 if splits > 1 and not cluster else 0  # the merge kernel
+        # rows of head_dim in the page tensors: lets the kernel fetch page boxes by TMA
+        kv_rows = k_pages.shape[0] * num_kv_heads * page_size if self.decode_page_boxes else 0
+        err = _ptr(self._error_word(out.device))
         if new_token is not None:
             cos, sin = new_token["cos"], new_token["sin"]
             self._call("attention_decode", "q3_paged_attention_decode_fused", "paged_attention_decode_fused",
@@ -316,12 +324,13 @@ class CudaOps:
                        _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                        num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
                        splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
-                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0)
+                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, kv_rows, err, cluster)
             return out
         self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
-                   num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits)
+                   num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
+                   kv_rows, err, cluster)
         return out
 
     # ---- matrix products ----------------------------------------------------------------

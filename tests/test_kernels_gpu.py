@@ -348,10 +348,23 @@ def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list
     return out
 
 
+@pytest.fixture(params=["page boxes, cluster merge", "16-byte copies, cluster merge", "16-byte copies, merge kernel"])
+def decode_loader(ops, request):
+    """The split-KV kernel fetches keys and values as TMA page boxes where the page size allows it
+    (8, 16, 32, multiples of 64) or with 16-byte copies, and merges up to 8 slices inside a
+    thread-block cluster or (always for more slices) with a second kernel."""
+    before = ops.decode_page_boxes, ops.decode_cluster_merge
+    ops.decode_page_boxes = request.param.startswith("page boxes")
+    ops.decode_cluster_merge = "cluster" in request.param
+    yield request.param
+    ops.decode_page_boxes, ops.decode_cluster_merge = before
+    ops.raise_if_kernel_error()
+
+
 @pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 16), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
-                                          (14, 2, 64, 3), (40, 8, 128, 64)])
-@pytest.mark.parametrize("splits", [None, 1, 3, 8])
-def test_decode_attention_split_kv(ops, nq, nkv, D, ps, splits):
+                                          (14, 2, 64, 3), (40, 8, 128, 64), (4, 2, 128, 128), (16, 4, 256, 8)])
+@pytest.mark.parametrize("splits", [None, 1, 3, 8, 11])
+def test_decode_attention_split_kv(ops, decode_loader, nq, nkv, D, ps, splits):
     lens = [1, 63, 64, 65, 700, 129, 2, 1000]
     pr = decode_problem(nq, nkv, D, ps, lens, 80)
     want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16)
@@ -364,9 +377,9 @@ def test_decode_attention_split_kv(ops, nq, nkv, D, ps, splits):
 
 
 @pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 64), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
-                                          (14, 2, 64, 3)])
+                                          (14, 2, 64, 3), (32, 8, 128, 16)])
 @pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False), (False, False)])
-def test_decode_attention_makes_the_newest_token_itself(ops, nq, nkv, D, ps, norm, rotate):
+def test_decode_attention_makes_the_newest_token_itself(ops, decode_loader, nq, nkv, D, ps, norm, rotate):
     """One kernel (per-head norm, rotation, cache write, attention) against the two kernels it
     replaces: the same bits in the output and in the pages, for every split count and window."""
     lens = [1, 63, 64, 65, 700, 129, 2, 1000]
@@ -401,7 +414,7 @@ def test_decode_attention_makes_the_newest_token_itself(ops, nq, nkv, D, ps, nor
         assert not torch.equal(one["k"], pr["k"])
 
 
-def test_decode_attention_far_key_poison_and_subset(ops):
+def test_decode_attention_far_key_poison_and_subset(ops, decode_loader):
     nq, nkv, D, ps = 32, 8, 128, 16
     lens = [900, 333, 64]
     pr = decode_problem(nq, nkv, D, ps, lens, 81)
