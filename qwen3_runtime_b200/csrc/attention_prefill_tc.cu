@@ -4,20 +4,27 @@
 // bfloat16, head_dim 128, group size a divisor of 128, page size 8/16/32/64, no window; the
 // mma.sync kernel of attention_prefill.cu serves everything else.
 //
-// Work item: (sequence, kv head, block of 128 rows); rows are the (query token, head of the
-// group) pairs in token-major order, so one 3-D TMA box [128/G tokens, G heads, 64] is the Q
-// tile and the group's heads share every K/V tile.  Keys come in tiles of 64 (64/page_size
-// pages, one TMA box per page and half of D).  Six warps:
-//   warp 0           : TMA producer (Q once, then K and V tiles through 4-stage rings; the
-//                      lanes issue a tile's page boxes side by side);
-//   warp 1, one lane : MMA issuer.  Order: S_0, S_1, then per tile j: P_j ready -> PV_j,
-//                      S_{j+2}.  S has two TMEM buffers, so the tensor core computes S_{j+1}
-//                      and PV_{j-1} while the softmax warps work on tile j;
-//   warps 2..5       : softmax, one thread per row: reads S from TMEM, masks, online softmax
-//                      in fp32 (exp2, scale folded in), writes P (bf16) to shared memory (two
-//                      buffers) in the swizzled K-major layout that the PV MMA reads; O stays in
-//                      TMEM (the MMAs accumulate into it) and is rescaled there only when a
-//                      row's maximum has grown by more than 2^8; finally stores O / l.
+// Work item: (sequence, kv head, two consecutive blocks of 128 rows, A and B); rows are the
+// (query token, head of the group) pairs in token-major order, so one 3-D TMA box
+// [128/G tokens, G heads, 64] is half a Q tile and the group's heads share every K/V tile.  Keys
+// come in tiles of 64 (64/page_size pages, one TMA box per page and half of D), and each tile
+// is used by both row blocks.  Per 64-key tile a row block's chain is long (TMEM load, exp2
+// on the special-function unit, shared-memory stores, fences, barrier round trips) and
+// leaves the tensor core and the exp2 unit idle most of the time; two blocks in flight hide
+// each other's chain.  Ten warps:
+//   warp 0           : TMA producer (Q of both blocks once, then K and V tiles through 3-stage
+//                      rings; the lanes issue a tile's page boxes side by side);
+//   warp 1, one lane : MMA issuer.  Order: S_A0, S_B0, S_A1, S_B1, then per tile j:
+//                      P_Aj ready -> PV_Aj, S_A(j+2); P_Bj ready -> PV_Bj, S_B(j+2).  S has two
+//                      TMEM buffers per block, so the tensor core works for one block while
+//                      the other block's softmax runs;
+//   warps 2..5, 6..9 : softmax of block A and of block B, one thread per row: reads S from
+//                      TMEM, masks, online softmax in fp32 (exp2, scale folded in), writes P
+//                      (bf16) to shared memory (two buffers per block) in the swizzled K-major
+//                      layout that the PV MMA reads; O stays in TMEM (the MMAs accumulate into
+//                      it) and is rescaled there only when a row's maximum has grown by more
+//                      than 2^8; finally stores O / l.
+// Tensor memory: all 512 columns, per block S0 [0,64), S1 [64,128), O [128,256).
 // V is the B operand of PV in MN-major form (rows = keys): descriptor with the halves of D
 // 8 KB apart (leading offset) and 8-key groups 1 KB apart (stride offset); 16 keys = 2 KB.
 // Keys past a block's last position are zeroed in shared memory before PV (stale or poisoned
@@ -32,14 +39,15 @@ namespace {
 constexpr int D = 128;
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 32 KB: two halves of [128 rows][128 B]
 constexpr int KV_BYTES = BLOCK_N * D * 2;       // 16 KB: two halves of [64 rows][128 B]
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB: [128 rows][128 B]
-constexpr int KV_STAGES = 4;                    // key tiles and value tiles in flight
-constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 2 * P_BYTES + 1024;
-constexpr int TMEM_COLS = 256;                  // S0 [0,64), S1 [64,128), PV [128,256)
+constexpr int KV_STAGES = 3;                    // key tiles and value tiles in flight
+constexpr int SMEM_BYTES = 2 * Q_BYTES + 2 * KV_STAGES * KV_BYTES + 4 * P_BYTES + 1024;
+constexpr int TMEM_COLS = 512;                  // per row block: S0 [0,64), S1 [64,128), O [128,256)
+constexpr int TMEM_BLOCK = 256;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
@@ -130,8 +138,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 enum { BAR_Q = 0, BAR_K_FULL = 1, BAR_K_EMPTY = BAR_K_FULL + KV_STAGES, BAR_V_FULL = BAR_K_EMPTY + KV_STAGES,
-       BAR_V_EMPTY = BAR_V_FULL + KV_STAGES, BAR_S_FULL = BAR_V_EMPTY + KV_STAGES, BAR_P_FULL = BAR_S_FULL + 2,
-       BAR_PV_FULL = BAR_P_FULL + 1, NUM_BARS = BAR_PV_FULL + 1 };
+       BAR_V_EMPTY = BAR_V_FULL + KV_STAGES, BAR_S_FULL = BAR_V_EMPTY + KV_STAGES,  // [block][buffer]
+       BAR_P_FULL = BAR_S_FULL + 4, BAR_PV_FULL = BAR_P_FULL + 2, NUM_BARS = BAR_PV_FULL + 2 };
 
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -141,30 +149,31 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                             float scale_log2, int skip_single, int* __restrict__ error_word) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;                         // [2 halves][128 rows][128 B]
-  unsigned char* k_s = q_s + Q_BYTES;                // KV_STAGES x [2 halves][64 rows][128 B]
+  unsigned char* q_s = base;                         // 2 blocks x [2 halves][128 rows][128 B]
+  unsigned char* k_s = q_s + 2 * Q_BYTES;            // KV_STAGES x [2 halves][64 rows][128 B]
   unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;   // KV_STAGES x [2 halves][64 rows][128 B]
-  unsigned char* p_s = v_s + KV_STAGES * KV_BYTES;   // 2 buffers x [128 rows][128 B]
+  unsigned char* p_s = v_s + KV_STAGES * KV_BYTES;   // 2 blocks x 2 buffers x [128 rows][128 B]
   __shared__ __align__(8) unsigned long long bars[NUM_BARS];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ int s_item[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvh = blockIdx.y;
+  // heavy items first over the whole grid: all kv heads of the heaviest item, then the next ...
+  const int kvh = blockIdx.x % nkv;
   const int G = nq / nkv;
   const uint32_t bar0 = smem_addr(&bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
   if (tid == 0) {
     abort_flag = 0;
-    // heavy blocks (late rows of long prompts) first: walk the work list from its end
+    // heavy work (late rows of long prompts) first: walk the work list from its end
     int acc = 0, found = -1, rb = 0;
-    const int w = num_work - 1 - (int)blockIdx.x;
+    const int w = num_work - 1 - (int)(blockIdx.x / nkv);
     for (int s = 0; s < num_seqs; ++s) {
       const int ql = cu_seqlens[s + 1] - cu_seqlens[s];
       if (ql <= 0 || (skip_single && ql == 1)) continue;
-      const int nb = (ql * G + BLOCK_M - 1) / BLOCK_M;
+      const int nb = ((ql * G + BLOCK_M - 1) / BLOCK_M + 1) / 2;  // pairs of row blocks
       if (w < acc + nb) {
         found = s;
         rb = w - acc;
@@ -181,9 +190,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       mbar_init(bar(BAR_V_FULL + i), 1);
       mbar_init(bar(BAR_V_EMPTY + i), 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(bar(BAR_S_FULL + i), 1);
-    mbar_init(bar(BAR_P_FULL), 128);
-    mbar_init(bar(BAR_PV_FULL), 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(BAR_S_FULL + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_P_FULL + i), 128);
+      mbar_init(bar(BAR_PV_FULL + i), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -199,23 +210,35 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   const int seq = s_item[0];
 
   if (seq >= 0) {
-    const int row0 = s_item[1] * BLOCK_M;
     const int tok0 = cu_seqlens[seq];
     const int q_len = cu_seqlens[seq + 1] - tok0;
     const int kv_len = kv_lens[seq];
     const int rows = q_len * G;
     const int base_pos = kv_len - q_len;
-    const int last_row = min(rows, row0 + BLOCK_M) - 1;
-    const int p_max = base_pos + last_row / G;
-    const int num_tiles = p_max / BLOCK_N + 1;
+    // row blocks A and B of this item; B may not exist (odd number of blocks)
+    int row0[2], p_max[2], tiles[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      row0[x] = (2 * s_item[1] + x) * BLOCK_M;
+      const bool live = row0[x] < rows;
+      const int last_row = min(rows, row0[x] + BLOCK_M) - 1;
+      p_max[x] = live ? base_pos + last_row / G : -1;
+      tiles[x] = live ? p_max[x] / BLOCK_N + 1 : 0;
+    }
+    const int num_tiles = max(tiles[0], tiles[1]);  // B lies after A, so this is B's count when B exists
+    const int p_last = max(p_max[0], p_max[1]);
     const int* bt = block_table + (long)seq * max_pages;
     const int pages_per_tile = BLOCK_N / ps;
 
     if (warp == 0) {  // ---- TMA producer: lane 0 waits and arms the barriers, the lanes share the loads ----
       if (lane == 0) {
-        mbar_expect_tx(bar(BAR_Q), Q_BYTES);
-        tma_load_3d(smem_addr(q_s), &tmap_q, bar(BAR_Q), 0, kvh * G, tok0 + row0 / G);
-        tma_load_3d(smem_addr(q_s) + Q_BYTES / 2, &tmap_q, bar(BAR_Q), 64, kvh * G, tok0 + row0 / G);
+        mbar_expect_tx(bar(BAR_Q), tiles[1] ? 2 * Q_BYTES : Q_BYTES);
+        for (int x = 0; x < 2; ++x) {
+          if (!tiles[x]) continue;
+          const uint32_t dst = smem_addr(q_s) + x * Q_BYTES;
+          tma_load_3d(dst, &tmap_q, bar(BAR_Q), 0, kvh * G, tok0 + row0[x] / G);
+          tma_load_3d(dst + Q_BYTES / 2, &tmap_q, bar(BAR_Q), 64, kvh * G, tok0 + row0[x] / G);
+        }
       }
       // a tile is 64 / ps pages x 2 halves of D: one box per lane (small boxes are slow to issue
       // one after another from a single thread)
@@ -228,7 +251,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         int page = -1;
         if (my_page < pages_per_tile) {
           const int pi = j * pages_per_tile + my_page;
-          if (pi < max_pages && pi * ps <= p_max) page = bt[pi];
+          if (pi < max_pages && pi * ps <= p_last) page = bt[pi];
         }
         const uint32_t boxes = __popc(__ballot_sync(0xffffffffu, page >= 0));
         const uint32_t bytes = boxes * (uint32_t)ps * 128u;
@@ -255,50 +278,59 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       if (lane == 0) {  // ---- MMA issuer -----------------------------------------------------------
         constexpr uint32_t idesc_s = idesc_bf16(BLOCK_M, BLOCK_N, 0);   // S = Q K^T: N = 64 keys
         constexpr uint32_t idesc_pv = idesc_bf16(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
-        const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s);
-        auto issue_s = [&](int j) -> bool {  // S_j into TMEM buffer j & 1
+        const uint32_t p_addr = smem_addr(p_s);
+        // S_j of block x into its TMEM buffer j & 1; the key tile is released by its last user
+        auto issue_s = [&](int x, int j) -> bool {
           const int st = j % KV_STAGES, sbuf = j & 1;
           if (!mbar_wait(bar(BAR_K_FULL + st), (j / KV_STAGES) & 1, &abort_flag)) return false;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t k_addr = smem_addr(k_s) + st * KV_BYTES;
+          const uint32_t q_addr = smem_addr(q_s) + x * Q_BYTES;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t half = (k >> 2), sub = (k & 3) * 2;  // 4 steps of 32 bytes per 64-wide half
-            umma(tmem + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
+            umma(tmem + x * TMEM_BLOCK + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
                  desc_kmajor(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
           }
-          umma_commit(bar(BAR_K_EMPTY + st));  // the key tile may be overwritten
-          umma_commit(bar(BAR_S_FULL + sbuf)); // S_j is in TMEM
+          const bool last_user = x == 1 || j >= tiles[1];
+          if (last_user) umma_commit(bar(BAR_K_EMPTY + st));  // the key tile may be overwritten
+          umma_commit(bar(BAR_S_FULL + 2 * x + sbuf));        // S_j is in TMEM
           return true;
         };
         bool ok = mbar_wait(bar(BAR_Q), 0, &abort_flag);
-        if (ok) ok = issue_s(0);
-        if (ok && num_tiles > 1) ok = issue_s(1);
+        for (int j = 0; j < 2 && ok; ++j)
+          for (int x = 0; x < 2 && ok; ++x)
+            if (j < tiles[x]) ok = issue_s(x, j);
         for (int j = 0; j < num_tiles && ok; ++j) {
           const int st = j % KV_STAGES, pbuf = j & 1;
-          ok = mbar_wait(bar(BAR_P_FULL), j & 1, &abort_flag);  // P_j written, S_j and PV_{j-1} consumed
-          if (!ok) break;
-          ok = mbar_wait(bar(BAR_V_FULL + st), (j / KV_STAGES) & 1, &abort_flag);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
+          for (int x = 0; x < 2 && ok; ++x) {
+            if (j >= tiles[x]) continue;
+            ok = mbar_wait(bar(BAR_P_FULL + x), j & 1, &abort_flag);  // P_j written, S_j and PV_{j-1} consumed
+            if (!ok) break;
+            ok = mbar_wait(bar(BAR_V_FULL + st), (j / KV_STAGES) & 1, &abort_flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
 #pragma unroll
-          for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
-            umma(tmem + 2 * BLOCK_N, desc_kmajor(p_addr + pbuf * P_BYTES) + 2 * k,
-                 desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2),
-                 idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          umma_commit(bar(BAR_V_EMPTY + st));
-          umma_commit(bar(BAR_PV_FULL));
-          if (j + 2 < num_tiles) ok = issue_s(j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
+            for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
+              umma(tmem + x * TMEM_BLOCK + 2 * BLOCK_N, desc_kmajor(p_addr + (2 * x + pbuf) * P_BYTES) + 2 * k,
+                   desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            const bool last_user = x == 1 || j >= tiles[1];
+            if (last_user) umma_commit(bar(BAR_V_EMPTY + st));
+            umma_commit(bar(BAR_PV_FULL + x));
+            if (j + 2 < tiles[x]) ok = issue_s(x, j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
+          }
         }
       }
-    } else {  // ---- softmax: one thread per row ------------------------------------------------------
+    } else {  // ---- softmax: one thread per row; warps 2..5 block A, warps 6..9 block B ---------------
+      const int x = (warp - 2) >> 2;
       const int quarter = warp & 3;
       const int r = quarter * 32 + lane;  // row of the tile = TMEM lane
-      const int R = row0 + r;
+      const int R = row0[x] + r;
       const bool row_ok = R < rows;
       const int pos = row_ok ? base_pos + R / G : -1;
-      const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+      const int my_tiles = tiles[x];
+      const uint32_t lane_base = tmem + x * TMEM_BLOCK + ((uint32_t)(quarter * 32) << 16);
       const uint32_t o_addr = lane_base + 2 * BLOCK_N;
       // O stays in TMEM and the MMAs accumulate into it.  The reference point of the exponentials
       // (m_ref) is only moved when a row's maximum exceeds it by more than 2^8 after scaling; then
@@ -307,10 +339,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const float slack = 8.f / scale_log2;
       float m_ref = -INFINITY, l_run = 0.f;
       bool ok = true;
-      for (int j = 0; j < num_tiles && ok; ++j) {
+      for (int j = 0; j < my_tiles && ok; ++j) {
         const int st = j & 1;             // S buffer and P buffer of this tile
         const int vst = j % KV_STAGES;    // its value tile
-        ok = mbar_wait(bar(BAR_S_FULL + st), (j >> 1) & 1, &abort_flag);
+        ok = mbar_wait(bar(BAR_S_FULL + 2 * x + st), (j >> 1) & 1, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t sa[32], sb[32];
@@ -345,7 +377,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
         float sums[4] = {0.f, 0.f, 0.f, 0.f};
         // probabilities, rounded to bf16 as the MMA will see them, into the swizzled P tile
-        unsigned char* p_row = p_s + st * P_BYTES + r * 128;  // buffer j & 1: PV_{j-1} may still read the other
+        unsigned char* p_row = p_s + (2 * x + st) * P_BYTES + r * 128;  // buffer j & 1: PV_{j-1} may still read the other
         const float neg = -m_use * scale_log2;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -364,7 +396,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         // PV_{j-1} must be finished before P_j is signalled: it keeps this barrier from running a
         // phase ahead of the waiters, and O must be at rest if it has to be rescaled
         if (j > 0) {
-          ok = mbar_wait(bar(BAR_PV_FULL), (j - 1) & 1, &abort_flag);
+          ok = mbar_wait(bar(BAR_PV_FULL + x), (j - 1) & 1, &abort_flag);
           if (!ok) break;
           if (rescale) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -389,12 +421,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           }
         }
-        // keys of this tile past the block's last position: zero their value rows before PV reads them
-        if (key0 + BLOCK_N - 1 > p_max) {
+        // keys of this tile past the item's last position hold whatever the page held: zero their
+        // value rows before PV reads them (both blocks do, each before its own PV; keys between the
+        // blocks' last positions are real and only masked)
+        if (key0 + BLOCK_N - 1 > p_last) {
           ok = mbar_wait(bar(BAR_V_FULL + vst), (j / KV_STAGES) & 1, &abort_flag);
           if (!ok) break;
           const int vrow = r & 63, half = r >> 6;
-          if (key0 + vrow > p_max) {
+          if (key0 + vrow > p_last) {
             uint4* dst = reinterpret_cast<uint4*>(v_s + vst * KV_BYTES + half * (KV_BYTES / 2) + vrow * 128);
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) dst[ch] = make_uint4(0, 0, 0, 0);
@@ -402,10 +436,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V) visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(bar(BAR_P_FULL));
+        mbar_arrive(bar(BAR_P_FULL + x));
       }
-      if (ok) ok = mbar_wait(bar(BAR_PV_FULL), (num_tiles - 1) & 1, &abort_flag);
-      if (ok) {
+      if (ok && my_tiles) ok = mbar_wait(bar(BAR_PV_FULL + x), (my_tiles - 1) & 1, &abort_flag);
+      if (ok && my_tiles) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = 1.f / l_run;
         bf16* dst = row_ok ? out + ((long)(tok0 + R / G) * nq + kvh * G + R % G) * D : nullptr;
@@ -457,7 +491,7 @@ EncodeTiledFn encode_fn() {
 
 // q: the QKV buffer, [num_tokens, *] bf16 with row stride q_stride (elements), head h at column
 // h * 128.  kpages / vpages: [num_rows_kv / (nkv * ps), nkv, ps, 128] bf16 of one layer, num_rows_kv
-// rows of 128 in all.  num_work = sum over served sequences of ceil(q_len * (nq / nkv) / 128).
+// rows of 128 in all.  num_work = sum over served sequences of ceil(ceil(q_len * (nq / nkv) / 128) / 2).
 // Returns Q3_ERR_UNSUPPORTED for shapes this kernel does not take (the caller then uses the
 // mma.sync kernel).  error_word: device int set to 2 if a wait inside the kernel expired.
 Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num_tokens, const void* kpages,
@@ -502,7 +536,7 @@ Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num
       return Q3_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid(num_work, nkv);
+  dim3 grid((unsigned)num_work * nkv);
   prefill_attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, block_table, max_pages, kv_lens,
                                                                     cu_seqlens, (bf16*)out, num_seqs, num_work, nq,
                                                                     nkv, ps, scale * 1.4426950408889634f,

@@ -235,10 +235,11 @@ class CudaOps:
                     and self.prefill_attention == "tcgen05"):
                 # tcgen05/TMEM kernel; it answers "unsupported" for what it does not take
                 self.launches += 1
+                pairs = sum(-(-(-(-n * group // 128)) // 2) for n in qlens if n > 1)  # two row blocks per work item
                 code = self._get("attention_prefill_tc", "q3_paged_attention_prefill_tc")(
                     _ptr(q), q_stride, q.shape[0], _ptr(k_pages), _ptr(v_pages),
                     k_pages.shape[0] * num_kv_heads * page_size, _ptr(block_table), block_table.shape[1],
-                    _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), step.num_seqs, work, num_heads,
+                    _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), step.num_seqs, pairs, num_heads,
                     num_kv_heads, head_dim, page_size, float(scale), 1, _ptr(self._error_word(out.device)),
                     self._stream())
                 if code == 0:
