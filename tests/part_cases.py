@@ -1,7 +1,8 @@
 """Each part of a block alone against the plain implementation's function for it, and the
 generality of the parts: a run order that names a layer twice, a layer that reads another
-layer's cache, an attention window, and a toy mixer with state of its own that is defined
-and registered here, without any change to the framework's files.  Run on the CPU with the
+layer's cache, an attention window, and toy parts that are defined and registered here,
+without any change to the framework's files: a mixer with state of its own, a feed-forward with
+routing, a position encoding.  Run on the CPU with the
 torch statements of the kernels and on the GPU with the kernels."""
 
 from __future__ import annotations
@@ -302,3 +303,169 @@ def case_toy_state_mixer(dtype, ops, device):
         assert float((whole["a"][5:] - whole["a"][:-5]).abs().max()) > 1e-3
     finally:
         unregister_part("mixer", "toy_decay_state")
+
+
+def _plain_layers(raw, tensors, ids, act, *, positions=None, feed_forward=None):
+    """The plain model written out layer by layer, with the rotation's positions and the
+    feed-forward open to replacement (tests of toy parts)."""
+    ids_t = torch.as_tensor(ids, dtype=torch.long)
+    pos = torch.arange(len(ids)) if positions is None else positions
+    wf = {k: v.float() for k, v in tensors.items()}
+    h = wf["model.embed_tokens.weight"][ids_t]
+    eps = raw["rms_norm_eps"]
+    for layer in range(raw["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        n = pm._round(pm.rmsnorm(h, wf[p + "input_layernorm.weight"], eps), act)
+        a, _ = pm.attention_part(n, wf, p + "self_attn.", raw, pos, act_dtype=act)
+        h = h + a
+        n = pm._round(pm.rmsnorm(h, wf[p + "post_attention_layernorm.weight"], eps), act)
+        ff = feed_forward(layer, n, wf) if feed_forward is not None else None
+        h = h + (ff if ff is not None else pm.swiglu_part(n, wf, p + "mlp.", act_dtype=act))
+    head = wf.get("lm_head.weight", wf["model.embed_tokens.weight"])
+    return pm._round(pm.rmsnorm(h, wf["model.norm.weight"], eps), act) @ head.T
+
+
+class Top1ExpertsFeedForward(Part):
+    """A toy feed-forward with routing: a router picks one of E small SwiGLU experts per token
+    (router logits and their softmax in fp32) and the expert's output is scaled by the router's
+    probability.  The experts' products go through the framework's kernel table, with however
+    many tokens each expert happens to get.  A test fixture, not a model of anything."""
+
+    category = "feed_forward"
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.hidden, self.inter, self.experts = int(spec["hidden_size"]), int(spec["intermediate_size"]), int(spec["experts"])
+
+    def param_specs(self):
+        specs = {"router.weight": ParamSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            specs[f"experts.{e}.gate_up.weight"] = ParamSpec((2 * self.inter, self.hidden))
+            specs[f"experts.{e}.down.weight"] = ParamSpec((self.hidden, self.inter))
+        return specs
+
+    def load(self, tensors):
+        self.router = tensors["router.weight"].float()
+        self.gate_up = [tensors[f"experts.{e}.gate_up.weight"].contiguous() for e in range(self.experts)]
+        self.down = [tensors[f"experts.{e}.down.weight"].contiguous() for e in range(self.experts)]
+
+    def kernel_groups(self):
+        return (["norm", "gemm_f32"] if self.ctx.dtype == torch.float32
+                else ["norm", "gemm_small_m", "gemm_stream", "gemm_tcgen05"])
+
+    def forward(self, h, step):
+        probs = torch.softmax(h.float() @ self.router.t(), dim=-1)
+        weight, choice = probs.max(dim=-1)
+        out = torch.zeros_like(h)
+        for e in range(self.experts):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel() == 0:
+                continue
+            x = h[rows].contiguous()
+            mid = torch.empty((x.shape[0], self.inter), dtype=h.dtype, device=h.device)
+            self.ops.gated_linear(x, self.gate_up[e], mid)
+            y = self.ops.linear(mid, self.down[e])
+            out[rows] = (y.float() * weight[rows, None]).to(h.dtype)
+        return out
+
+
+def case_toy_routed_feed_forward(dtype, ops, device):
+    """Register, build and step a feed-forward with routing in layer 1, next to the dense one in
+    layer 0: against the plain arithmetic, and the same logits however the tokens are cut."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    E, inter = 3, 48
+    register_part("feed_forward", "toy_top1_experts", Top1ExpertsFeedForward)
+    try:
+        toy = PartSpec("toy_top1_experts", dict(hidden_size=cfg.hidden_size, intermediate_size=inter, experts=E))
+        blocks = (base.blocks[0], PartSpec("pre_norm", {**base.blocks[1].params, "feed_forward": toy}))
+        spec = ModelSpec(base.vocab_size, base.hidden_size, blocks, base.order, base.final_norm, True)
+        model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+        assert "model.layers.1.mlp.router.weight" in tensors and "model.layers.1.mlp.gate_proj.weight" not in tensors
+        ids = random_ids(cfg.vocab_size, 40, 41)
+        whole, _ = _run_cut(model, cfg, ids, cuts=(40,))
+        cut, _ = _run_cut(model, cfg, ids, cuts=(5, 2, 9, 1, 1, 30))
+        act = torch.bfloat16 if dtype == "bfloat16" else None
+        chosen = []
+
+        def routed(layer, n, wf):
+            if layer != 1:
+                return None
+            p = "model.layers.1.mlp."
+            probs = torch.softmax(n.float() @ wf[p + "router.weight"].T, dim=-1)
+            weight, choice = probs.max(dim=-1)
+            chosen.append(choice)
+            out = torch.zeros_like(n)
+            for e in range(E):
+                rows = choice == e
+                gu = n[rows] @ wf[p + f"experts.{e}.gate_up.weight"].T
+                g, u = pm._round(gu[:, :inter], act), pm._round(gu[:, inter:], act)
+                mid = pm._round(g * torch.sigmoid(g) * u, act)
+                y = pm._round(mid @ wf[p + f"experts.{e}.down.weight"].T, act)
+                out[rows] = pm._round(y * weight[rows, None], act)
+            return out
+
+        want = _plain_layers(cfg.to_hf_config(), tensors, ids, act, feed_forward=routed)
+        assert len(set(chosen[0].tolist())) == E, "the test wants every expert to get tokens"
+        scale = max(1.0, float(want.abs().max()))
+        if dtype == "float32":
+            assert float((whole - want).abs().max()) <= 3e-5 * scale
+            assert float((whole - cut).abs().max()) <= 3e-5 * scale
+        else:  # a token whose two best experts are close may go the other way in bfloat16: compare most rows
+            close_rows = ((whole - want).abs().amax(dim=1) <= 0.03 * scale).float().mean()
+            assert float(close_rows) >= 0.9
+            assert float(((whole - cut).abs().amax(dim=1) <= 0.03 * scale).float().mean()) >= 0.9
+    finally:
+        unregister_part("feed_forward", "toy_top1_experts")
+
+
+class SlowedRotary(Part):
+    """A toy position encoding: rotate-half rotary embedding whose angle grows `rate` times as
+    fast as the position (rate < 1: positions squeezed together).  It hands the attention kernel
+    its own tables; nothing else in the framework knows about it."""
+
+    category = "position"
+    style = "neox"
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.dim, self.theta = int(spec["rotary_dim"]), float(spec["theta"])
+        self.rate, self.max_positions = float(spec["rate"]), int(spec["max_positions"])
+
+    def kernel_groups(self):
+        return ["rope_kv"]
+
+    def rotation_tables(self):
+        key = ("toy_slowed_rotary", self.dim, self.theta, self.rate, self.max_positions)
+        if key not in self.ctx.shared:
+            inv = 1.0 / (self.theta ** (torch.arange(0, self.dim, 2, dtype=torch.float) / self.dim))
+            angle = (torch.arange(self.max_positions, dtype=torch.float) * self.rate)[:, None] * inv[None, :]
+            self.ctx.shared[key] = (angle.cos().to(self.ctx.device), angle.sin().to(self.ctx.device))
+        return self.ctx.shared[key]
+
+
+def case_toy_position_encoding(dtype, ops, device):
+    """Register a position encoding of the test's own and give it to the attention of both layers."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    rate = 0.25
+    register_part("position", "toy_slowed_rotary", SlowedRotary)
+    try:
+        toy = PartSpec("toy_slowed_rotary", dict(rotary_dim=cfg.head_dim, theta=cfg.rope_theta, rate=rate,
+                                                 max_positions=cfg.max_position_embeddings))
+        blocks = tuple(
+            PartSpec("pre_norm", {**b.params, "mixer": PartSpec("paged_attention", {**b["mixer"].params, "position": toy})})
+            for b in base.blocks)
+        spec = ModelSpec(base.vocab_size, base.hidden_size, blocks, base.order, base.final_norm, True)
+        model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+        ids = random_ids(cfg.vocab_size, 40, 42)
+        got, _ = _run_cut(model, cfg, ids)
+        act = torch.bfloat16 if dtype == "bfloat16" else None
+        raw = cfg.to_hf_config()
+        want = _plain_layers(raw, tensors, ids, act, positions=torch.arange(len(ids), dtype=torch.float) * rate)
+        ordinary = _plain_layers(raw, tensors, ids, act)
+        scale = max(1.0, float(want.abs().max()))
+        assert float((got - want).abs().max()) <= (3e-5 if dtype == "float32" else 0.03) * scale
+        assert float((want - ordinary).abs().max()) > 1e-2, "the encoding has to matter for the test to mean anything"
+    finally:
+        unregister_part("position", "toy_slowed_rotary")

@@ -32,3 +32,11 @@ def test_window_attention():
 
 def test_toy_state_mixer_registers_builds_and_steps():
     pc.case_toy_state_mixer(DT, OPS, DEV)
+
+
+def test_toy_routed_feed_forward_registers_builds_and_steps():
+    pc.case_toy_routed_feed_forward(DT, OPS, DEV)
+
+
+def test_toy_position_encoding_registers_builds_and_steps():
+    pc.case_toy_position_encoding(DT, OPS, DEV)
