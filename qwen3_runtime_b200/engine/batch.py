@@ -50,11 +50,12 @@ class BatchBuilder:
         self._turn = 0
         self._capacity = 0
         self.pin = torch.device(device).type == "cuda"
+        self._last_decode: dict | None = None  # what the last captured-size decode step packed
 
     def _buffers(self, need: int):
         if need > self._capacity:
             self._capacity = max(4096, 1 << (need - 1).bit_length())
-            self._host = [torch.empty(self._capacity, dtype=torch.int32, pin_memory=self.pin)
+            self._host = [torch.zeros(self._capacity, dtype=torch.int32, pin_memory=self.pin)
                           for _ in range(self.RING)]
             self._events = [None] * self.RING
             self._dev = torch.empty(self._capacity, dtype=torch.int32, device=self.device)
@@ -64,15 +65,77 @@ class BatchBuilder:
             ev.synchronize()
         return self._host[self._turn], self._dev
 
+    def _continue_decode(self, entries, pad_to, table_width, scratch_page, scratch_slot, device_buffer) -> bool:
+        """The same requests as in the last packed step, one more token each, into the same
+        device buffer: only token ids, positions, lengths and block-table rows that grew
+        change.  Updates the kept image of the buffer and copies it; False if the step is not
+        such a continuation (the caller then packs it in full)."""
+        last = self._last_decode
+        if (last is None or last["device_buffer"] is not device_buffer or len(entries) != len(last["caches"])
+                or last["key"] != (pad_to, table_width, scratch_page, scratch_slot)):
+            return False
+        for e, c in zip(entries, last["caches"]):
+            if e.cache is not c or len(e.tokens) != 1:
+                return False
+        n = len(entries)
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n)
+        starts = np.fromiter((e.cache.num_computed for e in entries), dtype=np.int32, count=n)
+        reserved = np.fromiter((e.cache.num_reserved for e in entries), dtype=np.int32, count=n)
+        if not np.array_equal(starts, last["starts"] + 1):
+            return False  # not exactly one token further than the step this image was packed for
+        if (toks.min() < 0 or toks.max() >= self.vocab_size or (starts + 1 > reserved).any()
+                or int(starts.max()) + 1 > self.max_positions or any(e.want not in ([0], []) for e in entries)):
+            return False  # the full path words the error
+        image, sections, width, B = last["image"], last["sections"], last["width"], last["B"]
+
+        def sec(name):
+            o, s = sections[name]
+            return image[o:o + s]
+
+        sec("ids")[:n] = toks
+        sec("pos")[:n] = starts
+        sec("kv")[:n] = starts + 1
+        for g, windowed in enumerate(last["windowed"]):
+            bt = None
+            for b, e in enumerate(entries):
+                size = len(e.cache.tables[g])
+                if windowed or size != last["table_lens"][b][g]:
+                    if size > width:
+                        return False
+                    if bt is None:
+                        bt = sec(f"bt{g}").reshape(B, width)
+                    bt[b, :] = scratch_page
+                    bt[b, :size] = e.cache.table_array(g)
+                    last["table_lens"][b][g] = size
+        last["starts"] = starts
+        off = last["off"]
+        host, _ = self._buffers(off)
+        views = last.setdefault("views", {})
+        view = views.get(self._turn)
+        if view is None or view[0] is not host:  # slices of the staging buffers, made once
+            view = views[self._turn] = (host, host.numpy()[:off], host[:off], device_buffer[:off])
+        view[1][:] = image
+        view[3].copy_(view[2], non_blocking=True)
+        if self.pin:
+            ev = self._events[self._turn] or torch.cuda.Event()
+            ev.record()
+            self._events[self._turn] = ev
+        return True
+
     def build(self, entries: list[StepEntry], *, pad_to: int | None = None, table_width: int | None = None,
               scratch_page: int = 0, scratch_slot: int = 0, device_buffer: torch.Tensor | None = None,
-              all_rows: bool = False) -> StepContext:
+              all_rows: bool = False, need_context: bool = True) -> StepContext | None:
         """Pack a step.  ``pad_to`` appends dummy one-token sequences (writing to the
         scratch page) so that a decode batch fills a captured batch size; ``table_width``
         fixes the block-table width; ``device_buffer`` is a preallocated int32 buffer that
-        the metadata is copied into (captured steps read from fixed addresses)."""
+        the metadata is copied into (captured steps read from fixed addresses).
+        ``need_context=False``: the caller only wants the device buffer filled (a replayed
+        graph reads it) and gets no :class:`StepContext`."""
         if not entries:
             raise BatchError("a step needs at least one entry")
+        if not need_context and device_buffer is not None and all_rows:
+            if self._continue_decode(entries, pad_to, table_width, scratch_page, scratch_slot, device_buffer):
+                return None
         ps = self.cache.page_size
         n_paged = len(self.cache.paged_groups)
         B_real = len(entries)
@@ -171,6 +234,15 @@ class BatchBuilder:
             ev = self._events[self._turn] or torch.cuda.Event()
             ev.record()
             self._events[self._turn] = ev
+        self._last_decode = None
+        if device_buffer is not None and all_rows and T_real == B_real:
+            windowed = [self.cache.groups[g].window is not None for g in self.cache.paged_groups]
+            self._last_decode = dict(
+                caches=[e.cache for e in entries], key=(pad_to, table_width, scratch_page, scratch_slot),
+                device_buffer=device_buffer, off=off, width=width, B=B, sections=sections, image=h[:off].copy(),
+                table_lens=[[len(t) for t in e.cache.tables] for e in entries], windowed=windowed, starts=starts.copy())
+        if not need_context:
+            return None
 
         def dsec(name, size=None):
             o, s = sections[name]

@@ -56,7 +56,7 @@ class DecodeGraphs:
         cap = self.captured.get(key)
         if cap is None:
             cap = self._capture(key, entries)
-        self._fill(cap, entries, bucket, width)
+        self._fill(cap, entries, bucket, width, need_context=False)
         cap.graph.replay()
         self.replays += 1
         wanted = [i for i, e in enumerate(entries) if e.want]
@@ -66,10 +66,11 @@ class DecodeGraphs:
             return cap.logits[:0]
         return cap.logits[torch.tensor(wanted, dtype=torch.long, device=cap.logits.device)]
 
-    def _fill(self, cap: _Captured, entries, bucket: int, width: int):
+    def _fill(self, cap: _Captured, entries, bucket: int, width: int, need_context: bool = True):
         r = self.runner
         return r.builder.build(entries, pad_to=bucket, table_width=width, scratch_page=r.storage.scratch_page,
-                               scratch_slot=r.storage.scratch_slot, device_buffer=cap.meta, all_rows=True)
+                               scratch_slot=r.storage.scratch_slot, device_buffer=cap.meta, all_rows=True,
+                               need_context=need_context)
 
     def _capture(self, key, entries) -> _Captured:
         bucket, width = key
