@@ -67,7 +67,14 @@ class Engine:
         logits = self.runner.run(entries)
         tokens: dict[int, int] = {}
         if sampling:
+            # kernels with bounded waits report through a device word: its copy rides along with
+            # the step and is looked at after the wait for the sampled tokens
+            ops = self.sampler.ops
+            if hasattr(ops, "watch_kernel_errors"):
+                ops.watch_kernel_errors()
             toks, logprobs = self.sampler.sample(logits, sampling)
+            if hasattr(ops, "raise_if_watched_error"):
+                ops.raise_if_watched_error()
             for req, tok, lp in zip(sampling, toks, logprobs):
                 tokens[req.request_id] = tok
                 if lp is not None:

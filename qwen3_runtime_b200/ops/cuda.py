@@ -337,8 +337,10 @@ class CudaOps:
     # ---- matrix products ----------------------------------------------------------------
     def linear(self, x, weight, out=None, out_dtype=None):
         """``x[M, K] @ weight[N, K]^T``.  float32: this engine's FMA kernel (no TF32).
-        bfloat16: the library product with fp32 accumulation, as the reference's
-        ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77, 134-135)."""
+        bfloat16, at most 16 tokens: one of this engine's two weight-streaming kernels
+        (:meth:`_small_product`).  bfloat16, more tokens: the library product with fp32
+        accumulation, as the reference's ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77,
+        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"``."""
         M, K = x.shape
         N = weight.shape[0]
         if weight.shape[1] != K:
@@ -381,6 +383,23 @@ class CudaOps:
             err.zero_()
             raise KernelError("a bounded wait inside a kernel expired (tcgen05 product or attention, or the "
                               "streaming product): the kernel gave up and its output is invalid")
+
+    def watch_kernel_errors(self) -> None:
+        """Enqueue a copy of the error word to pinned host memory, without waiting for it.
+        :meth:`raise_if_watched_error` looks at the copy once the host has waited for the
+        device for a reason of its own (the sampled tokens), so a step pays no extra wait."""
+        err = getattr(self, "_err", None)
+        if err is None:
+            return
+        if getattr(self, "_err_host", None) is None:
+            self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._err_host.copy_(err, non_blocking=True)
+
+    def raise_if_watched_error(self) -> None:
+        host = getattr(self, "_err_host", None)
+        if host is not None and int(host[0]) != 0:
+            host.zero_()
+            self.raise_if_kernel_error()
 
     def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None):
         """``x @ weight^T`` on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).  ``mode=2``: SwiGLU with

@@ -43,6 +43,24 @@ def test_llm_without_a_model_builds_a_tiny_random_one():
         llm.generate("text")
 
 
+def test_generation_stops_when_a_kernel_reports_an_expired_wait():
+    """Kernels with bounded waits give up through a word in device memory instead of hanging.
+    The test writes that word itself (nothing is made to wait): the next sampling step raises."""
+    from qwen3_runtime_b200 import LLM
+    from qwen3_runtime_b200.ops.cuda import KernelError
+
+    llm = LLM(dtype="bfloat16")
+    assert len(llm.generate([1, 2, 3], max_tokens=3)) == 3
+    ops = llm.engine.sampler.ops
+    ops._error_word(torch.device("cuda")).fill_(2)
+    with pytest.raises(KernelError, match="bounded wait"):
+        llm.generate([1, 2, 3], max_tokens=3)
+    assert int(ops._error_word(torch.device("cuda")).item()) == 0  # reported once, then cleared
+    for rid in list(llm.engine._requests):
+        llm.engine.abort_request(rid)
+    assert len(llm.generate([4, 5], max_tokens=2)) == 2
+
+
 def test_command_line(tmp_path):
     folder = make_model_dir(tmp_path, "A")
     raw, w = pm.read_model_dir(folder)
