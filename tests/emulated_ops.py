@@ -8,7 +8,6 @@ be exercised without a GPU.  Loops are deliberately simple; nothing here is fast
 
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -5,12 +5,11 @@ float32 and bfloat16."""
 
 from __future__ import annotations
 
-import math
 
 import torch
 
 import plain_model as pm
-from helpers import (TINY, first_mismatch, make_model_dir, max_abs_diff, peak_tokens, random_ids, run_trace,
+from helpers import (TINY, first_mismatch, make_model_dir, peak_tokens, random_ids, run_trace, 
                      trace_mixed, trace_portions, trace_tail_decode, trace_whole)
 from qwen3_runtime_b200.engine.factory import build_engine, build_runtime, load_model
 

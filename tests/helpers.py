@@ -2,9 +2,7 @@
 
 from __future__ import annotations
 
-import json
 import random
-from dataclasses import dataclass, field
 
 import torch
 

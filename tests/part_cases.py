@@ -20,7 +20,7 @@ from qwen3_runtime_b200.engine.factory import build_runtime
 from qwen3_runtime_b200.models.qwen3 import qwen3_spec
 from qwen3_runtime_b200.parts import (BuildContext, DecoderModel, ParamSpec, Part, ResidualStream, build_part,
                                       register_part, unregister_part)
-from qwen3_runtime_b200.weights import DictSource, load_into, random_state
+from qwen3_runtime_b200.weights import DictSource, load_into
 from qwen3_runtime_b200.weights.loader import place
 
 TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}

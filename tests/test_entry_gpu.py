@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_model as pm
-from helpers import TINY, make_model_dir, random_ids
+from helpers import make_model_dir, random_ids
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent

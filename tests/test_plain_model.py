@@ -7,7 +7,7 @@ import torch
 from safetensors.torch import load_file
 
 import plain_model as pm
-from helpers import TINY, make_model_dir
+from helpers import make_model_dir
 
 GOLDEN = Path(__file__).parent / "golden"
 

@@ -7,7 +7,7 @@ from safetensors.torch import load_file, save_file
 from emulated_ops import TorchOps
 from helpers import TINY, make_model_dir
 from qwen3_runtime_b200.engine.factory import load_model
-from qwen3_runtime_b200.weights import WeightError, expected_tensors_for, random_state, write_random_model
+from qwen3_runtime_b200.weights import WeightError, expected_tensors_for, random_state
 
 
 def test_random_model_is_a_function_of_config_and_seed(tmp_path):
