@@ -132,6 +132,13 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+// 2^x in one instruction (exp2f adds range fix-ups around the same instruction; results
+// below 2^-126 become zero here, which is what a probability that small is worth)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -375,24 +382,32 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         }
         const bool rescale = __any_sync(0xffffffffu, corr != 1.f) && j > 0;
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        float sums[4] = {0.f, 0.f, 0.f, 0.f};
-        // probabilities, rounded to bf16 as the MMA will see them, into the swizzled P tile
+        // probabilities, rounded to bf16 as the MMA will see them, into the swizzled P tile; the
+        // scaling and the row sum run on pairs of elements (packed fp32 instructions)
+        float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         unsigned char* p_row = p_s + (2 * x + st) * P_BYTES + r * 128;  // buffer j & 1: PV_{j-1} may still read the other
-        const float neg = -m_use * scale_log2;
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        const float2 neg2 = make_float2(-m_use * scale_log2, -m_use * scale_log2);
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = ch * 8 + 2 * e;
-            const float x0 = exp2f(fmaf(__uint_as_float(c < 32 ? sa[c] : sb[c - 32]), scale_log2, neg));
-            const float x1 = exp2f(fmaf(__uint_as_float(c + 1 < 32 ? sa[c + 1] : sb[c + 1 - 32]), scale_log2, neg));
-            sums[e] += x0 + x1;
-            w[e] = pack2(x0, x1);
+            const float2 s2 = make_float2(__uint_as_float(c < 32 ? sa[c] : sb[c - 32]),
+                                          __uint_as_float(c + 1 < 32 ? sa[c + 1] : sb[c + 1 - 32]));
+            const float2 t2 = __ffma2_rn(s2, scale2, neg2);
+            const float2 x2 = make_float2(ex2(t2.x), ex2(t2.y));
+            sums[e] = __fadd2_rn(sums[e], x2);
+            w[e] = pack2(x2.x, x2.y);
           }
           *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        l_run = l_run * corr + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+        {
+          const float2 a = __fadd2_rn(sums[0], sums[1]), b = __fadd2_rn(sums[2], sums[3]);
+          const float2 c = __fadd2_rn(a, b);
+          l_run = l_run * corr + (c.x + c.y);
+        }
         // PV_{j-1} must be finished before P_j is signalled: it keeps this barrier from running a
         // phase ahead of the waiters, and O must be at rest if it has to be rescaled
         if (j > 0) {
