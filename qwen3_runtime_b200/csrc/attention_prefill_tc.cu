@@ -11,13 +11,13 @@
 // is used by both row blocks.  Per 64-key tile a row block's chain is long (TMEM load, exp2
 // on the special-function unit, shared-memory stores, fences, barrier round trips) and
 // leaves the tensor core and the exp2 unit idle most of the time; two blocks in flight hide
-// each other's chain.  Ten warps:
+// each other's chain.  Eleven warps:
 //   warp 0           : TMA producer (Q of both blocks once, then K and V tiles through 3-stage
 //                      rings; the lanes issue a tile's page boxes side by side);
-//   warp 1, one lane : MMA issuer.  Order: S_A0, S_B0, S_A1, S_B1, then per tile j:
-//                      P_Aj ready -> PV_Aj, S_A(j+2); P_Bj ready -> PV_Bj, S_B(j+2).  S has two
-//                      TMEM buffers per block, so the tensor core works for one block while
-//                      the other block's softmax runs;
+//   warps 1 and 10,  : MMA issuers of block A and of block B.  Order per block: S_0, S_1, then
+//   one lane each      per tile j: P_j ready -> PV_j, S_(j+2).  S has two TMEM buffers per block,
+//                      so the tensor core works for one block while the other block's softmax
+//                      runs;
 //   warps 2..5, 6..9 : softmax of block A and of block B, one thread per row: reads S from
 //                      TMEM, masks, online softmax in fp32 (exp2, scale folded in), writes P
 //                      (bf16) to shared memory (two buffers per block) in the swizzled K-major
@@ -39,7 +39,7 @@ namespace {
 constexpr int D = 128;
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
-constexpr int THREADS = 320;
+constexpr int THREADS = 352;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 32 KB: two halves of [128 rows][128 B]
 constexpr int KV_BYTES = BLOCK_N * D * 2;       // 16 KB: two halves of [64 rows][128 B]
@@ -193,9 +193,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     mbar_init(bar(BAR_Q), 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(bar(BAR_K_FULL + i), 1);
-      mbar_init(bar(BAR_K_EMPTY + i), 1);
+      mbar_init(bar(BAR_K_EMPTY + i), 2);  // both issuers
       mbar_init(bar(BAR_V_FULL + i), 1);
-      mbar_init(bar(BAR_V_EMPTY + i), 1);
+      mbar_init(bar(BAR_V_EMPTY + i), 2);
     }
     for (int i = 0; i < 4; ++i) mbar_init(bar(BAR_S_FULL + i), 1);
     for (int i = 0; i < 2; ++i) {
@@ -281,52 +281,62 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         if (!ok) break;
         if (page >= 0) tma_load_2d(smem_addr(v_s) + off, &tmap_v, bar(BAR_V_FULL + st), my_half * 64, y);
       }
-    } else if (warp == 1) {
-      if (lane == 0) {  // ---- MMA issuer -----------------------------------------------------------
+    } else if (warp == 1 || warp == 10) {
+      if (lane == 0) {  // ---- MMA issuers: warp 1 for block A, warp 10 for block B ------------------
+        // Issuing is work too (descriptors, a dozen instructions per tile and block, barrier round
+        // trips), so each block has its own issuing thread.  Both use every K and V tile: its
+        // "empty" barrier counts two arrivals, a commit from an issuer that multiplied with the
+        // tile and a plain arrival (after the tile's "full") from one that had no use for it.
+        const int x = warp == 1 ? 0 : 1;
+        const int my_tiles = tiles[x];
         constexpr uint32_t idesc_s = idesc_bf16(BLOCK_M, BLOCK_N, 0);   // S = Q K^T: N = 64 keys
         constexpr uint32_t idesc_pv = idesc_bf16(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
-        const uint32_t p_addr = smem_addr(p_s);
-        // S_j of block x into its TMEM buffer j & 1; the key tile is released by its last user
-        auto issue_s = [&](int x, int j) -> bool {
+        const uint32_t p_addr = smem_addr(p_s) + 2 * x * P_BYTES;
+        const uint32_t q_addr = smem_addr(q_s) + x * Q_BYTES;
+        const uint32_t tmem_x = tmem + x * TMEM_BLOCK;
+        // S_j into TMEM buffer j & 1, or just the hand-back of key tile j
+        auto keys = [&](int j) -> bool {
           const int st = j % KV_STAGES, sbuf = j & 1;
           if (!mbar_wait(bar(BAR_K_FULL + st), (j / KV_STAGES) & 1, &abort_flag)) return false;
+          if (j >= my_tiles) {
+            mbar_arrive(bar(BAR_K_EMPTY + st));
+            return true;
+          }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t k_addr = smem_addr(k_s) + st * KV_BYTES;
-          const uint32_t q_addr = smem_addr(q_s) + x * Q_BYTES;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t half = (k >> 2), sub = (k & 3) * 2;  // 4 steps of 32 bytes per 64-wide half
-            umma(tmem + x * TMEM_BLOCK + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
+            umma(tmem_x + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
                  desc_kmajor(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
           }
-          const bool last_user = x == 1 || j >= tiles[1];
-          if (last_user) umma_commit(bar(BAR_K_EMPTY + st));  // the key tile may be overwritten
-          umma_commit(bar(BAR_S_FULL + 2 * x + sbuf));        // S_j is in TMEM
+          umma_commit(bar(BAR_K_EMPTY + st));           // this block is done with the key tile
+          umma_commit(bar(BAR_S_FULL + 2 * x + sbuf));  // S_j is in TMEM
           return true;
         };
-        bool ok = mbar_wait(bar(BAR_Q), 0, &abort_flag);
-        for (int j = 0; j < 2 && ok; ++j)
-          for (int x = 0; x < 2 && ok; ++x)
-            if (j < tiles[x]) ok = issue_s(x, j);
+        bool ok = my_tiles == 0 || mbar_wait(bar(BAR_Q), 0, &abort_flag);
+        for (int j = 0; j < 2 && j < num_tiles && ok; ++j) ok = keys(j);
         for (int j = 0; j < num_tiles && ok; ++j) {
           const int st = j % KV_STAGES, pbuf = j & 1;
-          for (int x = 0; x < 2 && ok; ++x) {
-            if (j >= tiles[x]) continue;
+          if (j < my_tiles) {
             ok = mbar_wait(bar(BAR_P_FULL + x), j & 1, &abort_flag);  // P_j written, S_j and PV_{j-1} consumed
             if (!ok) break;
-            ok = mbar_wait(bar(BAR_V_FULL + st), (j / KV_STAGES) & 1, &abort_flag);
-            if (!ok) break;
+          }
+          ok = mbar_wait(bar(BAR_V_FULL + st), (j / KV_STAGES) & 1, &abort_flag);
+          if (!ok) break;
+          if (j < my_tiles) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
 #pragma unroll
             for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
-              umma(tmem + x * TMEM_BLOCK + 2 * BLOCK_N, desc_kmajor(p_addr + (2 * x + pbuf) * P_BYTES) + 2 * k,
+              umma(tmem_x + 2 * BLOCK_N, desc_kmajor(p_addr + pbuf * P_BYTES) + 2 * k,
                    desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-            const bool last_user = x == 1 || j >= tiles[1];
-            if (last_user) umma_commit(bar(BAR_V_EMPTY + st));
+            umma_commit(bar(BAR_V_EMPTY + st));
             umma_commit(bar(BAR_PV_FULL + x));
-            if (j + 2 < tiles[x]) ok = issue_s(x, j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
+          } else {
+            mbar_arrive(bar(BAR_V_EMPTY + st));
           }
+          if (j + 2 < num_tiles) ok = keys(j + 2);  // its TMEM buffer (j & 1) was read before P_j was signalled
         }
       }
     } else {  // ---- softmax: one thread per row; warps 2..5 block A, warps 6..9 block B ---------------
