@@ -127,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int STAGE_BYTES = A_BYTES + NB * B_BYTES;
   constexpr int ACC_COLS = 256;          // columns per accumulator buffer (BN * NB of them are used)
   constexpr int TMEM_COLS = 2 * ACC_COLS;  // 512: the whole tensor memory of the SM
-  static_assert(BN * NB <= ACC_COLS && BN % 32 == 0, "tile width");
+  static_assert(BN * NB <= ACC_COLS && BN % 32 == 0 && (BN * NB) % 16 == 0, "tile width");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];
@@ -185,7 +185,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- MMA issuer ---------------------------------------------------------
-      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      // the B tiles of a stage lie one after the other, which is the layout of one tile of
+      // NB * BN rows: one MMA over all of them reads the A tile once instead of NB times
+      constexpr uint32_t idesc = umma_idesc(BM, NB * BN);
       int g = 0, i = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
@@ -202,13 +204,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
           const uint64_t a_desc = umma_desc(a_addr);
+          const uint64_t b_desc = umma_desc(a_addr + A_BYTES);
 #pragma unroll
-          for (int j = 0; j < NB; ++j) {
-            const uint64_t b_desc = umma_desc(a_addr + A_BYTES + j * B_BYTES);
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes = 2 descriptor units along K
-              umma_bf16(acc + j * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes = 2 descriptor units along K
+            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(empty0 + 8 * s);  // arrives when these MMAs have read the stage
         }
         if (ok) umma_commit(acc_full0 + 8 * buf);  // arrives when the tile's MMAs have written TMEM
