@@ -291,6 +291,238 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (threadIdx.x == 0 && abort_flag && error_word) atomicExch(error_word, 1);
 }
 
+// ---- the same product on pairs of SMs (cta_group::2) -------------------------------------------------
+// One MMA of 256 x 256 over two CTAs of a cluster: each CTA holds 128 token rows of A and 128
+// of the 256 feature rows of B (for SwiGLU: the leader the gate rows, its peer the up rows of
+// the same 128 features) and gets the accumulator rows of its own tokens in its own tensor
+// memory.  Per 16 k-values a CTA's shared memory is read for 4 KB of A and 4 KB of B instead
+// of 4 KB + 8 KB, which is what keeps the one-CTA kernel below 70 % of the tensor pipe.
+//   warp 0, one lane : TMA producer of this CTA's A and B boxes (6-stage ring).  Both CTAs'
+//                      loads complete their bytes on the leader's "full" barrier of the stage
+//                      (cp.async.bulk.tensor with .cta_group::2), which the leader arms for
+//                      both; a relay through the peer's own barrier cost several hundred
+//                      cycles per stage;
+//   warp 1, one lane : leader only: MMA issuer; it releases a stage, and hands over a finished
+//                      accumulator, in both CTAs at once with multicast commits;
+//   warps 2..5       : epilogue of this CTA's 128 rows; "accumulator drained" goes to the
+//                      leader (8 arrivals: 4 warps of each CTA).
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BN = 256;
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the box lands in this CTA's shared memory, its bytes count on the pair leader's barrier
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both)
+               : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                         void* __restrict__ out, int ldo, int M, int N, int K, int up_row_offset,
+                         int* __restrict__ error_word) {
+  constexpr int A_BYTES = BM * BK * 2;       // this CTA's 128 token rows
+  constexpr int B_BYTES = 128 * BK * 2;      // this CTA's 128 feature rows
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int ACC_COLS = 256;
+  constexpr int TMEM_COLS = 2 * ACC_COLS;
+  constexpr int TILE_N = MODE == OUT_SWIGLU ? 128 : PAIR_BN;  // output columns per tile
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * PAIR_STAGES + 4];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_n = (N + TILE_N - 1) / TILE_N, tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[PAIR_STAGES]);
+  const uint32_t acc_full0 = smem_addr(&bars[2 * PAIR_STAGES]), acc_empty0 = smem_addr(&bars[2 * PAIR_STAGES + 2]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 8);  // one arrival per epilogue warp of both CTAs (used in the leader)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // both CTAs of the pair execute the pair-wide allocation, and later the release
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer -------------------------------------------------------
+      const uint32_t leader_full0 = map_to_cta(full0, 0);
+      int g = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * (2 * BM) + rank * BM;  // token tiles fastest: a weight tile stays in L2
+        const int n0 = (tile / tiles_m) * TILE_N;
+        const int w_row = MODE == OUT_SWIGLU ? (rank ? up_row_offset + n0 : n0) : n0 + rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % PAIR_STAGES;
+          const uint32_t phase = (g / PAIR_STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, phase ^ 1, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);  // this CTA's boxes and the peer's
+          tma_load_2d_pair(a_dst, &tmap_a, leader_full0 + 8 * s, kb * BK, m0);
+          tma_load_2d_pair(a_dst + A_BYTES, &tmap_w, leader_full0 + 8 * s, kb * BK, w_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {  // ---- MMA issuer of the pair ------------------------------------
+      constexpr uint32_t idesc = umma_idesc(2 * BM, PAIR_BN);
+      int g = 0, i = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++i) {
+        const int buf = i & 1;
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_flag);  // both epilogues have drained it
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem_base + buf * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % PAIR_STAGES;
+          const uint32_t phase = (g / PAIR_STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, phase, &abort_flag);  // both CTAs' boxes of the stage have landed
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(empty0 + 8 * s);  // both CTAs may refill the stage once these MMAs have read it
+        }
+        if (ok) umma_commit_pair(acc_full0 + 8 * buf);  // both epilogues: the tile is in tensor memory
+      }
+    }
+  } else {  // ---- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 of this CTA ------------------
+    const int quarter = warp & 3;
+    const uint32_t leader_acc_empty0 = map_to_cta(acc_empty0, 0);
+    int i = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++i) {
+      const int m0 = (tile % tiles_m) * (2 * BM) + rank * BM, n0 = (tile / tiles_m) * TILE_N;
+      const int buf = i & 1;
+      const int row = m0 + quarter * 32 + lane;
+      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, &abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+        const bool last = c0 + 32 >= TILE_N || n0 + c0 + 32 >= N;
+        if (n0 + c0 < N) {  // (uniform)
+          uint32_t acc[32];
+          tmem_load32(lane_addr + c0, acc);
+          float v[32];
+          if (MODE == OUT_SWIGLU) {
+            uint32_t up[32];
+            tmem_load32(lane_addr + 128 + c0, up);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float gate = __uint_as_float(acc[e]);
+              v[e] = (gate / (1.f + expf(-gate))) * __uint_as_float(up[e]);
+            }
+          } else {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(acc[e]);
+          }
+          if (last) {  // everything of this buffer is in registers: hand it back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) remote_arrive(leader_acc_empty0 + 8 * buf);
+          }
+          if (row < M) {
+            const int col = n0 + c0;
+            if (MODE == OUT_F32) {
+              float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
+              if (col + 32 <= N && (ldo & 3) == 0) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                  *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+              } else {
+                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = v[e];
+              }
+            } else {
+              bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
+              if (col + 32 <= N && (ldo & 7) == 0) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                  float chunk[8];
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) chunk[x] = v[e + x];
+                  store8(dst + e, chunk);
+                }
+              } else {
+                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+              }
+            }
+          }
+        }
+        if (last) break;
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the other still reads its shared memory or signals its barriers
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_word) atomicExch(error_word, 1);
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -348,7 +580,66 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int
   return q3_launch_status();
 }
 
+template <int MODE>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K, int up_offset,
+                int* error_word, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)PAIR_STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  static int pairs = 0;  // pairs of SMs the device runs at once with this kernel
+  if (!pairs) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
+    cfg.gridDim = dim3(sms / 2 * 2);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<MODE>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      return Q3_ERR_UNSUPPORTED;
+    }
+    pairs = n < sms / 2 ? n : sms / 2;
+  }
+  constexpr int TILE_N = MODE == OUT_SWIGLU ? 128 : PAIR_BN;
+  const int tiles = ((N + TILE_N - 1) / TILE_N) * ((M + 2 * BM - 1) / (2 * BM));
+  cfg.gridDim = dim3(2 * (tiles < pairs ? tiles : pairs));
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<MODE>, ta, tw, out, ldo, M, N, K,
+                                             up_offset, error_word);
+  return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
 }  // namespace
+
+// The same product on pairs of SMs (tcgen05 cta_group::2, tiles of 256 tokens x 256 features, for
+// SwiGLU 256 tokens x 128 gate + 128 up): same arguments and modes as q3_gemm_tcgen05.
+Q3_EXPORT int q3_gemm_tcgen05_pair(int mode, const void* x, int ldx, const void* W, int ldw, void* out, int ldo,
+                                   int M, int N, int K, int* error_word, cudaStream_t stream) {
+  if (!x || !W || !out || N < 1 || K < 1 || M < 0 || mode < 0 || mode > 2) return Q3_ERR_ARGUMENT;
+  if (ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return Q3_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return Q3_ERR_UNSUPPORTED;
+  if (M == 0) return Q3_OK;
+  CUtensorMap ta, tw;
+  const long w_rows = mode == OUT_SWIGLU ? 2L * N : N;
+  if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, 128)) return Q3_ERR_LAUNCH;
+  if (mode == OUT_SWIGLU) return launch_pair<OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
+  if (mode == OUT_F32) return launch_pair<OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
+  return launch_pair<OUT_BF16>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
+}
 
 // mode 0: out bf16 [M, N]; 1: out fp32 [M, N]; 2: W is [2 * N, K] (gate rows, then up rows from
 // row N), out bf16 [M, N] = silu(x W_gate^T) * (x W_up^T).  x, W bf16 with 16-byte aligned bases

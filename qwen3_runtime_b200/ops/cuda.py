@@ -94,6 +94,8 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "q3_gemm_tcgen05": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                             c_void_p],
+        "q3_gemm_tcgen05_pair": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p],
     },
     "sampling": {
         "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -120,6 +122,7 @@ class CudaOps:
             raise ValueError("large_gemm must be auto, tcgen05 or library")
         self.large_gemm = large_gemm
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
+        self.tcgen05_pairs = True           # False: the tcgen05 product never pairs SMs (cta_group::1 only)
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
         # Two variants of the split-KV kernel that are correct and tested but measured slower inside a
         # whole decode step on a B200 (batch 8, context 4096: 3.36 ms and 3.48 ms against 3.19 ms), so off:
@@ -401,9 +404,10 @@ class CudaOps:
             host.zero_()
             self.raise_if_kernel_error()
 
-    def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None):
+    def linear_tcgen05(self, x, weight, out=None, out_dtype=None, mode=None, pair=None):
         """``x @ weight^T`` on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).  ``mode=2``: SwiGLU with
-        ``weight = [W_gate; W_up]``, ``out`` is ``[M, I]``."""
+        ``weight = [W_gate; W_up]``, ``out`` is ``[M, I]``.  ``pair``: the kernel that runs each
+        256-token tile on two SMs (cta_group::2); default: when there are more than 128 tokens."""
         M, K = x.shape
         if not self._tcgen05_ok(x, weight):
             raise KernelError("gemm_tcgen05: bfloat16 operands with 16-byte aligned rows (K multiple of 8) only")
@@ -416,8 +420,11 @@ class CudaOps:
             mode = 1 if odt == torch.float32 else 0
         if out is None:
             out = torch.empty((M, N), dtype=odt, device=x.device)
-        self._call("gemm_tcgen05", "q3_gemm_tcgen05", "gemm_tcgen05", mode, _ptr(x), x.stride(0), _ptr(weight),
-                   weight.stride(0), _ptr(out), out.stride(0), M, N, K, _ptr(self._error_word(x.device)))
+        if pair is None:
+            pair = self.tcgen05_pairs and M > 128
+        self._call("gemm_tcgen05", "q3_gemm_tcgen05_pair" if pair else "q3_gemm_tcgen05", "gemm_tcgen05", mode,
+                   _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
+                   _ptr(self._error_word(x.device)))
         return out
 
     SMALL_M = 16

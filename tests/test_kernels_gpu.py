@@ -543,24 +543,26 @@ def test_gated_linear_small_m(ops, small_gemm, M, I, K):
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (2048, 6144, 2560),
                                    (300, 2560, 4096), (17, 304, 96), (64, 2560, 9728), (1000, 1000, 72),
                                    (129, 151936, 64)])
-def test_gemm_tcgen05(ops, M, N, K):
+@pytest.mark.parametrize("pair", [False, True], ids=["one SM", "two SMs"])
+def test_gemm_tcgen05(ops, M, N, K, pair):
     x = rand((M, K), torch.bfloat16, 62)
     w = rand((N, K), torch.bfloat16, 63, scale=0.05)
     want = x.float() @ w.float().t()
-    got = ops.linear_tcgen05(x, w)
+    got = ops.linear_tcgen05(x, w, pair=pair)
     ops.raise_if_kernel_error()
     close(got, want, torch.bfloat16, "tcgen05 linear", bf16_tol=1e-2)
-    got32 = ops.linear_tcgen05(x, w, out_dtype=torch.float32)
+    got32 = ops.linear_tcgen05(x, w, out_dtype=torch.float32, pair=pair)
     ops.raise_if_kernel_error()
     close(got32, want, torch.float32, "tcgen05 linear fp32 out", f32_tol=2e-5 * max(1.0, K / 256))
 
 
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 9728, 2560), (300, 112, 80), (77, 1000, 256)])
-def test_gemm_tcgen05_swiglu(ops, M, I, K):
+@pytest.mark.parametrize("pair", [False, True], ids=["one SM", "two SMs"])
+def test_gemm_tcgen05_swiglu(ops, M, I, K, pair):
     x = rand((M, K), torch.bfloat16, 64)
     w = rand((2 * I, K), torch.bfloat16, 65, scale=0.05)
     out = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
-    ops.linear_tcgen05(x, w, out=out, mode=2)
+    ops.linear_tcgen05(x, w, out=out, mode=2, pair=pair)
     ops.raise_if_kernel_error()
     g, u = x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t()
     close(out, torch.nn.functional.silu(g) * u, torch.bfloat16, "tcgen05 fused SwiGLU", bf16_tol=1e-2)
