@@ -523,6 +523,182 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   if (threadIdx.x == 0 && abort_flag && error_word) atomicExch(error_word, 1);
 }
 
+// ---- pairs of SMs, tiles of 256 tokens x 320 features --------------------------------------------
+// For outputs whose width leaves the 256-wide tiles one round short of filling the machine
+// (2560 features x 2048 tokens: 80 tiles for 74 pairs, two rounds) a wider tile can do it in
+// one: 64 tiles of 320.  An MMA takes at most 256 features, so a stage is multiplied by two MMAs
+// of 160 (80 feature rows from each CTA); the accumulator has 320 columns and a single buffer
+// (tensor memory has 512), so a pair's next tile waits for its epilogue.  Plain products only.
+// Accumulator column c belongs to MMA c / 160; inside it columns [0,80) are the leader's rows and
+// [80,160) the peer's: feature = n0 + 160 * (c % 160 / 80) + 80 * (c / 160) + c % 80.
+constexpr int WIDE = 320;
+constexpr int WIDE_STAGES = 5;
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                              void* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ error_word) {
+  static_assert(MODE != OUT_SWIGLU, "plain products only");
+  constexpr int HALF = WIDE / 2;             // feature rows of this CTA: 160
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = HALF * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 512;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * WIDE_STAGES + 2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_n = (N + WIDE - 1) / WIDE, tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[WIDE_STAGES]);
+  const uint32_t acc_full = smem_addr(&bars[2 * WIDE_STAGES]), acc_empty = smem_addr(&bars[2 * WIDE_STAGES + 1]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < WIDE_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer -------------------------------------------------------
+      const uint32_t leader_full0 = map_to_cta(full0, 0);
+      int g = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * (2 * BM) + rank * BM;
+        const int w_row = (tile / tiles_m) * WIDE + rank * HALF;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % WIDE_STAGES;
+          ok = mbar_wait(empty0 + 8 * s, ((g / WIDE_STAGES) & 1) ^ 1, &abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &tmap_a, leader_full0 + 8 * s, kb * BK, m0);
+          tma_load_2d_pair(a_dst + A_BYTES, &tmap_w, leader_full0 + 8 * s, kb * BK, w_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {  // ---- MMA issuer of the pair ------------------------------------
+      constexpr uint32_t idesc = umma_idesc(2 * BM, HALF);  // N = 160: 80 feature rows of each CTA
+      int g = 0, i = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++i) {
+        ok = mbar_wait(acc_empty, (i & 1) ^ 1, &abort_flag);  // both epilogues have drained the accumulator
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          const int s = g % WIDE_STAGES;
+          ok = mbar_wait(full0 + 8 * s, (g / WIDE_STAGES) & 1, &abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint64_t b_desc = umma_desc(a_addr + A_BYTES + j * (HALF / 2) * 128);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              umma_pair(tmem_base + j * HALF, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(empty0 + 8 * s);
+        }
+        if (ok) umma_commit_pair(acc_full);
+      }
+    }
+  } else {  // ---- epilogue ------------------------------------------------------------------------------
+    const int quarter = warp & 3;
+    const uint32_t leader_acc_empty = map_to_cta(acc_empty, 0);
+    int i = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++i) {
+      const int m0 = (tile % tiles_m) * (2 * BM) + rank * BM, n0 = (tile / tiles_m) * WIDE;
+      const int row = m0 + quarter * 32 + lane;
+      ok = mbar_wait(acc_full, i & 1, &abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < WIDE; c0 += 16) {
+        const int within = c0 % HALF;
+        const int col = n0 + HALF * (within / (HALF / 2)) + (HALF / 2) * (c0 / HALF) + within % (HALF / 2);
+        uint32_t acc[16];
+        tmem_load16(lane_addr + c0, acc);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 16 >= WIDE) {  // the accumulator is in registers: hand it back to the MMA issuer
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          if (lane == 0) remote_arrive(leader_acc_empty);
+        }
+        if (row < M && col < N) {
+          if (MODE == OUT_F32) {
+            float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
+            if (col + 16 <= N && (ldo & 3) == 0) {
+#pragma unroll
+              for (int e = 0; e < 16; e += 4)
+                *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(acc[e]), __uint_as_float(acc[e + 1]),
+                                                                  __uint_as_float(acc[e + 2]), __uint_as_float(acc[e + 3]));
+            } else {
+              for (int e = 0; e < 16 && col + e < N; ++e) dst[e] = __uint_as_float(acc[e]);
+            }
+          } else {
+            bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
+            if (col + 16 <= N && (ldo & 7) == 0) {
+#pragma unroll
+              for (int e = 0; e < 16; e += 8) {
+                float chunk[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) chunk[x] = __uint_as_float(acc[e + x]);
+                store8(dst + e, chunk);
+              }
+            } else {
+              for (int e = 0; e < 16 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(__uint_as_float(acc[e]));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_word) atomicExch(error_word, 1);
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -623,10 +799,65 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo
   return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
+// pairs of SMs that run at once (clusters of two blocks that each take a whole SM)
+int resident_pairs(const void* kernel, size_t smem) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms / 2 * 2);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n < sms / 2 ? n : sms / 2;
+}
+
+template <int MODE>
+int launch_pair_wide(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K,
+                     int* error_word, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)WIDE_STAGES * (BM * BK * 2 + (WIDE / 2) * BK * 2) + 1024;
+  static int pairs = -1;
+  if (pairs < 0) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_pair_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return Q3_ERR_LAUNCH;
+    pairs = resident_pairs((const void*)gemm_tcgen05_pair_wide_kernel<MODE>, smem);
+  }
+  if (pairs < 1) return Q3_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int tiles = ((N + WIDE - 1) / WIDE) * ((M + 2 * BM - 1) / (2 * BM));
+  cfg.gridDim = dim3(2 * (tiles < pairs ? tiles : pairs));
+  const cudaError_t err =
+      cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_wide_kernel<MODE>, ta, tw, out, ldo, M, N, K, error_word);
+  return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
 }  // namespace
 
 // The same product on pairs of SMs (tcgen05 cta_group::2, tiles of 256 tokens x 256 features, for
-// SwiGLU 256 tokens x 128 gate + 128 up): same arguments and modes as q3_gemm_tcgen05.
+// SwiGLU 256 tokens x 128 gate + 128 up; 256 x 320 where that saves a round of tiles): same
+// arguments and modes as q3_gemm_tcgen05.
 Q3_EXPORT int q3_gemm_tcgen05_pair(int mode, const void* x, int ldx, const void* W, int ldw, void* out, int ldo,
                                    int M, int N, int K, int* error_word, cudaStream_t stream) {
   if (!x || !W || !out || N < 1 || K < 1 || M < 0 || mode < 0 || mode > 2) return Q3_ERR_ARGUMENT;
@@ -635,6 +866,19 @@ Q3_EXPORT int q3_gemm_tcgen05_pair(int mode, const void* x, int ldx, const void*
   if (M == 0) return Q3_OK;
   CUtensorMap ta, tw;
   const long w_rows = mode == OUT_SWIGLU ? 2L * N : N;
+  if (mode != OUT_SWIGLU) {
+    // tile width: rounds of one tile per pair x columns per tile (+24 when the wide tile's
+    // epilogue cannot overlap the next tile's MMAs)
+    const long tiles_m = (M + 2 * BM - 1) / (2 * BM);
+    const long pairs = 74;
+    const long cost_256 = ((tiles_m * ((N + PAIR_BN - 1) / PAIR_BN) + pairs - 1) / pairs) * PAIR_BN;
+    const long cost_wide = ((tiles_m * ((N + WIDE - 1) / WIDE) + pairs - 1) / pairs) * (WIDE + 24);
+    if (cost_wide < cost_256) {
+      if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, WIDE / 2)) return Q3_ERR_LAUNCH;
+      return mode == OUT_F32 ? launch_pair_wide<OUT_F32>(ta, tw, out, ldo, M, N, K, error_word, stream)
+                             : launch_pair_wide<OUT_BF16>(ta, tw, out, ldo, M, N, K, error_word, stream);
+    }
+  }
   if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, 128)) return Q3_ERR_LAUNCH;
   if (mode == OUT_SWIGLU) return launch_pair<OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
   if (mode == OUT_F32) return launch_pair<OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);

@@ -542,7 +542,7 @@ def test_gated_linear_small_m(ops, small_gemm, M, I, K):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (2048, 6144, 2560),
                                    (300, 2560, 4096), (17, 304, 96), (64, 2560, 9728), (1000, 1000, 72),
-                                   (129, 151936, 64)])
+                                   (129, 151936, 64), (2048, 2560, 4096), (2048, 2500, 96), (1900, 2564, 200)])
 @pytest.mark.parametrize("pair", [False, True], ids=["one SM", "two SMs"])
 def test_gemm_tcgen05(ops, M, N, K, pair):
     x = rand((M, K), torch.bfloat16, 62)
