@@ -295,6 +295,33 @@ def test_prefill_attention_tcgen05_matches_mma_kernel(ops, nq, nkv, ps):
     close(tc, want, torch.bfloat16, "tcgen05 prefill", bf16_tol=1e-2)
 
 
+def test_attention_kernels_at_long_contexts(ops, decode_loader):
+    """Tens of thousands of keys: many slices and pages for the split-KV kernel, many tiles and an
+    odd number of row blocks for the tcgen05 kernel (checked against the mma.sync kernel, the
+    plain statement being too slow here)."""
+    nq, nkv, D, ps = 8, 2, 128, 16
+    lens = [30000, 17, 4097]
+    pr = decode_problem(nq, nkv, D, ps, lens, 95)
+    want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16)
+    for splits in (None, 7, 23):
+        got = run_decode(ops, pr, nq, nkv, D, ps, lens, splits=splits)
+        close(got, want, torch.bfloat16, f"decode attention at 30000 keys, splits={splits}", bf16_tol=1e-2)
+    lens, qlens = [9000, 300], [4100, 300]   # a portion of a long prompt after 4900 cached tokens
+    pr = attention_problem(nq, nkv, D, ps, lens, qlens, torch.bfloat16, 96)
+    step = step_for(lens, qlens)
+    outs = {}
+    for which in ("tcgen05", "mma"):
+        ops.prefill_attention = which
+        outs[which] = torch.full((pr["T"], nq * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D, k_pages=pr["k"],
+                            v_pages=pr["v"], block_table=pr["bt"], token_seq=pr["seq"], positions=pr["pos"],
+                            out=outs[which], page_size=ps, scale=1 / math.sqrt(D), window=None, step=step)
+    ops.prefill_attention = "tcgen05"
+    ops.raise_if_kernel_error()
+    assert torch.isfinite(outs["tcgen05"]).all()
+    close(outs["tcgen05"], outs["mma"].float(), torch.bfloat16, "tcgen05 prefill at 9000 keys", bf16_tol=1e-2)
+
+
 def test_prefill_attention_far_key_diagonal_and_poison(ops):
     nq, nkv, D, ps = 8, 2, 128, 16
     lens, qlens = [900, 257], [300, 257]
