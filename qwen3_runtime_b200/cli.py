@@ -23,6 +23,8 @@ import sys
 def _generate(argv: list[str]) -> int:
     parser = argparse.ArgumentParser(prog="qwen3_runtime_b200.cli")
     parser.add_argument("--model", default=os.environ.get("QWEN3_RUNTIME_MODEL"))
+    parser.add_argument("--pin-path", default=None,
+                        help="a config.json that the model folder has to match (refuse any other model)")
     parser.add_argument("--max-tokens", type=int, default=8)
     parser.add_argument("--prompt-tokens", type=int, nargs="+", default=[151643, 8948, 198, 2610])
     parser.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=None,
@@ -45,7 +47,8 @@ def _generate(argv: list[str]) -> int:
 
     engine = build_engine(args.model, max_num_seqs=args.max_num_seqs,
                           max_num_batched_tokens=args.max_num_batched_tokens, block_size=args.block_size,
-                          dtype=args.dtype, num_kv_blocks=args.num_kv_blocks, cuda_graph=args.cuda_graph)
+                          dtype=args.dtype, num_kv_blocks=args.num_kv_blocks, cuda_graph=args.cuda_graph,
+                          pin_path=args.pin_path)
     sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                               seed=args.seed)
     out = engine.generate(args.prompt_tokens, max_tokens=args.max_tokens, sampling=sampling)

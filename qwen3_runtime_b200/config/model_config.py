@@ -25,6 +25,10 @@ def _require(raw: Mapping[str, Any], key: str) -> Any:
 class Qwen3Config:
     """Hyper-parameters of a Qwen3 dense decoder (qwen3_runtime/models/qwen3.py:19-31)."""
 
+    # what a pinned config.json is compared on (qwen3_runtime/utils/loader.py:20-30)
+    pin_fields = ("hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
+                  "intermediate_size", "vocab_size", "rope_theta", "tie_word_embeddings")
+
     vocab_size: int
     hidden_size: int
     num_hidden_layers: int

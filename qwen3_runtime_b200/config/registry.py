@@ -63,8 +63,25 @@ def read_config_json(model_dir: str | Path) -> dict[str, Any]:
     return json.loads(path.read_text())
 
 
-def load_config(model_dir: str | Path) -> tuple[Architecture, Any]:
-    """``(architecture, typed config)`` for a model folder."""
+def check_against_pin(config: Any, pinned: Any, pin_path: str | Path) -> None:
+    """The model a deployment expects, as a pinned config.json: every size that decides the
+    tensors' shapes and the arithmetic has to agree (qwen3_runtime/utils/loader.py:20-30, 57-60
+    compares the raw keys; here the typed configs, so a defaulted ``head_dim`` counts too).
+    ``max_position_embeddings`` and the norms' eps may differ, as in the reference."""
+    keys = getattr(config, "pin_fields", None) or [f for f in vars(config)]
+    wrong = [f"{k}={getattr(config, k)!r} (pin {getattr(pinned, k)!r})" for k in keys
+             if getattr(config, k) != getattr(pinned, k)]
+    if wrong:
+        raise ConfigError(f"config.json does not match the pinned model {pin_path}: " + ", ".join(wrong))
+
+
+def load_config(model_dir: str | Path, pin_path: str | Path | None = None) -> tuple[Architecture, Any]:
+    """``(architecture, typed config)`` for a model folder; with ``pin_path`` (a config.json of
+    the model that is expected) a folder that holds another model is refused."""
     raw = read_config_json(model_dir)
     arch = resolve_architecture(raw)
-    return arch, arch.config_class.from_hf_config(raw)
+    config = arch.config_class.from_hf_config(raw)
+    if pin_path is not None:
+        pin_raw = json.loads(Path(pin_path).read_text())
+        check_against_pin(config, resolve_architecture(pin_raw).config_class.from_hf_config(pin_raw), pin_path)
+    return arch, config

@@ -42,9 +42,12 @@ def build_model(config, source, *, dtype: str = "bfloat16", device="cuda", ops=N
     return model
 
 
-def load_model(model_dir: str | Path, *, dtype: str = "bfloat16", device="cuda", ops=None):
-    """``(model, typed config, raw config.json)`` from a folder with config.json and safetensors."""
-    _arch, config = load_config(model_dir)
+def load_model(model_dir: str | Path, *, dtype: str = "bfloat16", device="cuda", ops=None,
+               pin_path: str | Path | None = None):
+    """``(model, typed config, raw config.json)`` from a folder with config.json and safetensors.
+    ``pin_path``: a config.json that the folder's model has to match (checked before any weight
+    is read)."""
+    _arch, config = load_config(model_dir, pin_path)
     model = build_model(config, SafetensorsDir(model_dir), dtype=dtype, device=device, ops=ops)
     return model, config, read_config_json(model_dir)
 
@@ -94,14 +97,14 @@ def build_engine(model_dir: str | Path | None = None, *, max_num_seqs: int = 8, 
                  block_size: int = 16, dtype: str = "bfloat16", num_kv_blocks: int | None = None,
                  kv_budget: int | None = None, cuda_graph: bool | None = None, eos_token_id: int | None = None,
                  device="cuda", ops=None, model: DecoderModel | None = None, config=None,
-                 max_positions: int | None = None) -> Engine:
+                 max_positions: int | None = None, pin_path: str | Path | None = None) -> Engine:
     """An :class:`Engine` for a model folder (or an already built ``model`` with its ``config``)."""
     dtype = canonical_dtype(dtype)
     raw: dict = {}
     if model is None:
         if model_dir is None:
             raise ValueError("give a model folder or a built model")
-        model, config, raw = load_model(model_dir, dtype=dtype, device=device, ops=ops)
+        model, config, raw = load_model(model_dir, dtype=dtype, device=device, ops=ops, pin_path=pin_path)
     if max_positions is None:
         max_positions = int(getattr(config, "max_position_embeddings"))
     if cuda_graph is None:

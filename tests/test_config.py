@@ -94,3 +94,18 @@ def test_engine_config():
                 dict(num_kv_blocks=0)):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
+
+
+def test_pinned_config_refuses_another_model(tmp_path):
+    """A deployment may pin the model it expects (a config.json); a folder with another model is
+    refused before a weight is read, with every differing size in the message; sizes that do
+    not shape tensors or arithmetic (context length, eps) may differ."""
+    cfg = TINY["B"]["config"]
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_hf_config()))
+    pin = tmp_path / "pin.json"
+    pin.write_text(json.dumps({**cfg.to_hf_config(), "max_position_embeddings": 77, "rms_norm_eps": 1e-3}))
+    assert load_config(tmp_path, pin)[1] == cfg
+    pin.write_text(json.dumps(_raw(num_hidden_layers=cfg.num_hidden_layers + 1, rope_theta=123.0)))
+    with pytest.raises(ConfigError) as err:
+        load_config(tmp_path, pin)
+    assert "num_hidden_layers" in str(err.value) and "rope_theta" in str(err.value) and "vocab_size" not in str(err.value)
