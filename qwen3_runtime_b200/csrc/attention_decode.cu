@@ -599,19 +599,15 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
                   int num_splits, const NewToken& nt, long num_rows_kv, int* error_word, int cluster_merge,
                   cudaStream_t stream) {
-  static int stages = 0;
-  if (!stages) {
-    const char* v = getenv("Q3_DECODE_STAGES");
-    stages = v ? atoi(v) : 2;
-    if (stages < 2 || stages > MAX_STAGES || (!TMA && stages > 3)) stages = 2;
-  }
+  const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
   const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4 + 16 * D * 4 + 16 * 4;
   const size_t smem = 16 * D * 2 + (FUSED ? 2 * D * 2 : 0) + (pipe > merge ? pipe : merge);
   if (smem > 227 * 1024) return Q3_ERR_UNSUPPORTED;
   cluster_merge = cluster_merge && num_splits > 1 && num_splits <= 8;
   if (num_splits > 1 && !cluster_merge && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)

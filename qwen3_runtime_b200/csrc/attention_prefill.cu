@@ -258,7 +258,8 @@ int launch_prefill(const bf16* q, int q_stride, const bf16* kpages, const bf16* 
                    int max_pages, const int* kv_lens, const int* cu_seqlens, bf16* out, int num_seqs, int num_work,
                    int nq, int nkv, int ps, float scale, int window, int skip_single, cudaStream_t stream) {
   const size_t smem = (size_t)BLOCK_M * D * 2 + (size_t)STAGES * 2 * TILE * D * 2;
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)

@@ -554,7 +554,8 @@ Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num
            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return Q3_ERR_LAUNCH;
   }
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
         cudaSuccess)

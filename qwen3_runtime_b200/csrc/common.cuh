@@ -18,6 +18,15 @@ typedef __nv_bfloat16 bf16;
 
 #define Q3_EXPORT extern "C" __attribute__((visibility("default")))
 
+// Kernel attributes (opt-in shared memory sizes) and occupancy answers belong to a device: "done
+// once" flags are kept per device.
+#define Q3_MAX_DEVICES 64
+static inline int q3_current_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= Q3_MAX_DEVICES) device = 0;
+  return device;
+}
+
 static inline int q3_launch_status() {
   return cudaGetLastError() == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }

@@ -298,7 +298,8 @@ cudaError_t launch_stream(const void* kernel, int blocks, int cluster, size_t sm
 // runs at once; clusters live inside one GPC, so this can be less than SMs / cluster.
 int resident_clusters(const void* kernel, int cluster, int sm_count) {
   if (cluster == 1) return sm_count;
-  static int cached[9] = {0};
+  static int cached_on[Q3_MAX_DEVICES][9];
+  int* cached = cached_on[q3_current_device()];
   if (!cached[cluster]) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count / cluster * cluster);
@@ -362,7 +363,8 @@ template <int MODE, bool HI>
 int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, int M, int N, int K, int up_offset,
            int sm_count, int only_large, int* error_word, cudaStream_t stream) {
   const void* kernel = (const void*)gemm_stream_kernel<MODE, HI>;
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess)
       return Q3_ERR_LAUNCH;
@@ -381,7 +383,8 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
 }
 
 int sm_count_of_current_device() {
-  static int count = 0;
+  static int count_on[Q3_MAX_DEVICES];
+  int& count = count_on[q3_current_device()];
   if (!count) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess ||

@@ -705,6 +705,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+int sm_count() {
+  static int count_on[Q3_MAX_DEVICES];
+  int& count = count_on[q3_current_device()];
+  if (!count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count < 2) count = 148;
+  }
+  return count;
+}
+
 EncodeTiledFn encode_fn() {
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
@@ -736,20 +747,15 @@ template <int BN, int NB, int MODE>
 int launch(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K, int up_offset,
            int* error_word, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, NB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return Q3_ERR_LAUNCH;
     configured = true;
   }
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms < 1)
-      num_sms = 148;
-  }
+  const int num_sms = sm_count();
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   const int grid = tiles < num_sms ? tiles : num_sms;  // one persistent block per SM
   gemm_tcgen05_kernel<BN, NB, MODE><<<grid, THREADS, smem, stream>>>(ta, tw, out, ldo, M, N, K, up_offset, error_word);
@@ -760,7 +766,8 @@ template <int MODE>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K, int up_offset,
                 int* error_word, cudaStream_t stream) {
   constexpr size_t smem = (size_t)PAIR_STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024;
-  static bool configured = false;
+  static bool configured_on[Q3_MAX_DEVICES];
+  bool& configured = configured_on[q3_current_device()];
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
@@ -778,11 +785,10 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  static int pairs = 0;  // pairs of SMs the device runs at once with this kernel
+  static int pairs_on[Q3_MAX_DEVICES];  // pairs of SMs the device runs at once with this kernel
+  int& pairs = pairs_on[q3_current_device()];
   if (!pairs) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
+    const int sms = sm_count();
     cfg.gridDim = dim3(sms / 2 * 2);
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<MODE>, &cfg) != cudaSuccess || n < 1) {
@@ -801,9 +807,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo
 
 // pairs of SMs that run at once (clusters of two blocks that each take a whole SM)
 int resident_pairs(const void* kernel, size_t smem) {
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
+  const int sms = sm_count();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sms / 2 * 2);
   cfg.blockDim = dim3(THREADS);
@@ -827,12 +831,14 @@ template <int MODE>
 int launch_pair_wide(const CUtensorMap& ta, const CUtensorMap& tw, void* out, int ldo, int M, int N, int K,
                      int* error_word, cudaStream_t stream) {
   constexpr size_t smem = (size_t)WIDE_STAGES * (BM * BK * 2 + (WIDE / 2) * BK * 2) + 1024;
-  static int pairs = -1;
-  if (pairs < 0) {
+  static int pairs_on[Q3_MAX_DEVICES];  // 0: not asked yet, -1: none
+  int& pairs = pairs_on[q3_current_device()];
+  if (pairs == 0) {
     if (cudaFuncSetAttribute(gemm_tcgen05_pair_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return Q3_ERR_LAUNCH;
     pairs = resident_pairs((const void*)gemm_tcgen05_pair_wide_kernel<MODE>, smem);
+    if (pairs < 1) pairs = -1;
   }
   if (pairs < 1) return Q3_ERR_UNSUPPORTED;
   cudaLaunchConfig_t cfg = {};
@@ -870,7 +876,7 @@ Q3_EXPORT int q3_gemm_tcgen05_pair(int mode, const void* x, int ldx, const void*
     // tile width: rounds of one tile per pair x columns per tile (+24 when the wide tile's
     // epilogue cannot overlap the next tile's MMAs)
     const long tiles_m = (M + 2 * BM - 1) / (2 * BM);
-    const long pairs = 74;
+    const long pairs = sm_count() / 2;
     const long cost_256 = ((tiles_m * ((N + PAIR_BN - 1) / PAIR_BN) + pairs - 1) / pairs) * PAIR_BN;
     const long cost_wide = ((tiles_m * ((N + WIDE - 1) / WIDE) + pairs - 1) / pairs) * (WIDE + 24);
     if (cost_wide < cost_256) {
@@ -904,7 +910,7 @@ Q3_EXPORT int q3_gemm_tcgen05(int mode, const void* x, int ldx, const void* W, i
     long best = -1;
     for (int cand : {256, 192, 160, 128}) {
       const long tiles = (long)tiles_m * ((N + cand - 1) / cand);
-      const long cost = ((tiles + 147) / 148) * (cand + 24);
+      const long cost = ((tiles + sm_count() - 1) / sm_count()) * (cand + 24);
       if (best < 0 || cost < best) {
         best = cost;
         bn = cand;

@@ -142,6 +142,7 @@ class CudaOps:
             raise KernelsUnavailable(
                 f"the kernels are compiled for sm_100a; this device reports sm_{major}{_minor}"
             )
+        self.SM_COUNT = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self._fn: dict[str, ctypes._CFuncPtr] = {}
         self.launches = 0  # kernels of this engine launched (or captured) through this table
         if groups:
@@ -269,7 +270,7 @@ class CudaOps:
                   head_dim, page_size, float(scale), int(window or 0))
         return out
 
-    SM_COUNT = 148
+    SM_COUNT = 148  # of a B200; replaced by the device's own count when the table is built
     DECODE_MIN_KEYS_PER_SPLIT = 256
 
     DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
