@@ -44,13 +44,15 @@ __global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restri
 }
 
 // The same with 16-byte accesses: H a multiple of 8 and every row 16-byte aligned.
-template <typename T>
+// REGS: the block has a thread for every 8 elements of a row, so a thread's 8 values stay in
+// registers between the two passes (no staging through shared memory).
+template <typename T, bool REGS>
 __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __restrict__ resid,
                                       const int* __restrict__ ids, const T* __restrict__ table,
                                       const int* __restrict__ rows, const float* __restrict__ w,
                                       T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
   extern __shared__ float vals[];
-  float* red = vals + H;
+  float* red = REGS ? vals : vals + H;
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -64,6 +66,7 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
   const T* prow = pending ? pending + src * H : nullptr;
   float* rrow = resid ? resid + src * H : nullptr;
   float ss = 0.f;
+  float mine[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float v[8];
     if (trow) load8(trow + i, v); else load8(rrow + i, v);
@@ -74,7 +77,12 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
       for (int e = 0; e < 8; ++e) v[e] += pv[e];
     }
     if (write_resid) store8(rrow + i, v);
-    store8(vals + i, v);
+    if (REGS) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mine[e] = v[e];
+    } else {
+      store8(vals + i, v);
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
   }
@@ -83,7 +91,12 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
   T* orow = out + (long)r * H;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float v[8], wv[8];
-    load8(vals + i, v);
+    if (REGS) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = mine[e];
+    } else {
+      load8(vals + i, v);
+    }
     load8(w + i, wv);
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = (v[e] * rstd) * wv[e];
@@ -106,11 +119,17 @@ static int launch_fused_norm(const void* pending, float* resid, const int* ids, 
                    aligned16(out);
   if (vec) {
     if (smem > 48 * 1024)
-      cudaFuncSetAttribute(fused_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(fused_norm_vec_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int threads = ((H / 8 + 31) / 32) * 32;
     threads = threads > 1024 ? 1024 : threads;
-    return launch_pdl(fused_norm_vec_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending, resid,
-                      ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+    if (threads * 8 >= H)  // one chunk per thread: the values stay in registers
+      return launch_pdl(fused_norm_vec_kernel<T, true>, dim3(num_rows), dim3(threads), 33 * sizeof(float), stream,
+                        (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid,
+                        vocab) == cudaSuccess
+                 ? Q3_OK
+                 : Q3_ERR_LAUNCH;
+    return launch_pdl(fused_norm_vec_kernel<T, false>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending,
+                      resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
                ? Q3_OK
                : Q3_ERR_LAUNCH;
   }
