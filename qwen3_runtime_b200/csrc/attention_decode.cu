@@ -16,10 +16,10 @@
 // to scratch (mid_o [seqs, nq, splits, D] fp32, mid_lse [seqs, nq, splits]); a second
 // kernel merges the splits (triton_decode.py:447-501).  Slices are cut at multiples of 64
 // keys counted from the first visible key, so an empty slice writes lse = -inf.
-#include <cuda.h>
 #include <string.h>
 
-#include "common.cuh"
+#define Q3_WAIT_LIMIT_CYCLES 400000000ll
+#include "async_tiles.cuh"
 #include "mma_tiles.cuh"
 
 namespace {
@@ -31,42 +31,7 @@ namespace {
 // keeps DRAM far busier than 16-byte copies spread over threads.  Tile layout: D/64 slabs of
 // [64 keys][128 bytes]; chunk c of key r of slab h sits at h*8192 + r*128 + ((c ^ (r & 7)) * 16).
 constexpr int MAX_STAGES = 4;
-constexpr long long WAIT_LIMIT_CYCLES = 400000000ll;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded; on expiry the error word is set and the caller carries on with whatever is there.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* error_word) {
-  if (mbar_try_wait(bar, parity)) return;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
-      if (error_word) atomicExch(error_word, 4);
-      return;
-    }
-  }
-}
-__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
 template <int D, bool TMA> __device__ __forceinline__ int kv_off(int row, int chunk) {
   if (TMA) return (chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
   return swz<D>(row, chunk);
@@ -97,20 +62,15 @@ constexpr int THREADS = WARPS * 32;
 // every block's partials through distributed shared memory in slice order (the arithmetic of
 // decode_combine_kernel, so the bits are the same), and a second barrier keeps every block's
 // shared memory alive until all have read it.
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float ld_cluster(const float* local, uint32_t rank) {
-  uint32_t addr;
   float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(smem_u32(local), rank)) : "memory");
   return v;
 }
 template <int D>
 __device__ __forceinline__ void cluster_merge_slices(const float* part_o, const float* part_lse, int G, int rank,
                                                      int num_splits, bf16* __restrict__ out_row) {
-  cluster_barrier();
+  cluster_sync_all();
   const int total = G * D;
   const int share = (total + num_splits - 1) / num_splits;
   const int hi = min(total, (rank + 1) * share);
@@ -128,7 +88,7 @@ __device__ __forceinline__ void cluster_merge_slices(const float* part_o, const 
     }
     out_row[idx] = __float2bfloat16_rn(acc / wsum);
   }
-  cluster_barrier();
+  cluster_sync_all();
 }
 
 // FUSED: `q` is the raw q/k/v projection; the block norms and rotates its own queries, and the
@@ -161,7 +121,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   if (TMA) {
     if (threadIdx.x == 0) {
       for (int i = 0; i < stages; ++i) mbar_init(smem_u32(full_bar + i), 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      mbar_init_fence();
     }
     __syncthreads();
   }
@@ -247,7 +207,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
         if (page < 0) continue;
         const int y = (page * nkv + kvh) * ps + (j0 % ps);
         unsigned char* dst = (which ? v_dst : k_dst) + h * (TILE * 128) + j * box_rows * 128;
-        tma_box(smem_u32(dst), which ? &map_v : &map_k, bar, h * 64, y);
+        tma_load_2d(smem_u32(dst), which ? &map_v : &map_k, bar, h * 64, y);
       }
       return;
     }
@@ -377,7 +337,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
 
   for (int tile = 0; tile < num_tiles; ++tile) {
     if (TMA) {
-      mbar_wait(smem_u32(full_bar + tile % stages), (tile / stages) & 1, error_word);
+      mbar_wait_report(smem_u32(full_bar + tile % stages), (tile / stages) & 1, error_word, 4);
     } else {
       if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
     }
@@ -564,35 +524,6 @@ __global__ void decode_combine_kernel(const float* __restrict__ mid_o, const flo
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// Pages as a matrix [rows of all pages and kv heads][D]; a box is [box_rows][64 dims], swizzled.
-bool page_map(CUtensorMap* map, const void* pages, long num_rows_kv, int D, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_rows_kv};
-  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  const cuuint32_t es[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D, bool FUSED, bool TMA>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
@@ -619,7 +550,9 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
   memset(&map_v, 0, sizeof map_v);
   if (TMA) {
     const int box_rows = ps < TILE ? ps : TILE;
-    if (!page_map(&map_k, kpages, num_rows_kv, D, box_rows) || !page_map(&map_v, vpages, num_rows_kv, D, box_rows))
+    // pages as a matrix [rows of all pages and kv heads][D]; a box is [box_rows][64 dims], swizzled
+    if (!q3_bf16_map(&map_k, kpages, num_rows_kv, D, D, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
+        !q3_bf16_map(&map_v, vpages, num_rows_kv, D, D, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
       return Q3_ERR_LAUNCH;
   }
   dim3 grid(num_splits, nkv, num_seqs);

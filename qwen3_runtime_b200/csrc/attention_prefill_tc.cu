@@ -30,9 +30,7 @@
 // Keys past a block's last position are zeroed in shared memory before PV (stale or poisoned
 // page contents must not meet a zero probability).  Every mbarrier wait is bounded; on expiry
 // the block raises its abort flag and the global error word, frees TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "async_tiles.cuh"
 
 namespace {
 
@@ -40,7 +38,6 @@ constexpr int D = 128;
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
 constexpr int THREADS = 352;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 32 KB: two halves of [128 rows][128 B]
 constexpr int KV_BYTES = BLOCK_N * D * 2;       // 16 KB: two halves of [64 rows][128 B]
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB: [128 rows][128 B]
@@ -49,89 +46,6 @@ constexpr int SMEM_BYTES = 2 * Q_BYTES + 2 * KV_STAGES * KV_BYTES + 4 * P_BYTES 
 constexpr int TMEM_COLS = 512;                  // per row block: S0 [0,64), S1 [64,128), O [128,256)
 constexpr int TMEM_BLOCK = 256;
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-// K-major tile [rows][64] bf16, 128-byte swizzle: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// MN-major operand (rows = K index, 64 contiguous N per 128-byte row), 128-byte swizzle:
-// leading offset = distance between 64-wide blocks of N, stride offset = 8 rows of K.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t n_block_bytes) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(n_block_bytes >> 4) << 16) |
-         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                     uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
 // 2^x in one instruction (exp2f adds range fix-ups around the same instruction; results
 // below 2^-126 become zero here, which is what a probability that small is worth)
 __device__ __forceinline__ float ex2(float x) {
@@ -289,8 +203,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         // tile and a plain arrival (after the tile's "full") from one that had no use for it.
         const int x = warp == 1 ? 0 : 1;
         const int my_tiles = tiles[x];
-        constexpr uint32_t idesc_s = idesc_bf16(BLOCK_M, BLOCK_N, 0);   // S = Q K^T: N = 64 keys
-        constexpr uint32_t idesc_pv = idesc_bf16(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
+        constexpr uint32_t idesc_s = umma_idesc(BLOCK_M, BLOCK_N, 0);   // S = Q K^T: N = 64 keys
+        constexpr uint32_t idesc_pv = umma_idesc(BLOCK_M, D, 1);        // PV: N = 128, V MN-major
         const uint32_t p_addr = smem_addr(p_s) + 2 * x * P_BYTES;
         const uint32_t q_addr = smem_addr(q_s) + x * Q_BYTES;
         const uint32_t tmem_x = tmem + x * TMEM_BLOCK;
@@ -307,8 +221,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t half = (k >> 2), sub = (k & 3) * 2;  // 4 steps of 32 bytes per 64-wide half
-            umma(tmem_x + sbuf * BLOCK_N, desc_kmajor(q_addr + half * (Q_BYTES / 2)) + sub,
-                 desc_kmajor(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tmem_x + sbuf * BLOCK_N, umma_desc(q_addr + half * (Q_BYTES / 2)) + sub,
+                 umma_desc(k_addr + half * (KV_BYTES / 2)) + sub, idesc_s, k > 0 ? 1u : 0u);
           }
           umma_commit(bar(BAR_K_EMPTY + st));           // this block is done with the key tile
           umma_commit(bar(BAR_S_FULL + 2 * x + sbuf));  // S_j is in TMEM
@@ -329,8 +243,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             const uint32_t v_addr = smem_addr(v_s) + st * KV_BYTES;
 #pragma unroll
             for (int k = 0; k < BLOCK_N / 16; ++k)  // 16 keys: 32 bytes along P's rows, 2 KB down V's rows
-              umma(tmem_x + 2 * BLOCK_N, desc_kmajor(p_addr + pbuf * P_BYTES) + 2 * k,
-                   desc_mnmajor(v_addr + k * 2048, KV_BYTES / 2), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+              umma_bf16(tmem_x + 2 * BLOCK_N, umma_desc(p_addr + pbuf * P_BYTES) + 2 * k,
+                   umma_desc_mn_major(v_addr + k * 2048, KV_BYTES / 2), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             umma_commit(bar(BAR_V_EMPTY + st));
             umma_commit(bar(BAR_PV_FULL + x));
           } else {
@@ -496,22 +410,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   if (tid == 0 && abort_flag && error_word) atomicExch(error_word, 2);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 }  // namespace
 
 // q: the QKV buffer, [num_tokens, *] bf16 with row stride q_stride (elements), head h at column
@@ -531,7 +429,7 @@ Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num
       nkv > 65535 || (((uintptr_t)q | (uintptr_t)kpages | (uintptr_t)vpages) & 15))
     return Q3_ERR_UNSUPPORTED;
   if (num_work == 0) return Q3_OK;
-  EncodeTiledFn fn = encode_fn();
+  Q3EncodeTiledFn fn = q3_encode_tiled();
   if (!fn) return Q3_ERR_LAUNCH;
   CUtensorMap tq, tk, tv;
   {
@@ -544,16 +442,10 @@ Q3_EXPORT int q3_paged_attention_prefill_tc(const void* q, int q_stride, int num
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return Q3_ERR_LAUNCH;
   }
-  for (int which = 0; which < 2; ++which) {
-    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_rows_kv};
-    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)ps};
-    const cuuint32_t es[2] = {1, 1};
-    if (fn(which ? &tv : &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? vpages : kpages), dims,
-           strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return Q3_ERR_LAUNCH;
-  }
+  // pages as a matrix [rows of all pages and kv heads][D], read in boxes of one page x 64 dims
+  if (!q3_bf16_map(&tk, kpages, num_rows_kv, D, D, ps, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
+      !q3_bf16_map(&tv, vpages, num_rows_kv, D, D, ps, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+    return Q3_ERR_LAUNCH;
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
   if (!configured) {

@@ -27,7 +27,8 @@
 //
 // Every mbarrier wait is bounded; on expiry the waiter sets the error word and carries on
 // (the result is then invalid, and the host raises), so no barrier is ever abandoned.
-#include "common.cuh"
+#define Q3_WAIT_LIMIT_CYCLES 400000000ll
+#include "async_tiles.cuh"
 
 namespace {
 
@@ -39,64 +40,7 @@ constexpr int MAX_STAGES = 8;
 constexpr int MAX_LED = 16;                // units a block may lead in a cluster (slots are used once)
 constexpr int SMEM_LIMIT = 226 * 1024;     // dynamic; the barriers are static
 constexpr int RED_BYTES = 2 * CONSUMER_WARPS * 4 * 32 * 4;  // two buffers of the warps' tiles
-constexpr long long WAIT_LIMIT_CYCLES = 400000000ll;
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; on expiry records `code` in the error word and returns (the caller carries on).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* error_word, int code) {
-  if (mbar_try_wait(bar, parity)) return;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
-      atomicExch(error_word, code);
-      return;
-    }
-  }
-}
-__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -147,7 +91,7 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
     }
     for (int i = 0; i < plan.led; ++i) mbar_init(slot_bar0 + 8 * i, 128 * (plan.parts - 1));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (K & 31) {  // the tail of the last k-block is read but never copied: keep it finite
     for (int i = threadIdx.x * 16; i < plan.stages * stage_bytes; i += THREADS * 16)
@@ -162,7 +106,7 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     const uint32_t bytes_row = (uint32_t)klen * 2;
     for (int u = 0; u < my_units; ++u) {
       const int s = u % plan.stages;
-      if (u >= plan.stages) mbar_wait(empty0 + 8 * s, ((u / plan.stages) & 1) ^ 1, error_word, 1);
+      if (u >= plan.stages) mbar_wait_report(empty0 + 8 * s, ((u / plan.stages) & 1) ^ 1, error_word, 1);
       const int row0 = (first_panel + u * panel_step) * FPP;
       const int rows_live = min(FPP, N - row0);  // per half for SwiGLU: gate rows, then up rows
       if (lane == 0) mbar_expect_tx(full0 + 8 * s, bytes_row * rows_live * (ROWS / FPP));
@@ -193,7 +137,7 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   for (int u = 0; u < my_units; ++u) {
     const int s = u % plan.stages;
     const int panel = first_panel + u * panel_step;
-    mbar_wait(full0 + 8 * s, (u / plan.stages) & 1, error_word, 2);
+    mbar_wait_report(full0 + 8 * s, (u / plan.stages) & 1, error_word, 2);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned char* base = smem + (size_t)s * stage_bytes + g * plan.pitch + 16 * t;
 #pragma unroll
@@ -223,19 +167,17 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         const int leader = u % plan.parts, li = u / plan.parts;
         if (part != leader) {
           const int idx = part < leader ? part : part - 1;
-          const uint32_t dst = map_to_rank(smem_addr(slots + ((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x),
+          const uint32_t dst = map_to_cta(smem_addr(slots + ((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x),
                                            leader);
           asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(v) : "memory");
-          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
-                           map_to_rank(slot_bar0 + 8 * li, leader))
-                       : "memory");
+          remote_arrive(map_to_cta(slot_bar0 + 8 * li, leader));
           emit = false;
         } else {
           const uint32_t bar = slot_bar0 + 8 * li;
           if (!mbar_try_wait_cluster(bar, 0)) {
             const long long start = clock64();
             while (!mbar_try_wait_cluster(bar, 0)) {
-              if (clock64() - start > WAIT_LIMIT_CYCLES) {
+              if (clock64() - start > Q3_WAIT_LIMIT_CYCLES) {
                 atomicExch(error_word, 3);
                 break;
               }

@@ -23,9 +23,7 @@
 // Every wait on an mbarrier is bounded (about a second of SM clock): on expiry the waiter
 // raises the block's abort flag and a global error word, every role leaves its loop, TMEM is
 // freed and the block returns; the host reports the error.  No load uses cluster multicast.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "async_tiles.cuh"
 
 namespace {
 
@@ -34,84 +32,34 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int STAGES = 4;
 constexpr int THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  False: gave up (this or another role raised the abort flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      return false;
+// NV values of one output row, columns [col, col + NV) as far as they exist: fp32 or bf16, with
+// 16-byte stores where the row's alignment allows.
+template <int MODE, int NV>
+__device__ __forceinline__ void store_row(void* __restrict__ out, int ldo, int row, int col, int N,
+                                          const float (&v)[NV]) {
+  if (MODE == OUT_F32) {
+    float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
+    if (col + NV <= N && (ldo & 3) == 0) {
+#pragma unroll
+      for (int e = 0; e < NV; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+    } else {
+      for (int e = 0; e < NV && col + e < N; ++e) dst[e] = v[e];
+    }
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
+    if (col + NV <= N && (ldo & 7) == 0) {
+#pragma unroll
+      for (int e = 0; e < NV; e += 8) {
+        float chunk[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) chunk[x] = v[e + x];
+        store8(dst + e, chunk);
+      }
+    } else {
+      for (int e = 0; e < NV && col + e < N; ++e) dst[e] = __float2bfloat16_rn(v[e]);
     }
   }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile [rows][64] bf16 written by TMA with the
-// 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t tile_addr) {
-  uint64_t d = (uint64_t)((tile_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                                // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: next group of 8 rows
-  d |= (uint64_t)1 << 46;                                // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M x N.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
 }
 
 // BN: features per MMA (N of the instruction).  NB: B tiles per stage (2 for SwiGLU: gate, up).
@@ -250,32 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
           }
-          if (row < M) {
-            const int col = n0 + c0;
-            if (MODE == OUT_F32) {
-              float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
-              if (col + 32 <= N && (ldo & 3) == 0) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 4)
-                  *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-              } else {
-                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = v[e];
-              }
-            } else {
-              bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
-              if (col + 32 <= N && (ldo & 7) == 0) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                  float chunk[8];
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) chunk[x] = v[e + x];
-                  store8(dst + e, chunk);
-                }
-              } else {
-                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(v[e]);
-              }
-            }
-          }
+          if (row < M) store_row<MODE, 32>(out, ldo, row, n0 + c0, N, v);
         }
         if (last) break;
       }
@@ -308,41 +231,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 //                      leader (8 arrivals: 4 warps of each CTA).
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_BN = 256;
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// the box lands in this CTA's shared memory, its bytes count on the pair leader's barrier
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x,
-                                                 int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// arrives on the barrier at this shared-memory offset in both CTAs of the pair
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-  const uint16_t both = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"(both)
-               : "memory");
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -481,32 +369,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (lane == 0) remote_arrive(leader_acc_empty0 + 8 * buf);
           }
-          if (row < M) {
-            const int col = n0 + c0;
-            if (MODE == OUT_F32) {
-              float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
-              if (col + 32 <= N && (ldo & 3) == 0) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 4)
-                  *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-              } else {
-                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = v[e];
-              }
-            } else {
-              bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
-              if (col + 32 <= N && (ldo & 7) == 0) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                  float chunk[8];
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) chunk[x] = v[e + x];
-                  store8(dst + e, chunk);
-                }
-              } else {
-                for (int e = 0; e < 32 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(v[e]);
-              }
-            }
-          }
+          if (row < M) store_row<MODE, 32>(out, ldo, row, n0 + c0, N, v);
         }
         if (last) break;
       }
@@ -533,13 +396,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 // [80,160) the peer's: feature = n0 + 160 * (c % 160 / 80) + 80 * (c / 160) + c % 80.
 constexpr int WIDE = 320;
 constexpr int WIDE_STAGES = 5;
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -660,30 +516,10 @@ gemm_tcgen05_pair_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
           if (lane == 0) remote_arrive(leader_acc_empty);
         }
         if (row < M && col < N) {
-          if (MODE == OUT_F32) {
-            float* dst = reinterpret_cast<float*>(out) + (long)row * ldo + col;
-            if (col + 16 <= N && (ldo & 3) == 0) {
+          float v[16];
 #pragma unroll
-              for (int e = 0; e < 16; e += 4)
-                *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(acc[e]), __uint_as_float(acc[e + 1]),
-                                                                  __uint_as_float(acc[e + 2]), __uint_as_float(acc[e + 3]));
-            } else {
-              for (int e = 0; e < 16 && col + e < N; ++e) dst[e] = __uint_as_float(acc[e]);
-            }
-          } else {
-            bf16* dst = reinterpret_cast<bf16*>(out) + (long)row * ldo + col;
-            if (col + 16 <= N && (ldo & 7) == 0) {
-#pragma unroll
-              for (int e = 0; e < 16; e += 8) {
-                float chunk[8];
-#pragma unroll
-                for (int x = 0; x < 8; ++x) chunk[x] = __uint_as_float(acc[e + x]);
-                store8(dst + e, chunk);
-              }
-            } else {
-              for (int e = 0; e < 16 && col + e < N; ++e) dst[e] = __float2bfloat16_rn(__uint_as_float(acc[e]));
-            }
-          }
+          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(acc[e]);
+          store_row<MODE, 16>(out, ldo, row, col, N, v);
         }
       }
     }
@@ -701,10 +537,6 @@ gemm_tcgen05_pair_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
 
 // ---- host side ------------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 int sm_count() {
   static int count_on[Q3_MAX_DEVICES];
   int& count = count_on[q3_current_device()];
@@ -714,33 +546,6 @@ int sm_count() {
     if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count < 2) count = 148;
   }
   return count;
-}
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// A row-major [rows, cols] bf16 matrix with row stride `ld` elements, read in boxes of
-// [box_rows, 64] with the 128-byte swizzle; out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, int NB, int MODE>
@@ -880,12 +685,12 @@ Q3_EXPORT int q3_gemm_tcgen05_pair(int mode, const void* x, int ldx, const void*
     const long cost_256 = ((tiles_m * ((N + PAIR_BN - 1) / PAIR_BN) + pairs - 1) / pairs) * PAIR_BN;
     const long cost_wide = ((tiles_m * ((N + WIDE - 1) / WIDE) + pairs - 1) / pairs) * (WIDE + 24);
     if (cost_wide < cost_256) {
-      if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, WIDE / 2)) return Q3_ERR_LAUNCH;
+      if (!q3_bf16_map(&ta, x, M, K, ldx, BM) || !q3_bf16_map(&tw, W, w_rows, K, ldw, WIDE / 2)) return Q3_ERR_LAUNCH;
       return mode == OUT_F32 ? launch_pair_wide<OUT_F32>(ta, tw, out, ldo, M, N, K, error_word, stream)
                              : launch_pair_wide<OUT_BF16>(ta, tw, out, ldo, M, N, K, error_word, stream);
     }
   }
-  if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, 128)) return Q3_ERR_LAUNCH;
+  if (!q3_bf16_map(&ta, x, M, K, ldx, BM) || !q3_bf16_map(&tw, W, w_rows, K, ldw, 128)) return Q3_ERR_LAUNCH;
   if (mode == OUT_SWIGLU) return launch_pair<OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
   if (mode == OUT_F32) return launch_pair<OUT_F32>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
   return launch_pair<OUT_BF16>(ta, tw, out, ldo, M, N, K, 0, error_word, stream);
@@ -918,7 +723,7 @@ Q3_EXPORT int q3_gemm_tcgen05(int mode, const void* x, int ldx, const void* W, i
     }
   }
   const long w_rows = mode == OUT_SWIGLU ? 2L * N : N;
-  if (!make_map(&ta, x, M, K, ldx, BM) || !make_map(&tw, W, w_rows, K, ldw, bn)) return Q3_ERR_LAUNCH;
+  if (!q3_bf16_map(&ta, x, M, K, ldx, BM) || !q3_bf16_map(&tw, W, w_rows, K, ldw, bn)) return Q3_ERR_LAUNCH;
   if (mode == OUT_SWIGLU) return launch<128, 2, OUT_SWIGLU>(ta, tw, out, ldo, M, N, K, N, error_word, stream);
 #define Q3_TC_CASE(BN_)                                                                                   \
   if (bn == BN_)                                                                                          \
