@@ -25,6 +25,12 @@
 // slot's mbarrier there; the leader adds the partials in range order and runs the epilogue.
 // A slot is used once, so nobody ever waits for a slot to become free.
 //
+// Partial sums (mode 3): no exchange and no cluster at all.  The block of range p writes
+// its fp32 partial of every unit to out[p][token][feature], and whoever reads the product
+// adds the `parts` planes in order; in a decode step that is the norm kernel that folds the
+// product into the residual sum, which reads a few fp32 rows more and saves the products
+// the wait of every block for its cluster.
+//
 // Every mbarrier wait is bounded; on expiry the waiter sets the error word and carries on
 // (the result is then invalid, and the host raises), so no barrier is ever abandoned.
 #define Q3_WAIT_LIMIT_CYCLES 400000000ll
@@ -32,7 +38,7 @@
 
 namespace {
 
-enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_SWIGLU = 2 };
+enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_SWIGLU = 2, OUT_PARTIAL = 3 };
 constexpr int CONSUMER_WARPS = 16;
 constexpr int CONSUMERS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMERS + 32;
@@ -163,7 +169,7 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
 #pragma unroll
       for (int w = 0; w < CONSUMER_WARPS; ++w) v += rbuf[(w * 4 + e) * 32 + lane];
       bool emit = true;
-      if (plan.parts > 1) {
+      if (MODE != OUT_PARTIAL && plan.parts > 1) {
         const int leader = u % plan.parts, li = u / plan.parts;
         if (part != leader) {
           const int idx = part < leader ? part : part - 1;
@@ -199,7 +205,9 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       if (emit && token < M && feature < N && (MODE != OUT_SWIGLU || t < 2)) {
         float r = v;
         if (MODE == OUT_SWIGLU) r = (r / (1.f + expf(-r))) * up;
-        if (MODE == OUT_F32)
+        if (MODE == OUT_PARTIAL)
+          reinterpret_cast<float*>(out)[((long)part * M + token) * ldo + feature] = r;
+        else if (MODE == OUT_F32)
           reinterpret_cast<float*>(out)[(long)token * ldo + feature] = r;
         else
           reinterpret_cast<bf16*>(out)[(long)token * ldo + feature] = __float2bfloat16_rn(r);
@@ -267,7 +275,10 @@ int resident_clusters(const void* kernel, int cluster, int sm_count) {
 // Ranges of K: as few as keep a range within what a warp's registers hold and the ring at two
 // stages or more; more only while that shortens the longest block's work (units x (range +
 // a fixed part worth 256 k-values)).
-bool make_plan(const void* kernel, int N, int K, int features_per_panel, int max_range, int sm_count, Plan* plan) {
+// exchange: the blocks of a panel form a cluster and sum their partials there; without it
+// every block stands alone and writes its partial.
+bool make_plan(const void* kernel, bool exchange, int N, int K, int features_per_panel, int max_range, int sm_count,
+               Plan* plan) {
   const int panels = (N + features_per_panel - 1) / features_per_panel;
   long best_cost = 0;
   plan->parts = 0;
@@ -276,11 +287,11 @@ bool make_plan(const void* kernel, int N, int K, int features_per_panel, int max
     range = (range + 31) & ~31;
     if (range > max_range) continue;
     if ((long)(parts - 1) * range >= K) continue;  // an empty range
-    const int clusters = resident_clusters(kernel, parts, sm_count);
+    const int clusters = exchange ? resident_clusters(kernel, parts, sm_count) : sm_count / parts;
     if (clusters < 1) continue;
     const int groups = clusters < panels ? clusters : panels;  // clusters launched
     const int units = (panels + groups - 1) / groups;
-    const int led = parts > 1 ? (units + parts - 1) / parts : 0;
+    const int led = exchange && parts > 1 ? (units + parts - 1) / parts : 0;
     if (led > MAX_LED) continue;
     const int pitch = ((range * 2 + 127) & ~127) + 64;
     int stages = (SMEM_LIMIT - RED_BYTES - led * (parts - 1) * 512) / (8 * pitch);
@@ -303,7 +314,7 @@ bool make_plan(const void* kernel, int N, int K, int features_per_panel, int max
 
 template <int MODE, bool HI>
 int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, int M, int N, int K, int up_offset,
-           int sm_count, int only_large, int* error_word, cudaStream_t stream) {
+           int sm_count, int only_large, int planes, int* error_word, cudaStream_t stream) {
   const void* kernel = (const void*)gemm_stream_kernel<MODE, HI>;
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
@@ -313,15 +324,20 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
     configured = true;
   }
   Plan plan;
-  if (!make_plan(kernel, N, K, MODE == OUT_SWIGLU ? 4 : 8, CONSUMER_WARPS * 32 * Blocks<HI>::value, sm_count, &plan))
+  if (!make_plan(kernel, MODE != OUT_PARTIAL, N, K, MODE == OUT_SWIGLU ? 4 : 8,
+                 CONSUMER_WARPS * 32 * Blocks<HI>::value, sm_count, &plan))
     return Q3_ERR_UNSUPPORTED;
+  if (MODE == OUT_PARTIAL && plan.parts != planes) return Q3_ERR_ARGUMENT;
   // A block owns its SM, so kernels do not overlap at their ends: short products (few units
   // per block) and products that need the exchange between blocks are faster on the kernel
   // that streams through registers.
-  if (only_large && (plan.parts > 1 || plan.panels < 8 * plan.blocks)) return Q3_ERR_UNSUPPORTED;
+  if (MODE != OUT_PARTIAL && only_large && (plan.parts > 1 || plan.panels < 8 * plan.blocks))
+    return Q3_ERR_UNSUPPORTED;
   const size_t smem = (size_t)plan.stages * 8 * plan.pitch + RED_BYTES + (size_t)plan.led * (plan.parts - 1) * 512;
   void* args[] = {&x, &ldx, &W, &ldw, &out, &ldo, &M, &N, &K, &up_offset, &plan, &error_word};
-  return launch_stream(kernel, plan.blocks, plan.parts, smem, stream, args) == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+  return launch_stream(kernel, plan.blocks, MODE == OUT_PARTIAL ? 1 : plan.parts, smem, stream, args) == cudaSuccess
+             ? Q3_OK
+             : Q3_ERR_LAUNCH;
 }
 
 int sm_count_of_current_device() {
@@ -356,10 +372,37 @@ Q3_EXPORT int q3_gemm_stream(int mode, const void* x, int ldx, const void* W, in
   const bf16* wp = (const bf16*)W;
   const int up = mode == OUT_SWIGLU ? N : 0;
 #define Q3_STREAM_CASE(MODE)                                                                                  \
-  return M > 8 ? launch<MODE, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, error_word, stream)          \
-               : launch<MODE, false>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, error_word, stream)
+  return M > 8 ? launch<MODE, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, 0, error_word, stream)          \
+               : launch<MODE, false>(xp, ldx, wp, ldw, out, ldo, M, N, K, up, sms, only_large, 0, error_word, stream)
   if (mode == OUT_BF16) Q3_STREAM_CASE(OUT_BF16);
   if (mode == OUT_F32) Q3_STREAM_CASE(OUT_F32);
   Q3_STREAM_CASE(OUT_SWIGLU);
 #undef Q3_STREAM_CASE
+}
+
+// The number of K ranges that q3_gemm_stream_partial cuts this product into (its output has
+// that many planes); 0 if the product is not supported.
+Q3_EXPORT int q3_gemm_stream_parts(int M, int N, int K) {
+  if (N < 1 || K < 1 || M < 1 || M > 16 || K % 8) return 0;
+  const int sms = sm_count_of_current_device();
+  Plan plan;
+  if (!sms || !make_plan(nullptr, false, N, K, 8, CONSUMER_WARPS * 32 * Blocks<true>::value, sms, &plan)) return 0;
+  return plan.parts;
+}
+
+// out fp32 [parts, M, N] with out[p] = x[:, range p] * W[:, range p]^T, so that the product is
+// the sum of the planes; `parts` must be what q3_gemm_stream_parts returns for these sizes.
+// Otherwise as q3_gemm_stream.
+Q3_EXPORT int q3_gemm_stream_partial(const void* x, int ldx, const void* W, int ldw, float* out, int parts, int M,
+                                     int N, int K, int* error_word, cudaStream_t stream) {
+  if (!x || !W || !out || !error_word || N < 1 || K < 1 || M < 0 || parts < 1) return Q3_ERR_ARGUMENT;
+  if (M > 16 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K) return Q3_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return Q3_ERR_UNSUPPORTED;
+  if (M == 0) return Q3_OK;
+  const int sms = sm_count_of_current_device();
+  if (!sms) return Q3_ERR_LAUNCH;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  return M > 8 ? launch<OUT_PARTIAL, true>(xp, ldx, wp, ldw, out, N, M, N, K, 0, sms, 0, parts, error_word, stream)
+               : launch<OUT_PARTIAL, false>(xp, ldx, wp, ldw, out, N, M, N, K, 0, sms, 0, parts, error_word, stream);
 }

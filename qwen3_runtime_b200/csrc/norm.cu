@@ -2,6 +2,10 @@
 // row gather.  All arithmetic is fp32; one rounding at the store.
 //
 //   v   = (ids ? table[ids[r]] : resid[r]) + (pending ? pending[r] : 0)      (fp32)
+//         pending is either [rows, H] of the output's type or, with parts > 0, fp32
+//         [parts, rows, H] (planes `part_stride` elements apart) whose planes are the
+//         partial sums of a product over ranges of its inner dimension
+//         (csrc/gemm_stream.cu); they are added in plane order, then to the residual
 //   resid[r] = v                                  (when write_resid)
 //   out[i]  = (v * rsqrt(mean(v^2) + eps)) * w    (qwen3_runtime/layers/ops.py:17-37)
 //
@@ -11,10 +15,11 @@
 #include "common.cuh"
 
 template <typename T>
-__global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restrict__ resid,
-                                  const int* __restrict__ ids, const T* __restrict__ table,
-                                  const int* __restrict__ rows, const float* __restrict__ w,
-                                  T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+__global__ void fused_norm_kernel(const void* __restrict__ pending, int parts, long part_stride,
+                                  float* __restrict__ resid, const int* __restrict__ ids,
+                                  const T* __restrict__ table, const int* __restrict__ rows,
+                                  const float* __restrict__ w, T* __restrict__ out, int H, float eps,
+                                  int write_resid, int vocab) {
   extern __shared__ float vals[];  // H floats, then 33 for the reduction
   float* red = vals + H;
   pdl_wait();
@@ -27,12 +32,18 @@ __global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restri
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     trow = table + (long)id * H;
   }
-  const T* prow = pending ? pending + src * H : nullptr;
+  const T* prow = pending && !parts ? static_cast<const T*>(pending) + src * H : nullptr;
+  const float* frow = pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
   float* rrow = resid ? resid + src * H : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = trow ? to_f32(trow[i]) : rrow[i];
     if (prow) v += to_f32(prow[i]);
+    if (frow) {
+      float sum = frow[i];
+      for (int p = 1; p < parts; ++p) sum += frow[p * part_stride + i];
+      v += sum;
+    }
     if (write_resid) rrow[i] = v;
     vals[i] = v;
     ss += v * v;
@@ -47,10 +58,11 @@ __global__ void fused_norm_kernel(const T* __restrict__ pending, float* __restri
 // REGS: the block has a thread for every 8 elements of a row, so a thread's 8 values stay in
 // registers between the two passes (no staging through shared memory).
 template <typename T, bool REGS>
-__global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __restrict__ resid,
-                                      const int* __restrict__ ids, const T* __restrict__ table,
-                                      const int* __restrict__ rows, const float* __restrict__ w,
-                                      T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+__global__ void __launch_bounds__(512) fused_norm_vec_kernel(const void* __restrict__ pending, int parts, long part_stride,
+                                      float* __restrict__ resid, const int* __restrict__ ids,
+                                      const T* __restrict__ table, const int* __restrict__ rows,
+                                      const float* __restrict__ w, T* __restrict__ out, int H, float eps,
+                                      int write_resid, int vocab) {
   extern __shared__ float vals[];
   float* red = REGS ? vals : vals + H;
   pdl_wait();
@@ -63,7 +75,8 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     trow = table + (long)id * H;
   }
-  const T* prow = pending ? pending + src * H : nullptr;
+  const T* prow = pending && !parts ? static_cast<const T*>(pending) + src * H : nullptr;
+  const float* frow = pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
   float* rrow = resid ? resid + src * H : nullptr;
   float ss = 0.f;
   float mine[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -75,6 +88,23 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
       load8(prow + i, pv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += pv[e];
+    }
+    if (frow) {  // four planes' loads in flight at a time; added in plane order
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p0 = 0; p0 < parts; p0 += 4) {
+        float pv[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (p0 + j < parts) load8(frow + (p0 + j) * part_stride + i, pv[j]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (p0 + j < parts) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum[e] += pv[j][e];
+          }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += sum[e];
     }
     if (write_resid) store8(rrow + i, v);
     if (REGS) {
@@ -107,52 +137,55 @@ __global__ void fused_norm_vec_kernel(const T* __restrict__ pending, float* __re
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T>
-static int launch_fused_norm(const void* pending, float* resid, const int* ids, const void* table,
-                             const int* rows, const float* w, void* out, int num_rows, int H, float eps,
-                             int write_resid, int vocab, cudaStream_t stream) {
+static int launch_fused_norm(const void* pending, int parts, long part_stride, float* resid, const int* ids,
+                             const void* table, const int* rows, const float* w, void* out, int num_rows, int H,
+                             float eps, int write_resid, int vocab, cudaStream_t stream) {
   if (num_rows == 0) return Q3_OK;
   const size_t smem = (size_t)(H + 33) * sizeof(float);
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(fused_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  const bool vec = H % 8 == 0 && aligned16(pending) && aligned16(resid) && aligned16(table) && aligned16(w) &&
-                   aligned16(out);
+  const bool vec = H % 8 == 0 && part_stride % 4 == 0 && aligned16(pending) && aligned16(resid) &&
+                   aligned16(table) && aligned16(w) && aligned16(out);
   if (vec) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(fused_norm_vec_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int threads = ((H / 8 + 31) / 32) * 32;
-    threads = threads > 1024 ? 1024 : threads;
+    threads = threads > 512 ? 512 : threads;
     if (threads * 8 >= H)  // one chunk per thread: the values stay in registers
       return launch_pdl(fused_norm_vec_kernel<T, true>, dim3(num_rows), dim3(threads), 33 * sizeof(float), stream,
-                        (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid,
+                        pending, parts, part_stride, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid,
                         vocab) == cudaSuccess
                  ? Q3_OK
                  : Q3_ERR_LAUNCH;
-    return launch_pdl(fused_norm_vec_kernel<T, false>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending,
-                      resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+    return launch_pdl(fused_norm_vec_kernel<T, false>, dim3(num_rows), dim3(threads), smem, stream, pending, parts,
+                      part_stride, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
                ? Q3_OK
                : Q3_ERR_LAUNCH;
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   fused_norm_kernel<T><<<num_rows, threads, smem, stream>>>(
-      (const T*)pending, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
+      pending, parts, part_stride, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab);
   return q3_launch_status();
 }
 
 // out[num_rows, H]; resid fp32 [*, H] (may be null only when ids is given and
-// write_resid is 0); pending/table/out have `dtype`; w is fp32 [H].
-Q3_EXPORT int q3_fused_norm(int dtype, const void* pending, float* resid, const int* ids, const void* table,
+// write_resid is 0); table/out have `dtype`; w is fp32 [H].  pending has `dtype` when
+// pending_parts is 0, else it is fp32 with pending_parts planes, part_stride elements apart.
+Q3_EXPORT int q3_fused_norm(int dtype, const void* pending, int pending_parts, long part_stride, float* resid,
+                            const int* ids, const void* table,
                             const int* rows, const float* w, void* out, int num_rows, int H, float eps,
                             int write_resid, int vocab, cudaStream_t stream) {
   if (!w || !out || H < 1) return Q3_ERR_ARGUMENT;
   if (!ids && !resid) return Q3_ERR_ARGUMENT;
   if (ids && !table) return Q3_ERR_ARGUMENT;
   if (write_resid && !resid) return Q3_ERR_ARGUMENT;
+  if (pending_parts < 0 || (pending_parts && (!pending || part_stride < 0))) return Q3_ERR_ARGUMENT;
   if (dtype == Q3_DTYPE_F32)
-    return launch_fused_norm<float>(pending, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
+    return launch_fused_norm<float>(pending, pending_parts, part_stride, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
                                     vocab, stream);
   if (dtype == Q3_DTYPE_BF16)
-    return launch_fused_norm<bf16>(pending, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
+    return launch_fused_norm<bf16>(pending, pending_parts, part_stride, resid, ids, table, rows, w, out, num_rows, H, eps, write_resid,
                                    vocab, stream);
   return Q3_ERR_ARGUMENT;
 }

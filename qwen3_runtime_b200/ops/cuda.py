@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
 
@@ -47,8 +47,8 @@ def _check(code: int, what: str) -> None:
 
 _SIGNATURES = {
     "norm": {
-        "q3_fused_norm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "q3_fused_norm": [c_int, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "q3_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
     "rope_kv": {
@@ -90,6 +90,9 @@ _SIGNATURES = {
     "gemm_stream": {
         "q3_gemm_stream": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p],
+        "q3_gemm_stream_parts": [c_int, c_int, c_int],
+        "q3_gemm_stream_partial": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p],
     },
     "gemm_tcgen05": {
         "q3_gemm_tcgen05": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
@@ -132,6 +135,10 @@ class CudaOps:
         # large ones, the register stream (csrc/gemm_small_m.cu) for the rest; "stream" -- the first
         # for everything it supports; "registers" -- always the second
         self.small_gemm = "auto"
+        # True: a product whose result a norm folds into the residual sum may come as fp32 partial
+        # sums over ranges of K (linear(partial_sums=True)); False: always a finished product
+        self.partial_sums = True
+        self._parts_cache: dict[tuple, int] = {}
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -174,12 +181,21 @@ class CudaOps:
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
                    write_resid=True, num_rows=None):
-        """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu."""
+        """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu.
+        ``pending`` is ``[rows, H]`` of the output's type, or fp32 ``[parts, rows, H]``: the
+        partial sums of a product (:meth:`linear` with ``partial_sums``), added in order."""
         H = weight.numel()
         n = out.shape[0] if num_rows is None else num_rows
         vocab = table.shape[0] if table is not None else 0
+        parts = stride = 0
+        if pending is not None and pending.dim() == 3:
+            if pending.dtype != torch.float32 or pending.stride(2) != 1 or pending.stride(1) != H:
+                raise KernelError("fused_norm: partial sums are fp32 [parts, rows, H] with dense rows")
+            parts, stride = pending.shape[0], pending.stride(0)
+        elif pending is not None and pending.dtype != out.dtype:
+            raise KernelError(f"fused_norm: pending is {pending.dtype}, the output {out.dtype}")
         self._call("norm", "q3_fused_norm", f"fused_norm(H={H})",
-                   _dtype_code(out.dtype), _ptr(pending), _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
+                   _dtype_code(out.dtype), _ptr(pending), parts, stride, _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
                   _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab)
         return out
 
@@ -339,16 +355,30 @@ class CudaOps:
         return out
 
     # ---- matrix products ----------------------------------------------------------------
-    def linear(self, x, weight, out=None, out_dtype=None):
+    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False):
         """``x[M, K] @ weight[N, K]^T``.  float32: this engine's FMA kernel (no TF32).
         bfloat16, at most 16 tokens: one of this engine's two weight-streaming kernels
         (:meth:`_small_product`).  bfloat16, more tokens: the library product with fp32
         accumulation, as the reference's ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77,
-        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"``."""
+        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"``.
+
+        ``partial_sums``: the caller also takes float32 ``[parts, M, N]`` whose sum over the
+        first axis is the product (what :meth:`fused_norm` accepts as ``pending``).  It gets
+        that when the streaming kernel would cut K into ranges: the blocks then need not
+        wait for one another to add their parts up."""
         M, K = x.shape
         N = weight.shape[0]
         if weight.shape[1] != K:
             raise KernelError(f"linear: x is [{M},{K}] but weight is {list(weight.shape)}")
+        if (partial_sums and self.partial_sums and out is None and out_dtype is None and M > 0
+                and self.small_gemm != "registers" and self._small_m_ok(x, weight)):
+            parts = self._stream_parts(M, N, K)
+            if parts > 1:
+                planes = torch.empty((parts, M, N), dtype=torch.float32, device=x.device)
+                self._call("gemm_stream", "q3_gemm_stream_partial", "gemm_stream_partial", _ptr(x), x.stride(0),
+                           _ptr(weight), weight.stride(0), _ptr(planes), parts, M, N, K,
+                           _ptr(self._error_word(x.device)))
+                return planes
         if x.dtype == torch.float32:
             if out is None:
                 out = torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -429,6 +459,14 @@ class CudaOps:
         return out
 
     SMALL_M = 16
+
+    def _stream_parts(self, M: int, N: int, K: int) -> int:
+        """Ranges of K in the streaming kernel's partial-sum mode (0: it does not take the product)."""
+        key = (M > 8, N, K)
+        parts = self._parts_cache.get(key)
+        if parts is None:
+            parts = self._parts_cache[key] = int(self._get("gemm_stream", "q3_gemm_stream_parts")(M, N, K))
+        return parts
 
     def _small_product(self, mode: int, x, weight, out, M, N, K) -> None:
         """A product of at most 16 tokens: the streaming kernel (csrc/gemm_stream.cu), or the

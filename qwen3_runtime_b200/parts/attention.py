@@ -96,7 +96,7 @@ class PagedAttention(Part):
                 scale=self.scale, window=self.window, num_seqs=step.num_seqs,
                 max_kv_len=width * cache.page_size or step.max_kv_len,
                 new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin))
-            return ops.linear(ctx_out, self.o_weight)
+            return ops.linear(ctx_out, self.o_weight, partial_sums=self.partial_sums_ok)
         ops.qk_norm_rope_store(
             qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
@@ -108,7 +108,7 @@ class PagedAttention(Part):
             head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,
             token_seq=step.token_seq, positions=step.positions, out=ctx_out, page_size=cache.page_size,
             scale=self.scale, window=self.window, step=step)
-        return ops.linear(ctx_out, self.o_weight)
+        return ops.linear(ctx_out, self.o_weight, partial_sums=self.partial_sums_ok)
 
 
 register_part("mixer", "paged_attention", PagedAttention)

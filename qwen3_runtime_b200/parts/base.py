@@ -70,6 +70,12 @@ class StepContext:
 
 class Part:
     category = ""
+    # A norm that can take ``ResidualStream.pending`` as partial sums (see there) says so here.
+    adds_partial_sums = False
+    # Set on a mixer or feed-forward by whoever arranges the parts, when the norm that will
+    # fold its output into the residual sum adds partial sums itself: ``forward`` may then
+    # return float32 ``[parts, tokens, hidden]`` whose sum over the first axis is the output.
+    partial_sums_ok = False
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         self.spec = spec
@@ -117,7 +123,9 @@ class ResidualStream:
     """The residual sum of a step, kept in float32, plus what has not been added yet.
 
     ``pending`` is the output of the last sublayer; the next norm adds it to ``resid``
-    and normalises in one kernel.  A fresh stream holds an embedding lookup instead of
+    and normalises in one kernel.  It is ``[tokens, hidden]`` in the compute dtype, or float32
+    ``[parts, tokens, hidden]``: partial sums of the sublayer's last product over ranges of
+    its inner dimension, which the norm adds in order (one kernel less waits for the sum).  A fresh stream holds an embedding lookup instead of
     values: the first norm gathers the rows, stores them as ``resid`` and normalises.
     """
 

@@ -21,6 +21,14 @@ class PreNormBlock(Part):
             spec.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm,
             spec.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm,
         }
+        # the mixer's output meets this block's second norm; where the feed-forward's output
+        # goes only the model knows (exit_to)
+        self.entry_norm = self.mixer_norm
+        self.mixer.partial_sums_ok = self.feed_forward_norm.adds_partial_sums
+
+    def exit_to(self, norms) -> None:
+        """``norms``: every norm that may fold this block's output into the residual sum."""
+        self.feed_forward.partial_sums_ok = all(n.adds_partial_sums for n in norms)
 
     def param_specs(self):
         return {prefix + name: ps for prefix, part in self.children.items()

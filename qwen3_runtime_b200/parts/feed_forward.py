@@ -38,7 +38,7 @@ class GatedMLP(Part):
     def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
         mid = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
         self.ops.gated_linear(h, self.gate_up_weight, mid)
-        return self.ops.linear(mid, self.down_weight)
+        return self.ops.linear(mid, self.down_weight, partial_sums=self.partial_sums_ok)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

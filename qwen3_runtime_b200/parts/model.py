@@ -20,6 +20,17 @@ class DecoderModel:
         self.ops = ctx.ops
         self.blocks = [build_part("block", b, ctx) for b in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, ctx)
+        # tell each block which norms take its output: the entry norm of whatever runs after
+        # it (a block may run more than once), or the final norm
+        takers: dict[int, list] = {}
+        for i, run in enumerate(spec.order):
+            after = self.blocks[spec.order[i + 1].block] if i + 1 < len(spec.order) else None
+            norm = self.final_norm if after is None else getattr(after, "entry_norm", None)
+            takers.setdefault(run.block, []).append(norm)
+        for index, norms in takers.items():
+            block = self.blocks[index]
+            if hasattr(block, "exit_to") and all(n is not None for n in norms):
+                block.exit_to(norms)
         self.embed: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
         self.loaded = False

@@ -10,6 +10,7 @@ from .base import BuildContext, ParamSpec, Part, ResidualStream, register_part
 
 class RMSNorm(Part):
     category = "norm"
+    adds_partial_sums = True
 
     def __init__(self, spec, ctx: BuildContext):
         super().__init__(spec, ctx)

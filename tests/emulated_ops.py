@@ -27,7 +27,12 @@ class TorchOps:
             v = table[ids.long()[src]].float()
         else:
             v = resid[src].float()
-        if pending is not None:
+        if pending is not None and pending.dim() == 3:  # fp32 partial sums [parts, rows, H], added in order
+            total = pending[0][src]
+            for p in range(1, pending.shape[0]):
+                total = total + pending[p][src]
+            v = v + total
+        elif pending is not None:
             v = v + pending[src].float()
         if write_resid:
             resid[src] = v
@@ -99,7 +104,12 @@ class TorchOps:
         return out
 
     # ---- matrix products ----------------------------------------------------------------
-    def linear(self, x, weight, out=None, out_dtype=None):
+    partial_parts = 0  # > 1: linear(partial_sums=True) answers with that many planes
+
+    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False):
+        if partial_sums and self.partial_parts > 1 and out is None and out_dtype is None:
+            cuts = torch.linspace(0, x.shape[1], self.partial_parts + 1).long().tolist()
+            return torch.stack([x[:, a:b].float() @ weight[:, a:b].float().t() for a, b in zip(cuts, cuts[1:])])
         res = x.float() @ weight.float().t()
         res = res.to(out_dtype or x.dtype)
         if out is not None:

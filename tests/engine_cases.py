@@ -26,6 +26,21 @@ def tolerance(dtype: str, scale: float) -> float:
     return TOL_F32 * max(1.0, scale / 4.0) if dtype == "float32" else REL_TOL_BF16 * scale
 
 
+def check_greedy_within_rounding(raw, w, prompt, tokens, what):
+    """bfloat16 greedy tokens: two logits within rounding of each other may swap, after which a
+    recomputed sequence goes another way, so whole sequences are not compared.  Instead every
+    token is checked at its own place: given the tokens the engine chose before it, the plain
+    model's logit for it is the largest, or below the largest by no more than the two logits'
+    tolerances together."""
+    logits = pm.forward_logits(raw, w, list(prompt) + list(tokens[:-1]), act_dtype=torch.bfloat16)
+    rows = logits[len(prompt) - 1:]
+    assert rows.shape[0] == len(tokens)
+    tol = 2 * tolerance("bfloat16", float(logits.abs().max()))
+    for i, tok in enumerate(tokens):
+        gap = float(rows[i].max() - rows[i][tok])
+        assert gap <= tol, f"{what}: token {i} ({tok}) is {gap:.3g} below the plain argmax (allowed {tol:.3g})"
+
+
 def plain_logits(folder, requests, dtype):
     raw, w = pm.read_model_dir(folder)
     act = torch.bfloat16 if dtype == "bfloat16" else None
@@ -138,10 +153,11 @@ def case_greedy_generation(tmp_path, name, dtype, ops, device, *, cuda_graph=Fal
     if dtype == "float32":
         assert alone == want and batched == want and squeezed == tight_want and unsqueezed == tight_want
     else:
-        # greedy ids may flip where two logits are within bfloat16 rounding of each other; the
-        # engine's own three ways must still agree with each other on most tokens
-        agree = sum(a == b for x, y in zip(alone, want) for a, b in zip(x, y))
-        assert agree >= 0.7 * 8 * len(prompts), (alone, want)
+        # greedy ids may flip where two logits are within bfloat16 rounding of each other
+        for p, toks in zip(prompts, alone):
+            check_greedy_within_rounding(raw, w, p, toks, f"{name} alone")
+        for p, toks in zip(tight_prompts, squeezed):
+            check_greedy_within_rounding(raw, w, p, toks, f"{name} squeezed")
         assert batched == alone and squeezed == unsqueezed
     return alone
 

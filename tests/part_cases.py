@@ -92,6 +92,14 @@ def case_norm_part(dtype, ops, device):
     want2 = pm.rmsnorm(x2, t["weight"].float(), 3e-5)
     assert float((h2.float().cpu() - want2).abs().max()) <= tol(dtype, float(want2.abs().max()))
     assert torch.equal(stream.resid.cpu(), x2) and stream.pending is None
+    # what is pending may be partial sums: float32 planes, added in order, then to the residual
+    planes = (torch.randn(3, 4, 80) * 0.3).to(ctx.device)
+    stream.pending = planes
+    h3 = norm.add_norm(stream)
+    x3 = x2 + ((planes[0] + planes[1]) + planes[2]).cpu()
+    want3 = pm.rmsnorm(x3, t["weight"].float(), 3e-5)
+    assert float((h3.float().cpu() - want3).abs().max()) <= tol(dtype, float(want3.abs().max()))
+    assert torch.equal(stream.resid.cpu(), x3) and stream.pending is None
 
 
 def case_position_part(dtype, ops, device):
@@ -219,6 +227,88 @@ def case_window_attention(dtype, ops, device, window=7):
     want = pm._round(pm.rmsnorm(h, wf["model.norm.weight"], raw["rms_norm_eps"]), act) @ wf["model.embed_tokens.weight"].T
     scale = float(want.abs().max())
     assert float((got - want).abs().max()) <= (3e-5 if dtype == "float32" else 0.03) * max(1.0, scale)
+
+
+class FinishedOnlyNorm(Part):
+    """A toy norm that does not add partial sums (it does not say ``adds_partial_sums``): the parts
+    that feed it must hand it finished products."""
+
+    category = "norm"
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.inner = build_part("norm", PartSpec("rmsnorm", spec.params), ctx)
+        self.seen = 0
+
+    def param_specs(self):
+        return self.inner.param_specs()
+
+    def load(self, tensors):
+        self.inner.load(tensors)
+
+    def kernel_groups(self):
+        return self.inner.kernel_groups()
+
+    def add_norm(self, stream, rows=None, num_rows=None):
+        assert stream.pending is None or stream.pending.dim() == 2, "this norm was promised finished products"
+        self.seen += 1
+        return self.inner.add_norm(stream, rows=rows, num_rows=num_rows)
+
+
+def case_partial_sums(dtype, ops, device):
+    """A sublayer may hand its last product to the next norm as partial sums, if that norm adds
+    them: who may is settled when the model is put together, from the run order.  The logits
+    are the plain model's either way."""
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    ids = random_ids(cfg.vocab_size, 40, 23)
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    limit = (3e-5 if dtype == "float32" else 0.03)
+    # (1) every norm adds partial sums: every mixer and feed-forward may produce them
+    model, tensors = _toy_model(base, cfg, dtype, ops, device)
+    assert all(b.mixer.partial_sums_ok and b.feed_forward.partial_sums_ok for b in model.blocks)
+    want = pm.forward_logits(cfg.to_hf_config(), tensors, ids, act_dtype=act)
+    scale = max(1.0, float(want.abs().max()))
+    emulated = hasattr(ops, "partial_parts")
+    try:
+        if emulated:  # the stand-in for the kernels cuts every such product into three ranges
+            ops.partial_parts = 3
+        got, _ = _run_cut(model, cfg, ids)
+    finally:
+        if emulated:
+            ops.partial_parts = 0
+    assert float((got - want).abs().max()) <= limit * scale
+    # (2) a norm that does not: block 1's second norm and the final norm
+    register_part("norm", "finished_only", FinishedOnlyNorm)
+    try:
+        blocks = list(base.blocks)
+        ffn = base.blocks[1]["feed_forward_norm"]
+        blocks[1] = PartSpec("pre_norm", {**base.blocks[1].params,
+                                          "feed_forward_norm": PartSpec("finished_only", ffn.params)})
+        spec = ModelSpec(base.vocab_size, base.hidden_size, tuple(blocks), base.order,
+                         PartSpec("finished_only", base.final_norm.params), True)
+        model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+        flags = [(b.mixer.partial_sums_ok, b.feed_forward.partial_sums_ok) for b in model.blocks]
+        assert flags == [(True, True), (False, False)]
+        try:
+            if emulated:
+                ops.partial_parts = 3
+            got, _ = _run_cut(model, cfg, ids)
+        finally:
+            if emulated:
+                ops.partial_parts = 0
+        assert model.final_norm.seen > 0 and model.blocks[1].feed_forward_norm.seen > 0
+        want = pm.forward_logits(cfg.to_hf_config(), tensors, ids, act_dtype=act)
+        assert float((got - want).abs().max()) <= limit * scale
+        # (3) a block that runs twice hands on to two norms: both must add partial sums
+        order = (LayerRun(0, 0), LayerRun(1, 1), LayerRun(0, 2))
+        spec = ModelSpec(base.vocab_size, base.hidden_size, base.blocks, order,
+                         PartSpec("finished_only", base.final_norm.params), True)
+        model, _ = _toy_model(spec, cfg, dtype, ops, device)
+        flags = [(b.mixer.partial_sums_ok, b.feed_forward.partial_sums_ok) for b in model.blocks]
+        assert flags == [(True, False), (True, True)]
+    finally:
+        unregister_part("norm", "finished_only")
 
 
 class DecayStateMixer(Part):

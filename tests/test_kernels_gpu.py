@@ -549,6 +549,57 @@ def test_gemm_stream_rows_do_not_depend_on_the_other_tokens(ops):
     ops.raise_if_kernel_error()
 
 
+@pytest.mark.parametrize("M", [1, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (2560, 9728), (301, 80), (17, 4096), (40, 20488), (1000, 5128),
+                                 (8, 40968), (2560, 2560), (48, 64)])
+def test_gemm_stream_partial_sums(ops, M, N, K):
+    """The planes are the products over consecutive ranges of K (multiples of 32 wide) and add
+    up to the product; the norm kernel adds them in order, then the residual."""
+    x = rand((M, K), torch.bfloat16, 68)
+    w = rand((N, K), torch.bfloat16, 69, scale=0.05)
+    planes = ops.linear(x, w, partial_sums=True)
+    want = x.float() @ w.float().t()
+    if planes.dim() == 2:  # the kernel keeps K whole for these sizes: a finished product
+        assert ops._stream_parts(M, N, K) <= 1
+        close(planes, want, torch.bfloat16, "finished product", bf16_tol=1e-2)
+        return
+    parts = planes.shape[0]
+    assert planes.dtype == torch.float32 and planes.shape == (parts, M, N) and parts in (2, 4, 8)
+    width = (-(-K // parts) + 31) // 32 * 32
+    for p in range(parts):
+        a, b = p * width, min(K, (p + 1) * width)
+        close(planes[p], x[:, a:b].float() @ w[:, a:b].float().t(), torch.float32, f"plane {p}", f32_tol=2e-5)
+    close(planes.sum(0), want, torch.float32, "sum of the planes", f32_tol=2e-5)
+    assert torch.equal(ops.linear(x, w, partial_sums=True), planes), "the same bits every time"
+    if M > 1:  # a token's planes do not depend on the other tokens
+        assert torch.equal(ops.linear(x[:1], w, partial_sums=True), planes[:, :1])
+    # consumed by the norm: bfloat16 and float32 outputs, whole and gathered rows
+    for dtype in DTYPES:
+        g = (1 + 0.1 * torch.randn(N, generator=torch.Generator().manual_seed(70))).cuda()
+        resid = rand((M, N), torch.float32, 71)
+        r1, r2 = resid.clone(), resid.clone()
+        o1 = torch.empty((M, N), dtype=dtype, device="cuda")
+        o2 = torch.empty_like(o1)
+        ops.fused_norm(o1, g, 1e-6, resid=r1, pending=planes)
+        REF.fused_norm(o2, g, 1e-6, resid=r2, pending=planes)
+        close(o1, o2, dtype, "partial sums + add + norm")
+        assert torch.equal(r1, r2), "planes are added in order, then to the residual, all in float32"
+        rows = torch.tensor([M - 1, 0], dtype=torch.int32).cuda()
+        g1 = torch.empty((2, N), dtype=dtype, device="cuda")
+        g2 = torch.empty_like(g1)
+        ops.fused_norm(g1, g, 1e-6, resid=resid, pending=planes, rows=rows, write_resid=False)
+        REF.fused_norm(g2, g, 1e-6, resid=resid.clone(), pending=planes, rows=rows, write_resid=False)
+        close(g1, g2, dtype, "partial sums + gather + norm")
+    # without leave, or with the register kernel, the product comes finished
+    assert ops.linear(x, w).dim() == 2
+    ops.partial_sums = False
+    try:
+        assert ops.linear(x, w, partial_sums=True).dim() == 2
+    finally:
+        ops.partial_sums = True
+    ops.raise_if_kernel_error()
+
+
 @pytest.mark.parametrize("M", [1, 8, 13])
 @pytest.mark.parametrize("I,K", [(9728, 2560), (112, 80), (160, 96), (24, 4096), (301, 2560), (6, 9728)])
 def test_gated_linear_small_m(ops, small_gemm, M, I, K):

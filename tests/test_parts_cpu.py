@@ -40,3 +40,7 @@ def test_toy_routed_feed_forward_registers_builds_and_steps():
 
 def test_toy_position_encoding_registers_builds_and_steps():
     pc.case_toy_position_encoding(DT, OPS, DEV)
+
+
+def test_partial_sums_are_allowed_by_the_run_order_and_added_by_the_norm():
+    pc.case_partial_sums(DT, OPS, DEV)
