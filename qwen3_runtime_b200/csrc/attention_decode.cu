@@ -13,9 +13,12 @@
 // never read, so stale or poisoned pages cannot leak in.
 //
 // With more than one split a block writes a normalised partial result and its log-sum-exp
-// to scratch (mid_o [seqs, nq, splits, D] fp32, mid_lse [seqs, nq, splits]); a second
-// kernel merges the splits (triton_decode.py:447-501).  Slices are cut at multiples of 64
-// keys counted from the first visible key, so an empty slice writes lse = -inf.
+// to scratch (mid_o [seqs, nq, splits, D] fp32, mid_lse [seqs, nq, splits]) and the splits
+// are merged (triton_decode.py:447-501): by a second kernel, or, when the caller gives a
+// ticket word per (sequence, kv head), by whichever block of the pair finishes last -- it
+// draws the last ticket, reads all partials back and writes the result, so no kernel has to
+// start, wait for this one to drain and run just for the merge.  Slices are cut at multiples
+// of 64 keys counted from the first visible key, so an empty slice writes lse = -inf.
 #include <string.h>
 
 #define Q3_WAIT_LIMIT_CYCLES 400000000ll
@@ -55,40 +58,72 @@ constexpr int TILE = 64;     // keys per pipeline stage
 constexpr int WARPS = 4;     // each takes 16 keys of a tile
 constexpr int THREADS = WARPS * 32;
 
-// ---- merge of the slices inside a thread-block cluster ---------------------------------------------
-// With `cluster_merge` the blocks of one (sequence, kv head) -- its slices -- are one cluster.
-// Each leaves its normalised partial result [G][D] and its log-sum-exp [G] in its own shared
-// memory; after a cluster barrier block r merges the r-th share of the G x D outputs, reading
-// every block's partials through distributed shared memory in slice order (the arithmetic of
-// decode_combine_kernel, so the bits are the same), and a second barrier keeps every block's
-// shared memory alive until all have read it.
-__device__ __forceinline__ float ld_cluster(const float* local, uint32_t rank) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(smem_u32(local), rank)) : "memory");
-  return v;
-}
+// ---- merge of the slices ------------------------------------------------------------------------------
+// One output row: out[d] = sum_s w_s * mid_o[s][d] / sum_s w_s with w_s = 2^(lse_s - max lse), slices
+// in order; a thread makes 4 consecutive values.  Shared by the merge kernel and the merge by the last
+// block, so both give the same bits.  Loads go past L1 (the partials may have been written by other
+// blocks of the same kernel), eight slices' loads in flight at a time; an empty slice (lse = -inf)
+// never wrote its partial, which is loaded but not used.
 template <int D>
-__device__ __forceinline__ void cluster_merge_slices(const float* part_o, const float* part_lse, int G, int rank,
-                                                     int num_splits, bf16* __restrict__ out_row) {
-  cluster_sync_all();
-  const int total = G * D;
-  const int share = (total + num_splits - 1) / num_splits;
-  const int hi = min(total, (rank + 1) * share);
-  for (int idx = rank * share + threadIdx.x; idx < hi; idx += blockDim.x) {
-    const int g = idx / D;
-    float mx = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, ld_cluster(part_lse + g, s));
-    float acc = 0.f, wsum = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ls = ld_cluster(part_lse + g, s);
-      if (ls == -INFINITY) continue;
-      const float w = exp2f(ls - mx);
-      wsum += w;
-      acc += w * ld_cluster(part_o + idx, s);
+__device__ __forceinline__ void merge_row(const float* __restrict__ mid_o, const float* __restrict__ lse,
+                                          int num_splits, bf16* __restrict__ out_row, int first, int step) {
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, __ldcg(lse + s));
+  for (int d = 4 * first; d < D; d += 4 * step) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float wsum = 0.f;
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+      float4 v[8];
+      float ls[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < num_splits) {
+          ls[j] = __ldcg(lse + s0 + j);
+          v[j] = __ldcg(reinterpret_cast<const float4*>(mid_o + (long)(s0 + j) * D + d));
+        }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < num_splits && ls[j] != -INFINITY) {
+          const float w = exp2f(ls[j] - mx);
+          wsum += w;
+          acc[0] += w * v[j].x;
+          acc[1] += w * v[j].y;
+          acc[2] += w * v[j].z;
+          acc[3] += w * v[j].w;
+        }
     }
-    out_row[idx] = __float2bfloat16_rn(acc / wsum);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] / wsum, acc[1] / wsum);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] / wsum, acc[3] / wsum);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out_row + d) = packed;
   }
-  cluster_sync_all();
+}
+
+// Called by every thread of a block after its partials are written.  True in the block that
+// drew the pair's last ticket: every other slice's partials are then visible to it.  That
+// block puts the ticket word back to zero for the next launch.
+__device__ __forceinline__ bool drew_last_ticket(int* ticket, int num_splits) {
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    last = atomicAdd(ticket, 1) == num_splits - 1;
+    if (last) *ticket = 0;
+  }
+  __syncthreads();
+  if (last) __threadfence();
+  return last;
+}
+
+template <int D>
+__device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
+                                           long first_head, int G, int num_splits, bf16* __restrict__ out_rows) {
+  constexpr int PER_ROW = D / 4 < 32 ? D / 4 : 32;  // threads on one row, 4 values each
+  for (int g = threadIdx.x / PER_ROW; g < G; g += THREADS / PER_ROW)
+    merge_row<D>(mid_o + (first_head + g) * num_splits * D, mid_lse + (first_head + g) * num_splits, num_splits,
+                 out_rows + (long)g * D, threadIdx.x % PER_ROW, PER_ROW);
 }
 
 // FUSED: `q` is the raw q/k/v projection; the block norms and rotates its own queries, and the
@@ -105,7 +140,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
                         int num_splits, int stages, NewToken nt, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, int* __restrict__ error_word, int cluster_merge) {
+                        const __grid_constant__ CUtensorMap map_v, int* __restrict__ error_word, int* __restrict__ tickets) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -113,10 +148,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   unsigned char* q_s = smem;                  // [16][D] bf16
   unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile); 1024-byte aligned
   unsigned char* new_s = kv_s + (size_t)stages * 2 * TILE_BYTES;  // FUSED: the newest key, then value, [2][D]
-  // after the last tile the ring is reused: the warps' results [WARPS][16][D] + [WARPS][16][2],
-  // then (cluster_merge) this slice's partial [16][D] and its log-sum-exp [16]
-  float* part_o = reinterpret_cast<float*>(kv_s) + WARPS * 16 * D + WARPS * 16 * 2;
-  float* part_lse = part_o + 16 * D;
+  // after the last tile the ring is reused: the warps' results [WARPS][16][D] + [WARPS][16][2]
 
   if (TMA) {
     if (threadIdx.x == 0) {
@@ -143,16 +175,16 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   const int k_end = min(kv_len, k_begin + per);
   const int* bt = block_table + (long)seq * max_pages;
 
+  int* ticket = tickets && num_splits > 1 ? tickets + (long)slot * nkv + kvh : nullptr;
   if (k_begin >= k_end) {  // nothing visible in this slice
-    if (cluster_merge) {
-      pdl_launch_dependents();
-      if (tid < G) part_lse[tid] = -INFINITY;
-      if (FUSED) pdl_wait();
-      cluster_merge_slices<D>(part_o, part_lse, G, split, num_splits, out + ((long)tok * nq + kvh * G) * D);
-      return;
-    }
     if (num_splits > 1 && tid < G)
       mid_lse[((long)slot * nq + kvh * G + tid) * num_splits + split] = -INFINITY;
+    if (ticket) {
+      if (FUSED) pdl_wait();  // the ticket words and `out` belong to the kernels before this one until then
+      pdl_launch_dependents();
+      if (drew_last_ticket(ticket, num_splits))
+        merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
+    }
     return;
   }
   // FUSED: position p is not in the cache yet; its row is left out of the copies and patched in
@@ -488,55 +520,43 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     const float val = acc / l;
     if (num_splits == 1) {
       out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(val);
-    } else if (cluster_merge) {
-      part_o[idx] = val;
-      if (d == 0) part_lse[g] = m * scale_log2 + log2f(l);
     } else {
       mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = val;
       if (d == 0) mid_lse[((long)slot * nq + head) * num_splits + split] = m * scale_log2 + log2f(l);
     }
   }
-  if (cluster_merge) cluster_merge_slices<D>(part_o, part_lse, G, split, num_splits, out + ((long)tok * nq + kvh * G) * D);
+  if (ticket && drew_last_ticket(ticket, num_splits))
+    merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
 }
 
-// out[token of seq, head, :] = sum_s w_s * mid_o[s] / sum_s w_s,  w_s = 2^(lse_s - max lse)
-__global__ void decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
-                                      const int* __restrict__ cu_seqlens, const int* __restrict__ seq_list,
-                                      bf16* __restrict__ out, int nq, int D, int num_splits) {
+// The merge as a kernel of its own: one block per (kv head, sequence).
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ seq_list,
+                      bf16* __restrict__ out, int nq, int nkv, int num_splits) {
   pdl_wait();
   pdl_launch_dependents();
-  const int slot = blockIdx.y, head = blockIdx.x;
+  const int slot = blockIdx.y, kvh = blockIdx.x;
   const int seq = seq_list ? seq_list[slot] : slot;
   const int tok = cu_seqlens[seq];
-  const float* lse = mid_lse + ((long)slot * nq + head) * num_splits;
-  float mx = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, lse[s]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f, wsum = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ls = lse[s];
-      if (ls == -INFINITY) continue;
-      const float w = exp2f(ls - mx);
-      wsum += w;
-      acc += w * mid_o[(((long)slot * nq + head) * num_splits + s) * D + d];
-    }
-    out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(acc / wsum);
-  }
+  const int G = nq / nkv;
+  merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
 }
 
 template <int D, bool FUSED, bool TMA>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
-                  int num_splits, const NewToken& nt, long num_rows_kv, int* error_word, int cluster_merge,
+                  int num_splits, const NewToken& nt, long num_rows_kv, int* error_word, int* tickets,
                   cudaStream_t stream) {
   const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
-  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4 + 16 * D * 4 + 16 * 4;
+  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
   const size_t smem = 16 * D * 2 + (FUSED ? 2 * D * 2 : 0) + (pipe > merge ? pipe : merge);
   if (smem > 227 * 1024) return Q3_ERR_UNSUPPORTED;
-  cluster_merge = cluster_merge && num_splits > 1 && num_splits <= 8;
-  if (num_splits > 1 && !cluster_merge && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
+  if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
+  if (((uintptr_t)out & 7) || ((uintptr_t)mid_o & 15)) return Q3_ERR_UNSUPPORTED;
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
   if (!configured) {
@@ -562,15 +582,8 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     int n = 0;
-    if (cluster_merge) {
-      attr[n].id = cudaLaunchAttributeClusterDimension;
-      attr[n].val.clusterDim.x = num_splits;
-      attr[n].val.clusterDim.y = 1;
-      attr[n].val.clusterDim.z = 1;
-      ++n;
-    }
     if (q3_pdl_enabled()) {
       attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       attr[n].val.programmaticStreamSerializationAllowed = 1;
@@ -581,13 +594,13 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     const float scale_log2 = scale * 1.4426950408889634f;
     if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED, TMA>, q, q_stride, kpages, vpages, block_table,
                            max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps, scale_log2,
-                           window, num_splits, stages, nt, map_k, map_v, error_word, cluster_merge) != cudaSuccess)
+                           window, num_splits, stages, nt, map_k, map_v, error_word, tickets) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
-  if (num_splits > 1 && !cluster_merge) {
-    dim3 cgrid(nq, num_seqs);
-    if (launch_pdl(decode_combine_kernel, cgrid, dim3(D < 128 ? D : 128), 0, stream, (const float*)mid_o,
-                   (const float*)mid_lse, cu_seqlens, seq_list, out, nq, D, num_splits) != cudaSuccess)
+  if (num_splits > 1 && !tickets) {
+    dim3 cgrid(nkv, num_seqs);
+    if (launch_pdl(decode_combine_kernel<D>, cgrid, dim3(THREADS), 0, stream, (const float*)mid_o,
+                   (const float*)mid_lse, cu_seqlens, seq_list, out, nq, nkv, num_splits) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   return Q3_OK;
@@ -598,7 +611,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
                     int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
                     float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
                     int window, int num_splits, const NewToken& nt, long num_rows_kv, int* error_word,
-                    int cluster_merge, cudaStream_t stream) {
+                    int* tickets, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
   if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
@@ -614,12 +627,12 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
                                                  (const bf16*)vpages, block_table, max_pages, kv_lens,           \
                                                  cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs, nq, \
                                                  nkv, ps, scale, window, num_splits, nt, num_rows_kv,            \
-                                                 error_word, cluster_merge, stream)                              \
+                                                 error_word, tickets, stream)                              \
                : launch_decode<DIM, FUSED, false>((const bf16*)q, q_stride, (const bf16*)kpages,                 \
                                                   (const bf16*)vpages, block_table, max_pages, kv_lens,          \
                                                   cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs,    \
                                                   nq, nkv, ps, scale, window, num_splits, nt, num_rows_kv,       \
-                                                  error_word, cluster_merge, stream)
+                                                  error_word, tickets, stream)
   switch (D) {
     Q3_DECODE_CASE(64);
     Q3_DECODE_CASE(128);
@@ -640,18 +653,19 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
 // vpages (pages x kv heads x page size); when it is given (> 0) together with `error_word`
 // (a device int that is set non-zero if a bounded wait expires) and the page size is 8, 16, 32
 // or a multiple of 64, keys and values are fetched as page boxes by TMA, else by 16-byte copies.
-// cluster_merge != 0 and 2..8 slices: the slices of a sequence and kv head run as one thread-block
-// cluster and merge through distributed shared memory (mid_o / mid_lse are not used and may be
-// null); otherwise the merge is a second kernel over the scratch.
+// tickets: null, or num_seqs * nkv ints that are zero before the call (and again after it): with
+// them the slices of a sequence and kv head are merged by whichever of their blocks finishes
+// last, without them by a second kernel; the bits are the same.  Calls that share ticket words
+// must not overlap (one stream, or words of their own).
 Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void* kpages, const void* vpages,
                                         const int* block_table, int max_pages, const int* kv_lens,
                                         const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                         float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
                                         int window, int num_splits, long num_rows_kv, int* error_word,
-                                        int cluster_merge, cudaStream_t stream) {
+                                        int* tickets, cudaStream_t stream) {
   return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                 out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
-                                num_rows_kv, error_word, cluster_merge, stream);
+                                num_rows_kv, error_word, tickets, stream);
 }
 
 // The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the
@@ -665,7 +679,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
                                               float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
                                               float scale, int window, int num_splits, const float* q_w,
                                               const float* k_w, float eps, const float* cos_t, const float* sin_t,
-                                              int max_pos, long num_rows_kv, int* error_word, int cluster_merge,
+                                              int max_pos, long num_rows_kv, int* error_word, int* tickets,
                                               cudaStream_t stream) {
   if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w)) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
@@ -674,7 +688,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
   NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos};
   return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
-                               num_rows_kv, error_word, cluster_merge, stream);
+                               num_rows_kv, error_word, tickets, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -744,5 +758,5 @@ Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, co
   float* mid_lse = scratch + partials * D; // [num_seqs, nq, num_splits]
   return q3_paged_attention_decode(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens,
                                    seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window,
-                                   num_splits, 0, nullptr, 0, stream);
+                                   num_splits, 0, nullptr, nullptr, stream);
 }

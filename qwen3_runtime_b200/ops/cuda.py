@@ -65,11 +65,11 @@ _SIGNATURES = {
     "attention_decode": {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_float, c_int, c_int, ctypes.c_long, c_void_p, c_int, c_void_p],
+                                      c_float, c_int, c_int, c_long, c_void_p, c_void_p, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
-                                            c_void_p, c_void_p, c_int, ctypes.c_long, c_void_p, c_int, c_void_p],
+                                            c_void_p, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -127,10 +127,13 @@ class CudaOps:
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         self.tcgen05_pairs = True           # False: the tcgen05 product never pairs SMs (cta_group::1 only)
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
-        # Two variants of the split-KV kernel that are correct and tested but measured slower inside a
-        # whole decode step on a B200 (batch 8, context 4096: 3.36 ms and 3.48 ms against 3.19 ms), so off:
+        # A variant of the split-KV kernel that is correct and tested but measured slower inside a
+        # whole decode step on a B200 (batch 8, context 4096: 3.36 ms against 3.19 ms), so off:
         self.decode_page_boxes = False      # True: keys and values as TMA page boxes instead of 16-byte copies
-        self.decode_cluster_merge = False   # True: up to 8 slices merge inside a thread-block cluster
+        # True: the slices of a sequence and kv head are merged by whichever of their blocks finishes
+        # last (a ticket word per pair); False: by a second kernel.  The bits are the same.
+        self.decode_merge_by_last_block = True
+        self._tickets: torch.Tensor | None = None
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
         # large ones, the register stream (csrc/gemm_small_m.cu) for the rest; "stream" -- the first
         # for everything it supports; "registers" -- always the second
@@ -287,6 +290,7 @@ class CudaOps:
         return out
 
     SM_COUNT = 148  # of a B200; replaced by the device's own count when the table is built
+    TICKETS = 1 << 16  # ticket words for the merge by the last block: sequences x kv heads of one launch
     DECODE_MIN_KEYS_PER_SPLIT = 256
 
     DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
@@ -330,11 +334,16 @@ class CudaOps:
             max_kv_len = min(max_kv_len, int(window) + 63)
         splits = num_splits or self.decode_splits(num_seqs, num_kv_heads, max_kv_len)
         mid_o = mid_lse = None
-        cluster = int(self.decode_cluster_merge and 1 < splits <= 8)
-        if splits > 1 and not cluster:
+        tickets = None
+        if splits > 1:
             mid_o = torch.empty((num_seqs, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
             mid_lse = torch.empty((num_seqs, num_heads, splits), dtype=torch.float32, device=out.device)
-        self.launches += 1 if splits > 1 and not cluster else 0  # the merge kernel
+            if self.decode_merge_by_last_block and num_seqs * num_kv_heads <= self.TICKETS:
+                if self._tickets is None:  # zero between launches: the kernel leaves them so
+                    self._tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=out.device)
+                tickets = self._tickets
+            else:
+                self.launches += 1  # the merge kernel
         # rows of head_dim in the page tensors: lets the kernel fetch page boxes by TMA
         kv_rows = k_pages.shape[0] * num_kv_heads * page_size if self.decode_page_boxes else 0
         err = _ptr(self._error_word(out.device))
@@ -345,13 +354,13 @@ class CudaOps:
                        _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                        num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
                        splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
-                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, kv_rows, err, cluster)
+                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, kv_rows, err, _ptr(tickets))
             return out
         self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                    num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
-                   kv_rows, err, cluster)
+                   kv_rows, err, _ptr(tickets))
         return out
 
     # ---- matrix products ----------------------------------------------------------------
@@ -415,6 +424,8 @@ class CudaOps:
         err = getattr(self, "_err", None)
         if err is not None and int(err.item()) != 0:
             err.zero_()
+            if self._tickets is not None:  # a kernel that gave up may have left tickets drawn
+                self._tickets.zero_()
             raise KernelError("a bounded wait inside a kernel expired (tcgen05 product or attention, or the "
                               "streaming product): the kernel gave up and its output is invalid")
 

@@ -375,17 +375,19 @@ def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list
     return out
 
 
-@pytest.fixture(params=["page boxes, cluster merge", "16-byte copies, cluster merge", "16-byte copies, merge kernel"])
+@pytest.fixture(params=["page boxes, last block merges", "16-byte copies, last block merges",
+                        "16-byte copies, merge kernel"])
 def decode_loader(ops, request):
     """The split-KV kernel fetches keys and values as TMA page boxes where the page size allows it
-    (8, 16, 32, multiples of 64) or with 16-byte copies, and merges up to 8 slices inside a
-    thread-block cluster or (always for more slices) with a second kernel."""
-    before = ops.decode_page_boxes, ops.decode_cluster_merge
+    (8, 16, 32, multiples of 64) or with 16-byte copies, and the slices are merged by the block
+    that finishes last or by a second kernel."""
+    before = ops.decode_page_boxes, ops.decode_merge_by_last_block
     ops.decode_page_boxes = request.param.startswith("page boxes")
-    ops.decode_cluster_merge = "cluster" in request.param
+    ops.decode_merge_by_last_block = "last block" in request.param
     yield request.param
-    ops.decode_page_boxes, ops.decode_cluster_merge = before
+    ops.decode_page_boxes, ops.decode_merge_by_last_block = before
     ops.raise_if_kernel_error()
+    assert ops._tickets is None or not bool(ops._tickets.any()), "every ticket word is zero again after a launch"
 
 
 @pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 16), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
@@ -401,6 +403,28 @@ def test_decode_attention_split_kv(ops, decode_loader, nq, nkv, D, ps, splits):
         want = run_attention(REF, pr, nq, nkv, D, ps, torch.bfloat16, window=window)
         got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
         close(got, want, torch.bfloat16, f"decode attention window={window} splits={splits}", bf16_tol=1e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 16), (14, 2, 64, 3), (6, 2, 256, 16)])
+def test_decode_attention_merge_by_last_block_gives_the_bits_of_the_merge_kernel(ops, nq, nkv, D, ps):
+    """Whichever block of a pair finishes last merges the slices; the result does not depend on
+    which one it was, and equals the merge kernel's bit for bit.  Ticket words are zero afterwards,
+    also with empty slices (windows, lengths far below the slice count)."""
+    lens = [1, 63, 64, 65, 700, 129, 2, 1000, 4096, 333]
+    pr = decode_problem(nq, nkv, D, ps, lens, 81)
+    before = ops.decode_merge_by_last_block
+    try:
+        for splits in (2, 6, 13):
+            for window in (None, 100):
+                ops.decode_merge_by_last_block = False
+                want = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
+                ops.decode_merge_by_last_block = True
+                for _ in range(3):
+                    got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
+                    assert torch.equal(got, want), (splits, window)
+                assert not bool(ops._tickets.any())
+    finally:
+        ops.decode_merge_by_last_block = before
 
 
 @pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 64), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
