@@ -185,6 +185,11 @@ class CacheManager:
             n = min(n, capacity - rc.num_computed)
         return max(0, n)
 
+    def new_pages_needed(self, rc: RequestCache, num_tokens: int) -> list[int]:
+        """Pages that :meth:`reserve` would take from each paged group's pool for these tokens."""
+        need = self.pages_for(rc.num_computed + num_tokens)
+        return [max(0, need - len(table)) for table in rc.tables]
+
     def can_reserve(self, rc: RequestCache, num_tokens: int) -> bool:
         return self.max_reservable(rc, num_tokens) >= num_tokens
 

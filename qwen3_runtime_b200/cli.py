@@ -29,6 +29,8 @@ def _generate(argv: list[str]) -> int:
     parser.add_argument("--prompt-tokens", type=int, nargs="+", default=[151643, 8948, 198, 2610])
     parser.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=None,
                         help="Decode-only CUDA Graph. Default: on.")
+    parser.add_argument("--run-ahead", action=argparse.BooleanOptionalAction, default=True,
+                        help="put the next decode step on the device before reading this one's tokens")
     parser.add_argument("--dtype", default="bfloat16", help="bfloat16 (serving) or float32 (true 32-bit path)")
     parser.add_argument("--temperature", type=float, default=0.0, help="<= 0: greedy")
     parser.add_argument("--top-p", type=float, default=1.0)
@@ -48,7 +50,7 @@ def _generate(argv: list[str]) -> int:
     engine = build_engine(args.model, max_num_seqs=args.max_num_seqs,
                           max_num_batched_tokens=args.max_num_batched_tokens, block_size=args.block_size,
                           dtype=args.dtype, num_kv_blocks=args.num_kv_blocks, cuda_graph=args.cuda_graph,
-                          pin_path=args.pin_path)
+                          pin_path=args.pin_path, run_ahead=args.run_ahead)
     sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                               seed=args.seed)
     out = engine.generate(args.prompt_tokens, max_tokens=args.max_tokens, sampling=sampling)

@@ -32,6 +32,7 @@ class EngineConfig:
     cuda_graph: bool = True  # replay captured decode steps
     dtype: str = "bfloat16"
     kv_memory_fraction: float = 0.85  # share of free device memory given to the pages
+    run_ahead: bool = True  # put the next decode step on the device before reading this one's tokens
 
     def __post_init__(self) -> None:
         if self.block_size < 1:

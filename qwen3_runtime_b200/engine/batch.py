@@ -51,6 +51,10 @@ class BatchBuilder:
         self._capacity = 0
         self.pin = torch.device(device).type == "cuda"
         self._last_decode: dict | None = None  # what the last captured-size decode step packed
+        # device view of the real token ids of the step packed last: whoever has those ids on the
+        # device only (tokens sampled by a step whose result the host has not read yet) writes
+        # them here after packing and before the step runs
+        self.last_token_ids: torch.Tensor | None = None
 
     def _buffers(self, need: int):
         if need > self._capacity:
@@ -116,6 +120,7 @@ class BatchBuilder:
             view = views[self._turn] = (host, host.numpy()[:off], host[:off], device_buffer[:off])
         view[1][:] = image
         view[3].copy_(view[2], non_blocking=True)
+        self.last_token_ids = last["ids_view"]
         if self.pin:
             ev = self._events[self._turn] or torch.cuda.Event()
             ev.record()
@@ -230,6 +235,7 @@ class BatchBuilder:
         R = int(rows_np.size)
         sec("rows")[:R] = rows_np
         dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_token_ids = dev[sections["ids"][0]:sections["ids"][0] + T_real]
         if self.pin:
             ev = self._events[self._turn] or torch.cuda.Event()
             ev.record()
@@ -240,7 +246,8 @@ class BatchBuilder:
             self._last_decode = dict(
                 caches=[e.cache for e in entries], key=(pad_to, table_width, scratch_page, scratch_slot),
                 device_buffer=device_buffer, off=off, width=width, B=B, sections=sections, image=h[:off].copy(),
-                table_lens=[[len(t) for t in e.cache.tables] for e in entries], windowed=windowed, starts=starts.copy())
+                table_lens=[[len(t) for t in e.cache.tables] for e in entries], windowed=windowed, starts=starts.copy(),
+                ids_view=self.last_token_ids)
         if not need_context:
             return None
 

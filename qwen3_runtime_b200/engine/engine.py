@@ -2,6 +2,18 @@
 
 Parity: qwen3_runtime/engine/engine.py:53-92 (``add_request``), :216-260 (``step``),
 :183-205 (``stream_request``), :359-366 (``generate``), :340-357 (per-step stats).
+
+Running ahead.  A decode step's only input that the host does not know beforehand is the
+token the step before it sampled, and that token is on the device already.  So while the
+requests just keep decoding, ``step()`` puts the next step on the device (its token ids
+copied from the sampler's output, device to device) *before* it waits for the tokens of the
+step it returns; the device then never waits for the host between steps.  What the host
+cannot know in time is a stop token: if a request turns out to have finished, the step that
+was already running for it is simply not read for that request (its pages were returned when
+it finished; work queued later on the same stream comes after the abandoned writes).  Nothing
+runs ahead when the batch is about to change: a request waits for admission, one reaches its
+``max_tokens``, pages may run out, or a request's sampling needs the token history on the
+host (penalties).  The tokens are the same with and without running ahead.
 """
 
 from __future__ import annotations
@@ -15,6 +27,16 @@ from .request import Request, RequestStatus
 from .scheduler import Scheduler
 
 
+class _Launched:
+    """A step that is on the device: who takes part, who samples, and the sampler's handle."""
+
+    __slots__ = ("reqs", "sampling", "sampled", "decode_only", "stats")
+
+    def __init__(self, reqs, sampling, sampled, decode_only, stats):
+        self.reqs, self.sampling, self.sampled = reqs, sampling, sampled
+        self.decode_only, self.stats = decode_only, stats
+
+
 class Engine:
     def __init__(self, config: EngineConfig, runner, cache: CacheManager, sampler: Sampler):
         self.config = config
@@ -24,6 +46,8 @@ class Engine:
         self.scheduler = Scheduler(config, cache)
         self._requests: dict[int, Request] = {}
         self.last_step_stats: dict | None = None
+        self._ahead: _Launched | None = None  # the step launched before the last one was read
+        self.num_run_ahead = 0
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, token_ids: list[int], max_tokens: int = 16, *, ignore_eos: bool = True,
@@ -49,11 +73,22 @@ class Engine:
     def step(self) -> list[tuple[int, int | None, bool]]:
         """Schedule and run one batch.  Returns ``(request_id, new token or None, finished)``
         for every request that took part."""
-        preempt_before = self.scheduler.num_preemptions
-        reqs = self.scheduler.schedule()
-        if not reqs:
-            self.last_step_stats = None
-            return []
+        launched, self._ahead = self._ahead, None
+        if launched is not None and all(r.status == RequestStatus.FINISHED for r in launched.reqs):
+            launched = None  # everyone it ran for has finished or was aborted meanwhile
+        if launched is None:
+            preempt_before = self.scheduler.num_preemptions
+            reqs = self.scheduler.schedule()
+            if not reqs:
+                self.last_step_stats = None
+                return []
+            launched = self._launch(reqs, preempt_before)
+        self.last_step_stats = launched.stats
+        if self.config.run_ahead and self._may_run_ahead(launched):
+            self._ahead = self._launch_next_decode(launched)
+        return self._read(launched)
+
+    def _launch(self, reqs: list[Request], preempt_before: int) -> _Launched:
         entries, sampling = [], []
         for req in reqs:
             start = req.cache.num_computed
@@ -63,22 +98,68 @@ class Engine:
                                      [req.num_scheduled_tokens - 1] if samples else []))
             if samples:
                 sampling.append(req)
-        self.last_step_stats = self._collect_step_stats(reqs, preempt_before)
+        stats = self._collect_step_stats(reqs, preempt_before)
+        decode_only = len(sampling) == len(reqs) and all(r.num_scheduled_tokens == 1 for r in reqs)
         logits = self.runner.run(entries)
+        return _Launched(reqs, sampling, self._sample(logits, sampling), decode_only, stats)
+
+    def _sample(self, logits, sampling: list[Request]):
+        if not sampling:
+            return None
+        # kernels with bounded waits report through a device word: its copy rides along with
+        # the step and is looked at after the wait for the sampled tokens
+        ops = self.sampler.ops
+        if hasattr(ops, "watch_kernel_errors"):
+            ops.watch_kernel_errors()
+        return self.sampler.launch(logits, sampling)
+
+    def _may_run_ahead(self, launched: _Launched) -> bool:
+        """The next step is this one again, one token further, whatever this one samples --
+        unless a stop token ends a request, which is found out afterwards."""
+        if not launched.decode_only or self.scheduler.waiting:
+            return False
+        reqs = launched.reqs
+        if len(reqs) != len(self.scheduler.running) or any(a is not b for a, b in zip(reqs, self.scheduler.running)):
+            return False
+        for r in reqs:
+            # the token on its way is output number num_output_tokens + 1: the last one allowed?
+            if r.status != RequestStatus.RUNNING or r.num_output_tokens + 1 >= r.max_tokens:
+                return False
+            if r.sampling.has_penalties():  # needs the token on its way in the host's history
+                return False
+        # pages for everybody's next token, without preempting anyone
+        free = list(self.cache.num_free_pages)
+        for r in reqs:
+            for g, n in enumerate(self.cache.new_pages_needed(r.cache, 1)):
+                free[g] -= n
+        return all(f >= 0 for f in free)
+
+    def _launch_next_decode(self, before: _Launched) -> _Launched:
+        reqs = before.reqs
+        entries = []
+        for req in reqs:
+            self.cache.reserve(req.cache, 1)
+            req.num_scheduled_tokens = 1
+            entries.append(StepEntry(req.cache, [0], [0]))  # the id is on the device: before.sampled.tokens
+        stats = self._collect_step_stats(reqs, self.scheduler.num_preemptions)
+        logits = self.runner.run(entries, device_tokens=before.sampled.tokens)
+        self.num_run_ahead += 1
+        return _Launched(reqs, list(reqs), self._sample(logits, reqs), True, stats)
+
+    def _read(self, launched: _Launched) -> list[tuple[int, int | None, bool]]:
+        """Wait for the step's tokens, append them, finish what is done."""
         tokens: dict[int, int] = {}
-        if sampling:
-            # kernels with bounded waits report through a device word: its copy rides along with
-            # the step and is looked at after the wait for the sampled tokens
+        if launched.sampled is not None:
+            toks, logprobs = self.sampler.read(launched.sampled)
             ops = self.sampler.ops
-            if hasattr(ops, "watch_kernel_errors"):
-                ops.watch_kernel_errors()
-            toks, logprobs = self.sampler.sample(logits, sampling)
             if hasattr(ops, "raise_if_watched_error"):
                 ops.raise_if_watched_error()
-            for req, tok, lp in zip(sampling, toks, logprobs):
+            for req, tok, lp in zip(launched.sampling, toks, logprobs):
                 tokens[req.request_id] = tok
-                if lp is not None:
+                if lp is not None and req.status != RequestStatus.FINISHED:
                     req.logprobs.append(lp)
+        # a request that finished while this step was already running for it takes no part
+        reqs = [r for r in launched.reqs if r.status != RequestStatus.FINISHED]
         finished = {r.request_id for r in self.scheduler.postprocess(reqs, [tokens.get(r.request_id) for r in reqs])}
         out = [(r.request_id, tokens.get(r.request_id), r.request_id in finished) for r in reqs]
         for rid in finished:

@@ -97,7 +97,8 @@ def build_engine(model_dir: str | Path | None = None, *, max_num_seqs: int = 8, 
                  block_size: int = 16, dtype: str = "bfloat16", num_kv_blocks: int | None = None,
                  kv_budget: int | None = None, cuda_graph: bool | None = None, eos_token_id: int | None = None,
                  device="cuda", ops=None, model: DecoderModel | None = None, config=None,
-                 max_positions: int | None = None, pin_path: str | Path | None = None) -> Engine:
+                 max_positions: int | None = None, pin_path: str | Path | None = None,
+                 run_ahead: bool = True) -> Engine:
     """An :class:`Engine` for a model folder (or an already built ``model`` with its ``config``)."""
     dtype = canonical_dtype(dtype)
     raw: dict = {}
@@ -115,7 +116,7 @@ def build_engine(model_dir: str | Path | None = None, *, max_num_seqs: int = 8, 
                        max_num_seqs=max_num_seqs, cuda_graph=cuda_graph, kv_budget=kv_budget)
     cfg = EngineConfig(block_size=block_size, num_kv_blocks=rt.cache.num_pages[0] if rt.cache.num_pages else 0,
                        max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
-                       eos_token_id=eos_token_id, cuda_graph=bool(cuda_graph), dtype=dtype)
+                       eos_token_id=eos_token_id, cuda_graph=bool(cuda_graph), dtype=dtype, run_ahead=bool(run_ahead))
     engine = Engine(cfg, rt.runner, rt.cache, Sampler(model.ops, model.ctx.device))
     engine.runtime = rt
     engine.model_config = config

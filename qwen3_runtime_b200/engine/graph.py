@@ -13,6 +13,7 @@ input and logits buffers, metadata refreshed outside the capture).
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 
 import torch
@@ -41,7 +42,7 @@ class DecodeGraphs:
         self.captured: dict[tuple[int, int], _Captured] = {}
         self.replays = 0
 
-    def try_run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def try_run(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """Logits for the entries that want them (an empty tensor when none does), or None
         when the step is not a decode-only step that fits a bucket."""
         if any(len(e.tokens) != 1 for e in entries):
@@ -57,6 +58,8 @@ class DecodeGraphs:
         if cap is None:
             cap = self._capture(key, entries)
         self._fill(cap, entries, bucket, width, need_context=False)
+        if device_tokens is not None:  # ids that only the device knows, over the placeholders
+            self.runner.builder.last_token_ids.copy_(device_tokens)
         cap.graph.replay()
         self.replays += 1
         wanted = [i for i, e in enumerate(entries) if e.want]
@@ -87,7 +90,17 @@ class DecodeGraphs:
             r.model.forward(step, r.storage)
         torch.cuda.current_stream(r.device).wait_stream(side)
         torch.cuda.synchronize(r.device)
-        with torch.cuda.graph(cap.graph):
-            cap.logits = r.model.forward(step, r.storage)
+        # Python's cycle collector must not run inside the capture: if it finds a dead engine
+        # there (engines hold cycles), freeing its graphs, pinned buffers and events makes CUDA
+        # calls that are not allowed while a stream is capturing and invalidates the capture.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(cap.graph):
+                cap.logits = r.model.forward(step, r.storage)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.captured[key] = cap
         return cap

@@ -37,8 +37,15 @@ class ModelRunner:
             self.graphs = DecodeGraphs(self, graph_batch_sizes)
         self.num_steps = 0
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        """One step; returns logits ``[sum(len(want)), vocab]`` float32, or None."""
+    def run(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
+        """One step; returns logits ``[sum(len(want)), vocab]`` float32, or None.
+
+        ``device_tokens`` (int32, one per entry, every entry bringing one token): the token ids
+        are on the device only -- sampled by a step whose result the host has not read yet --
+        and replace the placeholders in ``entries`` after the step's metadata is packed."""
+        if device_tokens is not None and (any(len(e.tokens) != 1 for e in entries)
+                                          or device_tokens.numel() != len(entries)):
+            raise ValueError("device_tokens: one token per entry, every entry bringing exactly one")
         resets = [e.cache.slot for e in entries if e.cache.needs_state_reset]
         if resets:
             self.storage.zero_state_slots(resets)
@@ -46,10 +53,12 @@ class ModelRunner:
                 e.cache.needs_state_reset = False
         logits = None
         if self.graphs is not None:
-            logits = self.graphs.try_run(entries)
+            logits = self.graphs.try_run(entries, device_tokens)
         if logits is None:
             step = self.builder.build(entries, scratch_page=self.storage.scratch_page,
                                       scratch_slot=self.storage.scratch_slot)
+            if device_tokens is not None:
+                self.builder.last_token_ids.copy_(device_tokens)
             logits = self.model.forward(step, self.storage)
         else:
             logits = logits if logits.numel() else None

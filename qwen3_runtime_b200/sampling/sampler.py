@@ -5,7 +5,8 @@ the device with a uniform number from the request's own CPU generator (so a seed
 gives the same draws on any device, qwen3_runtime/sampling.py:208-227, 293-298).
 Rows that use logit bias, penalties, min_p, top_k or top_p first pass the processor
 kernels, in the reference's order (sampling.py:120-135).  Token ids come back to the
-host in one copy.
+host in one copy, which :meth:`Sampler.launch` starts and :meth:`Sampler.read` waits for, so
+that the engine can put the next step on the device in between.
 """
 
 from __future__ import annotations
@@ -19,13 +20,61 @@ def draw_uniform(generator: torch.Generator | None) -> float:
     return float(torch.rand((), dtype=torch.float32, generator=generator))
 
 
+class Sampled:
+    """What :meth:`Sampler.launch` leaves: the tokens on the device (the next step may read
+    them there) and their copy to the host, under way."""
+
+    __slots__ = ("tokens", "logprobs", "host_tokens", "host_logprobs", "event", "count")
+
+    def __init__(self, tokens, logprobs, host_tokens, host_logprobs, event, count):
+        self.tokens, self.logprobs = tokens, logprobs
+        self.host_tokens, self.host_logprobs = host_tokens, host_logprobs
+        self.event, self.count = event, count
+
+
 class Sampler:
+    RING = 4  # pinned result buffers; at most two steps are ever unread
+
     def __init__(self, ops, device):
         self.ops = ops
         self.device = device
+        self.on_cuda = torch.device(device).type == "cuda"
+        self._ring: list[tuple[torch.Tensor, torch.Tensor]] = []
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, requests: list) -> tuple[list[int], list[float | None]]:
         """``logits`` [R, V] float32, one row per request in ``requests``."""
+        return self.read(self.launch(logits, requests))
+
+    def launch(self, logits: torch.Tensor, requests: list) -> Sampled:
+        """Choose on the device and start the copy to the host; waits for nothing."""
+        tok, lp = self._choose(logits, requests)
+        R = len(requests)
+        if not self.on_cuda:
+            return Sampled(tok, lp, tok, lp, None, R)
+        if not self._ring or self._ring[0][0].numel() < R:
+            size = max(64, 1 << (R - 1).bit_length())
+            self._ring = [(torch.zeros(size, dtype=torch.int32, pin_memory=True),
+                           torch.zeros(size, dtype=torch.float32, pin_memory=True)) for _ in range(self.RING)]
+        self._turn = (self._turn + 1) % self.RING
+        host_tok, host_lp = self._ring[self._turn]
+        host_tok[:R].copy_(tok, non_blocking=True)
+        if lp is not None:
+            host_lp[:R].copy_(lp, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return Sampled(tok, lp, host_tok, host_lp if lp is not None else None, event, R)
+
+    def read(self, sampled: Sampled) -> tuple[list[int], list[float | None]]:
+        if sampled.event is not None:
+            sampled.event.synchronize()
+        R = sampled.count
+        toks = sampled.host_tokens[:R].tolist()
+        lps = sampled.host_logprobs[:R].tolist() if sampled.host_logprobs is not None else [None] * R
+        return toks, lps
+
+    def _choose(self, logits: torch.Tensor, requests: list) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """int32 tokens [R] (and float32 log-probabilities, if any request asks) on the device."""
         R = len(requests)
         if logits.shape[0] != R:
             raise ValueError(f"logits rows {logits.shape[0]} must equal {R} sampling requests")
@@ -38,7 +87,7 @@ class Sampler:
             logits = self._process(logits, requests, touched)
         if len(greedy) == R:
             tok, lp = self.ops.argmax(logits, want_lp)
-            return tok.tolist(), (lp.tolist() if want_lp else [None] * R)
+            return tok, (lp if want_lp else None)
         # rows that went through the filters are already divided by their temperature
         filtered = {i for i in touched if not params[i].is_greedy() and params[i].needs_filter()}
         temps = [1.0 if (p.is_greedy() or i in filtered) else p.temperature for i, p in enumerate(params)]
@@ -53,7 +102,7 @@ class Sampler:
             tok_s = torch.where(mask, tok_g, tok_s)
             if want_lp:
                 lp_s = torch.where(mask, lp_g, lp_s)
-        return tok_s.tolist(), (lp_s.tolist() if want_lp else [None] * R)
+        return tok_s, (lp_s if want_lp else None)
 
     def _to_device(self, host: torch.Tensor) -> torch.Tensor:
         if torch.device(self.device).type == "cuda":

@@ -191,3 +191,80 @@ def case_temperature_sampling(tmp_path, name, dtype, ops, device):
             # the chosen token's interval of the CDF contains u (up to float32 rounding of the sums)
             assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5, (tok, u, lo, float(cdf[tok]))
             ids.append(tok)
+
+
+def case_run_ahead(tmp_path, name, dtype, ops, device, *, cuda_graph=False):
+    """The engine puts the next decode step on the device before it reads the tokens of the last
+    one.  The tokens are those of the engine that does not, step by step: with requests of
+    different lengths, a stop token that ends one of them while a step is already running for
+    it, seeded temperature sampling, a request that arrives later, one that is aborted, and so
+    few pages that a request is preempted."""
+    from qwen3_runtime_b200 import SamplingParams
+
+    folder = make_model_dir(tmp_path, name)
+    ps = TINY[name]["page_size"]
+    vocab = TINY[name]["config"].vocab_size
+    prompts = list(requests_for(name, (7, 19, 5, 13), seed=8).values())
+
+    def engine(run_ahead, pages=64, eos=None):
+        return build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=pages,
+                            max_num_seqs=4, max_num_batched_tokens=16, cuda_graph=cuda_graph, run_ahead=run_ahead,
+                            eos_token_id=eos)
+
+    def scenario(eng, stop=(), late=True, abort=False):
+        lengths = (12, 5, 9, 12)
+        sampling = [SamplingParams(), SamplingParams(temperature=0.9, seed=3), SamplingParams(),
+                    SamplingParams(temperature=0.7, top_k=20, seed=4)]
+        ids = [eng.add_request(p, max_tokens=n, sampling=s, ignore_eos=not stop, stop_token_ids=tuple(stop))
+               for p, n, s in zip(prompts[:3], lengths, sampling)]
+        reqs = [eng.get_request(i) for i in ids]
+        steps = []
+        for i in range(200):
+            if late and i == 6:  # arrives while the others decode
+                ids.append(eng.add_request(prompts[3], max_tokens=lengths[3], sampling=sampling[3]))
+                reqs.append(eng.get_request(ids[-1]))
+            if abort and i == 9 and reqs[0].status.name != "FINISHED":
+                eng.abort_request(ids[0])
+            out = eng.step()
+            if not out:
+                break
+            first = ids[0]
+            steps.append(sorted((rid - first, tok, fin) for rid, tok, fin in out))
+        assert eng.is_finished() and eng.cache.num_free_pages == eng.cache.num_pages
+        eng.cache.check_invariants()
+        return steps, [r.output_token_ids for r in reqs], [r.finish_reason for r in reqs]
+
+    # (1) plain: lengths differ, one request arrives late
+    want = scenario(engine(False))
+    eng = engine(True)
+    got = scenario(eng)
+    assert got == want
+    assert eng.num_run_ahead >= 4, "decode steps were meant to run ahead"
+    assert got[2] == ["length"] * 4
+    # (2) a stop token: the third output token of the first request (it decodes greedily)
+    stop = [want[1][0][2]]
+    want_stop = scenario(engine(False), stop=stop)
+    eng = engine(True)
+    got_stop = scenario(eng, stop=stop)
+    assert got_stop == want_stop and "stop" in got_stop[2] and eng.num_run_ahead >= 1
+    assert len(got_stop[1][0]) <= 3
+    # (3) aborted while a step may be running for it
+    want_abort = scenario(engine(False), abort=True)
+    got_abort = scenario(engine(True), abort=True)
+    assert got_abort == want_abort and got_abort[2][0] == "abort"
+    # (4) so few pages that somebody is preempted: never runs ahead into a pool that cannot take it
+    tight_prompts = [random_ids(vocab, 2 * ps, 77), random_ids(vocab, ps, 78)]
+
+    def squeeze(run_ahead):
+        eng = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=3, max_num_seqs=4,
+                           max_num_batched_tokens=64, cuda_graph=cuda_graph, run_ahead=run_ahead)
+        out = eng.generate_batch(tight_prompts, max_tokens=8)
+        assert eng.scheduler.num_preemptions >= 1 and eng.cache.num_free_pages == eng.cache.num_pages
+        return out
+
+    assert squeeze(True) == squeeze(False)
+    # (5) an engine that is left with a step in flight (everybody stopped) starts afresh
+    eng = engine(True)
+    first = eng.generate(prompts[0], max_tokens=6, ignore_eos=False, stop_token_ids=(want[1][0][2],))
+    again = eng.generate(prompts[2], max_tokens=6)
+    assert first == want[1][0][:len(first)] and first[-1] == want[1][0][2] and again == want[1][2][:6], (first, again, want[1])

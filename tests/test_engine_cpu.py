@@ -40,3 +40,8 @@ def test_without_a_gpu_the_product_path_refuses_loudly():
         pytest.skip("a CUDA device is present")
     with pytest.raises(KernelsUnavailable, match="no CPU path"):
         CudaOps()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_running_ahead_gives_the_same_tokens_step_by_step(tmp_path, name):
+    ec.case_run_ahead(tmp_path, name, "float32", OPS, DEV)

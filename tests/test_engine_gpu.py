@@ -44,6 +44,13 @@ def test_greedy_generation(tmp_path, ops, name, dtype, cuda_graph):
     ec.case_greedy_generation(tmp_path, name, dtype, ops, "cuda", cuda_graph=cuda_graph)
 
 
+@pytest.mark.parametrize("cuda_graph", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_running_ahead_gives_the_same_tokens_step_by_step(tmp_path, ops, name, dtype, cuda_graph):
+    ec.case_run_ahead(tmp_path, name, dtype, ops, "cuda", cuda_graph=cuda_graph)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_temperature_sampling(tmp_path, ops, dtype):
     ec.case_temperature_sampling(tmp_path, "B", dtype, ops, "cuda")
