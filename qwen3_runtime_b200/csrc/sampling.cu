@@ -39,6 +39,116 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ token, 
   }
 }
 
+// The same for few rows: with one block per row a batch of 8 keeps 8 SMs busy for tens of
+// microseconds.  Here a row is cut into `slices` equal parts, one block each; a block leaves its
+// best value, the lowest index that has it and (for the log-probability) sum exp(x - best) over
+// its part, draws a ticket for its row, and the block that draws the last one merges the
+// row's parts: greatest value, lowest index among equals; z = sum z_s * exp(best_s - top).
+struct ArgmaxPart {
+  float best;
+  int idx;
+  float z;
+  int pad;
+};
+
+#define ARGMAX_SPLIT_THREADS 256
+
+__global__ void __launch_bounds__(ARGMAX_SPLIT_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, int V, int slices, ArgmaxPart* __restrict__ parts,
+                    int* __restrict__ tickets, int* __restrict__ token, float* __restrict__ logprob) {
+  __shared__ float red[33];
+  __shared__ int best_idx;
+  __shared__ int last;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y, s = blockIdx.x;
+  const float* row = logits + (long)r * V;
+  int per = (V + slices - 1) / slices;
+  per = (per + 3) & ~3;
+  const int lo = s * per, hi = min(V, lo + per);
+  const bool vec = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  float best = -INFINITY;
+  int idx = INT_MAX;
+  if (vec) {
+    for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {  // hi - lo and lo are multiples of 4
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (e[k] > best) {  // ascending index: the first of equals stays
+          best = e[k];
+          idx = i + k;
+        }
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best) {
+        best = v;
+        idx = i;
+      }
+    }
+  }
+  const float top = block_max(best, red);
+  if (threadIdx.x == 0) best_idx = INT_MAX;
+  __syncthreads();
+  if (best == top && idx != INT_MAX) atomicMin(&best_idx, idx);
+  __syncthreads();
+  float z = 0.f;
+  if (logprob && best_idx != INT_MAX) {
+    float sum = 0.f;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) sum += expf(row[i] - top);
+    z = block_sum(sum, red);
+  }
+  if (threadIdx.x == 0) {
+    ArgmaxPart part;
+    part.best = top;
+    part.idx = best_idx;
+    part.z = z;
+    part.pad = 0;
+    parts[(long)r * slices + s] = part;
+    __threadfence();
+    last = atomicAdd(tickets + r, 1) == slices - 1;
+    if (last) tickets[r] = 0;  // for the next launch
+  }
+  __syncthreads();
+  if (!last || threadIdx.x >= 32) return;
+  __threadfence();
+  // one warp merges the row's parts
+  const float4* in = reinterpret_cast<const float4*>(parts + (long)r * slices);
+  float mbest = -INFINITY;
+  int midx = INT_MAX;
+  for (int k = threadIdx.x; k < slices; k += 32) {
+    const float4 raw = __ldcg(in + k);
+    const float b = raw.x;
+    const int i = __float_as_int(raw.y);
+    if (i != INT_MAX && (b > mbest || (b == mbest && i < midx))) {
+      mbest = b;
+      midx = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, mbest, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, midx, o);
+    if (oi != INT_MAX && (ob > mbest || (ob == mbest && oi < midx))) {
+      mbest = ob;
+      midx = oi;
+    }
+  }
+  if (midx == INT_MAX) midx = 0;  // a row without any comparable value (all NaN)
+  if (threadIdx.x == 0) token[r] = midx;
+  if (logprob) {
+    float zsum = 0.f;
+    for (int k = threadIdx.x; k < slices; k += 32) {
+      const float4 raw = __ldcg(in + k);
+      if (__float_as_int(raw.y) != INT_MAX) zsum += raw.z * expf(raw.x - mbest);
+    }
+    zsum = warp_sum(zsum);
+    if (threadIdx.x == 0) logprob[r] = row[midx] - mbest - logf(zsum);
+  }
+}
+
 // x = logits / temperature; p = softmax(x); token = first i with cumsum(p)[i] > u.
 // The cumulative sum runs in index order: a chunk of blockDim * ITEMS consecutive
 // elements at a time, each thread summing ITEMS consecutive ones, the block scanning
@@ -100,10 +210,19 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   }
 }
 
-Q3_EXPORT int q3_argmax(const float* logits, int num_rows, int V, int* token, float* logprob,
-                        cudaStream_t stream) {
-  if (!logits || !token || V < 1) return Q3_ERR_ARGUMENT;
+// scratch / tickets (both may be null: one block per row): `slices` x 16 bytes per row, 16-byte
+// aligned, and an int per row that is zero before the call and again after it.  slices <= 1024.
+Q3_EXPORT int q3_argmax(const float* logits, int num_rows, int V, int* token, float* logprob, void* scratch,
+                        int* tickets, int slices, cudaStream_t stream) {
+  if (!logits || !token || V < 1 || slices < 0 || slices > 1024) return Q3_ERR_ARGUMENT;
   if (num_rows == 0) return Q3_OK;
+  if (slices > 1 && scratch && tickets && num_rows <= 65535) {
+    if (reinterpret_cast<uintptr_t>(scratch) & 15) return Q3_ERR_ARGUMENT;
+    return launch_pdl(argmax_split_kernel, dim3(slices, num_rows), dim3(ARGMAX_SPLIT_THREADS), 0, stream, logits, V,
+                      slices, static_cast<ArgmaxPart*>(scratch), tickets, token, logprob) == cudaSuccess
+               ? Q3_OK
+               : Q3_ERR_LAUNCH;
+  }
   argmax_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, token, logprob);
   return q3_launch_status();
 }

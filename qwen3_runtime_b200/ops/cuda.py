@@ -101,7 +101,7 @@ _SIGNATURES = {
                                  c_void_p, c_void_p],
     },
     "sampling": {
-        "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "q3_bias_penalty": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                             c_float, c_void_p],
@@ -134,6 +134,7 @@ class CudaOps:
         # last (a ticket word per pair); False: by a second kernel.  The bits are the same.
         self.decode_merge_by_last_block = True
         self._tickets: torch.Tensor | None = None
+        self._argmax_tickets: torch.Tensor | None = None
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
         # large ones, the register stream (csrc/gemm_small_m.cu) for the rest; "stream" -- the first
         # for everything it supports; "registers" -- always the second
@@ -426,6 +427,8 @@ class CudaOps:
             err.zero_()
             if self._tickets is not None:  # a kernel that gave up may have left tickets drawn
                 self._tickets.zero_()
+            if self._argmax_tickets is not None:
+                self._argmax_tickets.zero_()
             raise KernelError("a bounded wait inside a kernel expired (tcgen05 product or attention, or the "
                               "streaming product): the kernel gave up and its output is invalid")
 
@@ -519,8 +522,16 @@ class CudaOps:
         R, V = logits.shape
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
+        # few rows: cut each into slices so that about two blocks per SM share the work
+        slices = min(1024, 2 * self.SM_COUNT // max(R, 1), V // 2048)
+        scratch = tickets = None
+        if slices > 1 and R <= self.TICKETS:
+            if self._argmax_tickets is None:  # zero between launches: the kernel leaves them so
+                self._argmax_tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=logits.device)
+            tickets = self._argmax_tickets
+            scratch = torch.empty((R, slices, 4), dtype=torch.float32, device=logits.device)
         self._call("sampling", "q3_argmax", "argmax",
-                   _ptr(logits), R, V, _ptr(token), _ptr(logprob))
+                   _ptr(logits), R, V, _ptr(token), _ptr(logprob), _ptr(scratch), _ptr(tickets), max(slices, 0))
         return token, logprob
 
     def sample(self, logits, temperature, uniform, want_logprob=False):

@@ -670,17 +670,32 @@ def test_gemm_tcgen05_swiglu(ops, M, I, K, pair):
     close(out, torch.nn.functional.silu(g) * u, torch.bfloat16, "tcgen05 fused SwiGLU", bf16_tol=1e-2)
 
 
-@pytest.mark.parametrize("V,R", [(151936, 3), (301, 5), (32, 1), (4099, 64)])
+@pytest.mark.parametrize("V,R", [(151936, 3), (301, 5), (32, 1), (4099, 64), (151936, 8), (151937, 1), (40000, 33),
+                                 (151936, 200), (8192, 2)])
 def test_argmax_lowest_index_on_ties(ops, V, R):
+    """One block per row, or (few rows, long rows) a row cut into slices whose last block merges."""
     logits = rand((R, V), torch.float32, 60)
     logits[0, V // 3] = 50.0
-    logits[0, V - 1] = 50.0  # tie: the lower index wins
+    logits[0, V - 1] = 50.0  # tie, in different slices of a long row: the lower index wins
+    if R > 1:
+        logits[1, 5] = logits[1, 6] = 60.0  # tie of neighbours
+    if R > 2:
+        logits[2] = float("nan")  # nothing comparable: token 0, as the one-block kernel answers
     tok, lp = ops.argmax(logits, want_logprob=True)
+    plain = [r for r in range(R) if r not in (0, 1, 2)]
     want = logits.argmax(-1)
     assert tok[0].item() == V // 3
-    assert torch.equal(tok.long()[1:], want[1:])
+    if R > 1:
+        assert tok[1].item() == 5
+    if R > 2:
+        assert tok[2].item() == 0
+    assert torch.equal(tok.long()[plain], want[plain])
+    rows = [r for r in range(R) if r != 2]
     ref_lp = torch.log_softmax(logits, -1).gather(1, tok.long()[:, None])[:, 0]
-    assert float((lp - ref_lp).abs().max()) < 1e-4
+    assert float((lp[rows] - ref_lp[rows]).abs().max()) < 1e-4
+    only_tok, none = ops.argmax(logits)
+    assert none is None and torch.equal(only_tok, tok)
+    assert ops._argmax_tickets is None or not bool(ops._argmax_tickets.any())
 
 
 @pytest.mark.parametrize("V,R", [(151936, 4), (301, 16), (4099, 3)])
