@@ -3,7 +3,7 @@
 // Parity: qwen3_runtime/sampling.py:28-32 (argmax, lowest id on ties), :260-270
 // (softmax(logits / temperature)), :208-227 (first index whose cumulative
 // probability exceeds u, clamped to the vocabulary).
-#include "common.cuh"
+#include "async_tiles.cuh"
 #include <limits.h>
 
 #define SAMPLE_THREADS 1024
@@ -210,6 +210,154 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   }
 }
 
+// The same draw for few long rows: a row is cut into `slices` parts, one block each, which leave
+// their maximum and sum exp(x - maximum); the block that draws the row's last ticket merges them
+// to the row's maximum and normaliser, adds the parts' masses up in order to find the part in
+// which the cumulative sum passes u, and scans only from there (carrying the mass before it).
+__global__ void __launch_bounds__(ARGMAX_SPLIT_THREADS)
+sample_split_kernel(const float* __restrict__ logits, int V, int slices, float2* __restrict__ parts,
+                    int* __restrict__ tickets, const float* __restrict__ temperature,
+                    const float* __restrict__ uniform, int* __restrict__ token, float* __restrict__ logprob) {
+  constexpr int ITEMS = 4;
+  constexpr int T = ARGMAX_SPLIT_THREADS;
+  __shared__ float red[33];
+  __shared__ float scan[T];
+  __shared__ int found;
+  __shared__ int last;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y, s = blockIdx.x;
+  const float* row = logits + (long)r * V;
+  const float temp = temperature[r];
+  const float u = uniform[r];
+  int per = (V + slices - 1) / slices;
+  per = (per + 3) & ~3;
+  const int lo = s * per, hi = min(V, lo + per);
+  float mx = -INFINITY;
+  for (int i = lo + threadIdx.x; i < hi; i += T) mx = fmaxf(mx, row[i] / temp);
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  if (mx != -INFINITY)  // a part that the filters emptied weighs nothing (and -inf - -inf is no number)
+    for (int i = lo + threadIdx.x; i < hi; i += T) sum += expf(row[i] / temp - mx);
+  sum = block_sum(sum, red);
+  if (threadIdx.x == 0) {
+    parts[(long)r * slices + s] = make_float2(mx, lo < hi ? sum : 0.f);
+    __threadfence();
+    last = atomicAdd(tickets + r, 1) == slices - 1;
+    if (last) tickets[r] = 0;  // for the next launch
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  // ---- the row's maximum and normaliser from the parts (fixed order: the same bits every time)
+  const float2* in = parts + (long)r * slices;
+  float top = -INFINITY;
+  for (int k = threadIdx.x; k < slices; k += T) {
+    const float2 p = __ldcg(in + k);
+    if (p.y > 0.f) top = fmaxf(top, p.x);
+  }
+  top = block_max(top, red);
+  float zpart = 0.f;
+  for (int k = threadIdx.x; k < slices; k += T) {
+    const float2 p = __ldcg(in + k);
+    if (p.y > 0.f) zpart += p.y * expf(p.x - top);
+  }
+  const float z = block_sum(zpart, red);
+  // ---- the part in which the cumulative mass passes u: thread t adds up parts [t*each, (t+1)*each)
+  const int each = (slices + T - 1) / T;
+  float mass[4];  // slices <= 1024 = 4 * T
+  float mine = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int k = threadIdx.x * each + e;
+    mass[e] = 0.f;
+    if (e < each && k < slices) {
+      const float2 p = __ldcg(in + k);
+      if (p.y > 0.f) mass[e] = p.y * expf(p.x - top) / z;
+    }
+    mine += mass[e];
+  }
+  scan[threadIdx.x] = mine;
+  if (threadIdx.x == 0) found = INT_MAX;
+  __syncthreads();
+  for (int off = 1; off < T; off <<= 1) {  // inclusive Hillis-Steele scan
+    const float add = threadIdx.x >= off ? scan[threadIdx.x - off] : 0.f;
+    __syncthreads();
+    scan[threadIdx.x] += add;
+    __syncthreads();
+  }
+  {
+    float c = scan[threadIdx.x] - mine;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int k = threadIdx.x * each + e;
+      if (e < each && k < slices) {
+        c += mass[e];
+        if (c > u) {
+          atomicMin(&found, k);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int start_slice = found == INT_MAX ? slices - 1 : found;
+  __syncthreads();
+  // mass before that part, added up the same way
+  float before = 0.f;
+  {
+    const int owner = start_slice / each;
+    if ((int)threadIdx.x == owner) {
+      float c = scan[threadIdx.x] - mine;
+      for (int e = 0; e < start_slice - owner * each; ++e) c += mass[e];
+      scan[0] = c;  // every thread has read its scan value
+    }
+    __syncthreads();
+    before = scan[0];
+    __syncthreads();
+  }
+  // ---- scan the elements from that part on (as sample_kernel does from the start of the row)
+  if (threadIdx.x == 0) found = INT_MAX;
+  __syncthreads();
+  float carried = before;
+  const int chunk = T * ITEMS;
+  for (int base = start_slice * per; base < V && found == INT_MAX; base += chunk) {
+    const int first = base + threadIdx.x * ITEMS;
+    float pr[ITEMS];
+    float my = 0.f;
+#pragma unroll
+    for (int e = 0; e < ITEMS; ++e) {
+      pr[e] = first + e < V ? expf(row[first + e] / temp - top) / z : 0.f;
+      my += pr[e];
+    }
+    scan[threadIdx.x] = my;
+    __syncthreads();
+    for (int off = 1; off < T; off <<= 1) {
+      const float add = threadIdx.x >= off ? scan[threadIdx.x - off] : 0.f;
+      __syncthreads();
+      scan[threadIdx.x] += add;
+      __syncthreads();
+    }
+    float c = carried + scan[threadIdx.x] - my;
+#pragma unroll
+    for (int e = 0; e < ITEMS; ++e) {
+      c += pr[e];
+      if (first + e < V && c > u) {
+        atomicMin(&found, first + e);
+        break;
+      }
+    }
+    carried += scan[T - 1];
+    __syncthreads();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int chosen = found == INT_MAX ? V - 1 : found;
+    token[r] = chosen;
+    if (logprob) logprob[r] = logf(fmaxf(expf(row[chosen] / temp - top) / z, 1e-30f));
+  }
+}
+
 // scratch / tickets (both may be null: one block per row): `slices` x 16 bytes per row, 16-byte
 // aligned, and an int per row that is zero before the call and again after it.  slices <= 1024.
 Q3_EXPORT int q3_argmax(const float* logits, int num_rows, int V, int* token, float* logprob, void* scratch,
@@ -227,10 +375,20 @@ Q3_EXPORT int q3_argmax(const float* logits, int num_rows, int V, int* token, fl
   return q3_launch_status();
 }
 
+// scratch / tickets / slices as for q3_argmax (8 bytes of scratch per slice and row are used).
 Q3_EXPORT int q3_sample(const float* logits, int num_rows, int V, const float* temperature,
-                        const float* uniform, int* token, float* logprob, cudaStream_t stream) {
-  if (!logits || !token || !temperature || !uniform || V < 1) return Q3_ERR_ARGUMENT;
+                        const float* uniform, int* token, float* logprob, void* scratch, int* tickets, int slices,
+                        cudaStream_t stream) {
+  if (!logits || !token || !temperature || !uniform || V < 1 || slices < 0 || slices > 1024) return Q3_ERR_ARGUMENT;
   if (num_rows == 0) return Q3_OK;
+  if (slices > 1 && scratch && tickets && num_rows <= 65535) {
+    if (reinterpret_cast<uintptr_t>(scratch) & 7) return Q3_ERR_ARGUMENT;
+    return launch_pdl(sample_split_kernel, dim3(slices, num_rows), dim3(ARGMAX_SPLIT_THREADS), 0, stream, logits, V,
+                      slices, static_cast<float2*>(scratch), tickets, temperature, uniform, token, logprob) ==
+                   cudaSuccess
+               ? Q3_OK
+               : Q3_ERR_LAUNCH;
+  }
   sample_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, uniform, token, logprob);
   return q3_launch_status();
 }
@@ -331,6 +489,126 @@ filter_kernel(float* __restrict__ logits, int V, const float* __restrict__ tempe
   }
 }
 
+// The same filters with the row in registers: a cluster of 8 blocks holds one row (thread t of
+// block b has elements b*512 + t + 4096*k), so a bisection step is arithmetic on registers and
+// one sum over the cluster instead of a pass over memory by a single block (1.8 ms for a
+// vocabulary of 152 K became tens of microseconds).  Sums over the cluster: every block
+// reduces its own part, leaves it in its shared memory, and after a cluster barrier every block
+// adds the 8 parts in rank order, so all blocks see the same bits and take the same branch.
+// Two slots used in turn make one barrier per sum enough.
+constexpr int FILTER_CLUSTER = 8;
+constexpr int FILTER_THREADS = 512;  // 128 registers a thread: room for 40 elements of the row
+
+struct ClusterReducer {
+  float* red;        // [33] block scratch
+  float* slots;      // [2] this block's part, by turn
+  unsigned turn;
+  __device__ __forceinline__ float finish(float mine, bool is_max) {
+    float* slot = slots + (turn & 1);
+    if (threadIdx.x == 0) *slot = mine;
+    cluster_sync_all();
+    float total = is_max ? -INFINITY : 0.f;
+    for (int r = 0; r < FILTER_CLUSTER; ++r) {
+      float v;
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(smem_addr(slot), r)) : "memory");
+      total = is_max ? fmaxf(total, v) : total + v;
+    }
+    ++turn;
+    return total;
+  }
+  __device__ __forceinline__ float sum(float part) { return finish(block_sum(part, red), false); }
+  __device__ __forceinline__ float max(float part) { return finish(block_max(part, red), true); }
+};
+
+// smallest key k with measure({element : key(x) > k}) <= limit; the measure is the number of
+// elements (count_mode) or the sum of exp(x - mx) / z.  Elements past the end of the row count
+// for nothing.
+template <int ITEMS>
+__device__ unsigned cutoff_key_regs(const float (&x)[ITEMS], int first, int V, bool count_mode, float limit, float mx,
+                                    float z, ClusterReducer& cr) {
+  constexpr int STEP = FILTER_CLUSTER * FILTER_THREADS;
+  unsigned lo = 0u, hi = 0xffffffffu;
+  while (lo < hi) {
+    const unsigned mid = lo + ((hi - lo) >> 1);
+    float part = 0.f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      if (first + k * STEP < V && ordered_key(x[k]) > mid) part += count_mode ? 1.f : expf(x[k] - mx) / z;
+    if (cr.sum(part) <= limit) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+template <int ITEMS>
+__global__ void __cluster_dims__(FILTER_CLUSTER, 1, 1) __launch_bounds__(FILTER_THREADS)
+filter_cluster_kernel(float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                      const float* __restrict__ min_p, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p) {
+  __shared__ float red[33];
+  __shared__ float slots[2];
+  ClusterReducer cr{red, slots, 0u};
+  const int r = blockIdx.y;
+  float* row = logits + (long)r * V;
+  const float temp = temperature[r];
+  const float mp = min_p[r], tp = top_p[r];
+  const int tk = top_k[r];
+  const float lowest = -3.4028234663852886e38f;  // finfo(float32).min, the reference's mask value
+  const int first = blockIdx.x * FILTER_THREADS + threadIdx.x;
+  constexpr int STEP = FILTER_CLUSTER * FILTER_THREADS;
+  // elements past the end are -inf, and left out of every count and sum
+  float x[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = first + k * STEP;
+    x[k] = i < V ? row[i] : -INFINITY;
+    if (temp != 1.f && i < V) x[k] = x[k] / temp;
+  }
+  if (mp > 0.f) {  // drop tokens whose probability is below min_p times the largest (sampling.py:75-81)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) mx = fmaxf(mx, x[k]);
+    mx = cr.max(mx);
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      if (expf(x[k] - mx) < mp) x[k] = -INFINITY;
+  }
+  if (tk > 0 && tk < V) {  // keep the k largest, ties with the k-th included (sampling.py:96-99)
+    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, true, (float)(tk - 1), 0.f, 1.f, cr);
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      if (ordered_key(x[k]) < cut) x[k] = lowest;
+  }
+  if (tp > 0.f && tp < 1.f) {  // nucleus: keep a token iff the mass ranked before it is <= top_p (:100-108)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) mx = fmaxf(mx, first + k * STEP < V ? x[k] : -INFINITY);
+    mx = cr.max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      if (first + k * STEP < V) s += expf(x[k] - mx);
+    const float z = cr.sum(s);
+    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, false, tp, mx, z, cr);
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      if (ordered_key(x[k]) < cut) x[k] = lowest;
+  }
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = first + k * STEP;
+    if (i < V) row[i] = x[k];
+  }
+  cluster_sync_all();  // nobody leaves while a neighbour may still read its slot
+}
+
+template <int ITEMS>
+static int launch_filter_cluster(float* logits, int num_rows, int V, const float* temperature, const float* min_p,
+                                 const int* top_k, const float* top_p, cudaStream_t stream) {
+  filter_cluster_kernel<ITEMS><<<dim3(FILTER_CLUSTER, num_rows), FILTER_THREADS, 0, stream>>>(
+      logits, V, temperature, min_p, top_k, top_p);
+  return q3_launch_status();
+}
+
 Q3_EXPORT int q3_bias_penalty(float* row, int V, const int* bias_ids, const float* bias_vals, int n_bias,
                               const int* seen_ids, int n_seen, int* counts, float repetition, float presence,
                               float frequency, cudaStream_t stream) {
@@ -345,6 +623,14 @@ Q3_EXPORT int q3_filter(float* logits, int num_rows, int V, const float* tempera
                         const int* top_k, const float* top_p, cudaStream_t stream) {
   if (!logits || !temperature || !min_p || !top_k || !top_p || V < 1) return Q3_ERR_ARGUMENT;
   if (num_rows == 0) return Q3_OK;
+  // rows that fit the registers of a cluster of 8 blocks (up to 163,840 elements) and are long
+  // enough to be worth it; the others take one block per row and passes over memory
+  constexpr int PER_ITEM = FILTER_CLUSTER * FILTER_THREADS;
+  if (V > 4096 && num_rows <= 65535) {
+    if (V <= 8 * PER_ITEM) return launch_filter_cluster<8>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+    if (V <= 20 * PER_ITEM) return launch_filter_cluster<20>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+    if (V <= 40 * PER_ITEM) return launch_filter_cluster<40>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+  }
   filter_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, min_p, top_k, top_p);
   return q3_launch_status();
 }

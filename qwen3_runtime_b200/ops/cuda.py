@@ -102,7 +102,8 @@ _SIGNATURES = {
     },
     "sampling": {
         "q3_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
-        "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "q3_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_void_p],
         "q3_bias_penalty": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                             c_float, c_void_p],
         "q3_filter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -522,24 +523,30 @@ class CudaOps:
         R, V = logits.shape
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
-        # few rows: cut each into slices so that about two blocks per SM share the work
-        slices = min(1024, 2 * self.SM_COUNT // max(R, 1), V // 2048)
-        scratch = tickets = None
-        if slices > 1 and R <= self.TICKETS:
-            if self._argmax_tickets is None:  # zero between launches: the kernel leaves them so
-                self._argmax_tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=logits.device)
-            tickets = self._argmax_tickets
-            scratch = torch.empty((R, slices, 4), dtype=torch.float32, device=logits.device)
+        slices, scratch, tickets = self._row_slices(logits)
         self._call("sampling", "q3_argmax", "argmax",
-                   _ptr(logits), R, V, _ptr(token), _ptr(logprob), _ptr(scratch), _ptr(tickets), max(slices, 0))
+                   _ptr(logits), R, V, _ptr(token), _ptr(logprob), _ptr(scratch), _ptr(tickets), slices)
         return token, logprob
+
+    def _row_slices(self, logits):
+        """Few long rows: cut each into slices so that about two blocks per SM share the work; the
+        slices' results meet in a scratch, and a ticket word per row tells the last block."""
+        R, V = logits.shape
+        slices = max(0, min(1024, 2 * self.SM_COUNT // max(R, 1), V // 2048))
+        if slices <= 1 or R > self.TICKETS:
+            return 0, None, None
+        if self._argmax_tickets is None:  # zero between launches: the kernels leave them so
+            self._argmax_tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=logits.device)
+        scratch = torch.empty((R, slices, 4), dtype=torch.float32, device=logits.device)
+        return slices, scratch, self._argmax_tickets
 
     def sample(self, logits, temperature, uniform, want_logprob=False):
         R, V = logits.shape
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
-        self._call("sampling", "q3_sample", "sample",
-                   _ptr(logits), R, V, _ptr(temperature), _ptr(uniform), _ptr(token), _ptr(logprob))
+        slices, scratch, tickets = self._row_slices(logits)
+        self._call("sampling", "q3_sample", "sample", _ptr(logits), R, V, _ptr(temperature), _ptr(uniform),
+                   _ptr(token), _ptr(logprob), _ptr(scratch), _ptr(tickets), slices)
         return token, logprob
 
 

@@ -698,13 +698,22 @@ def test_argmax_lowest_index_on_ties(ops, V, R):
     assert ops._argmax_tickets is None or not bool(ops._argmax_tickets.any())
 
 
-@pytest.mark.parametrize("V,R", [(151936, 4), (301, 16), (4099, 3)])
+@pytest.mark.parametrize("V,R", [(151936, 4), (301, 16), (4099, 3), (151936, 8), (151937, 1), (40000, 33), (8192, 70),
+                                 (151936, 200)])
 def test_sample_inverse_cdf(ops, V, R):
+    """One block per row, or (few long rows) slices whose last block finds the slice to scan."""
     g = torch.Generator().manual_seed(61)
     logits = rand((R, V), torch.float32, 62, scale=3.0)
+    lowest = torch.finfo(torch.float32).min
+    logits[0, : V // 2] = lowest  # what the filters leave behind: whole slices without mass
+    if R > 1:
+        logits[1, V // 3:] = float("-inf")
     temp = (0.5 + torch.rand(R, generator=g)).cuda()
-    for trial in range(4):
+    for trial in range(5):
         u = torch.rand(R, generator=g).cuda()
+        if trial == 4:
+            u[0] = 0.0
+            u[-1] = 0.99999994  # the largest float below one
         tok, lp = ops.sample(logits, temp, u, want_logprob=True)
         probs = torch.softmax(logits.double() / temp.double()[:, None], -1)
         cdf = probs.cumsum(-1)
@@ -715,7 +724,7 @@ def test_sample_inverse_cdf(ops, V, R):
             assert abs(float(lp[r]) - math.log(float(probs[r, t]))) < 1e-3
     # u = 0 picks the first token with any probability; u just below 1 the last one
     tok, _ = ops.sample(logits, temp, torch.zeros(R).cuda())
-    assert tok.tolist() == [0] * R
+    assert tok.tolist() == [V // 2] + [0] * (R - 1)  # row 0 has no mass in its first half
     peaked = torch.full((1, V), -1e4).cuda()
     peaked[0, V - 2] = 0.0
     tok, _ = ops.sample(peaked, torch.ones(1).cuda(), torch.tensor([0.9999]).cuda())
