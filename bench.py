@@ -12,7 +12,9 @@ step: every live request gets one new token.  It prints ONE JSON line:
                 exactly K step-function calls (metadata copy, all kernels, logits);
 * ``e2e``       the same through the public engine API (``Engine.step``): scheduling, the
                 pinned host->device copy of the step's inputs, the kernels, sampling and
-                the device->host read of the new token ids;
+                the device->host read of the new token ids (the engine runs ahead: a step's
+                ids are read while the next step, fed from the device, already runs; every
+                step's inputs are still copied in and every step's ids still read out);
 * ``prefill``   one 2,048-token prompt through the step function;
 * ``roofline``  bytes a decode step has to read (every weight once + the live requests'
                 keys and values) / its time, against the measured copy bandwidth;
@@ -255,7 +257,8 @@ def run_ours(args) -> dict:
             "layers": cfg.num_hidden_layers, "layers_full": layers_full, "hidden": H, "q_heads": cfg.num_attention_heads,
             "kv_heads": cfg.num_key_value_heads, "head_dim": D, "intermediate": I, "vocab": V,
             "tied_head": cfg.tie_word_embeddings, "page_size": PAGE, "cuda_graph": True,
-            "l2": "inputs (8 GB of weights) larger than L2", "build_s": round(build_s, 1),
+            "l2": "inputs (8 GB of weights) larger than L2", "run_ahead": bool(engine.config.run_ahead),
+            "build_s": round(build_s, 1),
         },
         "e2e": e2e, "prefill": prefill, "roofline": roofline, "points": points,
         "gpu_launches": gpu_launches, "clocks": clocks.summary(),

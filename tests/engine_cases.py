@@ -263,7 +263,16 @@ def case_run_ahead(tmp_path, name, dtype, ops, device, *, cuda_graph=False):
         return out
 
     assert squeeze(True) == squeeze(False)
-    # (5) an engine that is left with a step in flight (everybody stopped) starts afresh
+    # (5) long enough to cross many pages and to outgrow a captured block-table width
+    def long_run(run_ahead):
+        eng = engine(run_ahead)
+        out = eng.generate_batch(prompts[:2], max_tokens=150)
+        assert eng.cache.num_free_pages == eng.cache.num_pages
+        return out, eng.num_run_ahead
+
+    (long_ahead, n_ahead), (long_plain, _) = long_run(True), long_run(False)
+    assert long_ahead == long_plain and n_ahead >= 140
+    # (6) an engine that is left with a step in flight (everybody stopped) starts afresh
     eng = engine(True)
     first = eng.generate(prompts[0], max_tokens=6, ignore_eos=False, stop_token_ids=(want[1][0][2],))
     again = eng.generate(prompts[2], max_tokens=6)
