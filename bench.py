@@ -321,6 +321,7 @@ def e2e_ours(engine, args, rand_ids, torch) -> dict:
     for _ in range(W):
         engine.step()
     torch.cuda.synchronize()
+    ahead_before = engine.num_run_ahead
     t0 = time.perf_counter()
     produced = 0
     for _ in range(K):
@@ -334,7 +335,8 @@ def e2e_ours(engine, args, rand_ids, torch) -> dict:
     width = 1 << ((args.context + W + K + 8) // PAGE).bit_length()
     h2d = 4 * (4 * BATCH + (BATCH + 1) + 2 * BATCH + BATCH * width)
     return dict(value=round(produced / dt, 1), unit="tokens/s", ms_per_step=round(dt * 1000.0 / K, 4),
-                h2d_bytes_per_step=h2d, d2h_bytes_per_step=4 * BATCH, steps=K)
+                h2d_bytes_per_step=h2d, d2h_bytes_per_step=4 * BATCH, steps=K,
+                steps_run_ahead=engine.num_run_ahead - ahead_before)
 
 
 # ------------------------------------------------------------------------------------------
