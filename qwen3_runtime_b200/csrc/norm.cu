@@ -57,7 +57,9 @@ __global__ void fused_norm_kernel(const void* __restrict__ pending, int parts, l
 // The same with 16-byte accesses: H a multiple of 8 and every row 16-byte aligned.
 // REGS: the block has a thread for every 8 elements of a row, so a thread's 8 values stay in
 // registers between the two passes (no staging through shared memory).
-template <typename T, bool REGS>
+// PLANES: what is pending may be partial-sum planes (a variant of its own, so that the common one
+// keeps its registers).
+template <typename T, bool REGS, bool PLANES>
 __global__ void __launch_bounds__(512) fused_norm_vec_kernel(const void* __restrict__ pending, int parts, long part_stride,
                                       float* __restrict__ resid, const int* __restrict__ ids,
                                       const T* __restrict__ table, const int* __restrict__ rows,
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(512) fused_norm_vec_kernel(const void* __restr
     trow = table + (long)id * H;
   }
   const T* prow = pending && !parts ? static_cast<const T*>(pending) + src * H : nullptr;
-  const float* frow = pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
+  const float* frow = PLANES && pending && parts ? static_cast<const float*>(pending) + src * H : nullptr;
   float* rrow = resid ? resid + src * H : nullptr;
   float ss = 0.f;
   float mine[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(512) fused_norm_vec_kernel(const void* __restr
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += pv[e];
     }
-    if (frow) {  // four planes' loads in flight at a time; added in plane order
+    if (PLANES && frow) {  // four planes' loads in flight at a time; added in plane order
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int p0 = 0; p0 < parts; p0 += 4) {
         float pv[4][8];
@@ -148,18 +150,20 @@ static int launch_fused_norm(const void* pending, int parts, long part_stride, f
   const bool vec = H % 8 == 0 && part_stride % 4 == 0 && aligned16(pending) && aligned16(resid) &&
                    aligned16(table) && aligned16(w) && aligned16(out);
   if (vec) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(fused_norm_vec_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int threads = ((H / 8 + 31) / 32) * 32;
     threads = threads > 512 ? 512 : threads;
-    if (threads * 8 >= H)  // one chunk per thread: the values stay in registers
-      return launch_pdl(fused_norm_vec_kernel<T, true>, dim3(num_rows), dim3(threads), 33 * sizeof(float), stream,
-                        pending, parts, part_stride, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid,
-                        vocab) == cudaSuccess
-                 ? Q3_OK
-                 : Q3_ERR_LAUNCH;
-    return launch_pdl(fused_norm_vec_kernel<T, false>, dim3(num_rows), dim3(threads), smem, stream, pending, parts,
-                      part_stride, resid, ids, (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+    const bool regs = threads * 8 >= H;  // one chunk per thread: the values stay in registers
+    const size_t vec_smem = regs ? 33 * sizeof(float) : smem;
+    void (*kernel)(const void*, int, long, float*, const int*, const T*, const int*, const float*, T*, int, float, int,
+                   int);
+    if (parts)
+      kernel = regs ? fused_norm_vec_kernel<T, true, true> : fused_norm_vec_kernel<T, false, true>;
+    else
+      kernel = regs ? fused_norm_vec_kernel<T, true, false> : fused_norm_vec_kernel<T, false, false>;
+    if (vec_smem > 48 * 1024)
+      cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vec_smem);
+    return launch_pdl(kernel, dim3(num_rows), dim3(threads), vec_smem, stream, pending, parts, part_stride, resid, ids,
+                      (const T*)table, rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
                ? Q3_OK
                : Q3_ERR_LAUNCH;
   }
