@@ -520,21 +520,89 @@ struct ClusterReducer {
   __device__ __forceinline__ float max(float part) { return finish(block_max(part, red), true); }
 };
 
+// Sums of WAYS - 1 values at once over the cluster: warps by shuffles, the block's warps in warp
+// order, the cluster's blocks in rank order; every thread of every block gets the same bits.
+constexpr int FILTER_WAYS = 16;
+
+struct ClusterVectorSum {
+  float (*warp_part)[FILTER_WAYS];   // [warps][ways] block scratch
+  float (*slots)[FILTER_WAYS];       // [2][ways] this block's sums, by turn
+  float* total;                      // [ways]
+  unsigned turn;
+  __device__ __forceinline__ void run(float (&part)[FILTER_WAYS - 1]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < FILTER_WAYS - 1; ++j) {
+      float v = warp_sum(part[j]);
+      if (lane == 0) warp_part[warp][j] = v;
+    }
+    __syncthreads();
+    float* slot = slots[turn & 1];
+    if (threadIdx.x < FILTER_WAYS - 1) {
+      float v = 0.f;
+      for (int w = 0; w < FILTER_THREADS / 32; ++w) v += warp_part[w][threadIdx.x];
+      slot[threadIdx.x] = v;
+    }
+    cluster_sync_all();
+    if (threadIdx.x < FILTER_WAYS - 1) {
+      float v = 0.f;
+      for (int r = 0; r < FILTER_CLUSTER; ++r) {
+        float got;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                     : "=f"(got)
+                     : "r"(map_to_cta(smem_addr(slot + threadIdx.x), r))
+                     : "memory");
+        v += got;
+      }
+      total[threadIdx.x] = v;
+    }
+    __syncthreads();
+    ++turn;
+  }
+};
+
 // smallest key k with measure({element : key(x) > k}) <= limit; the measure is the number of
 // elements (count_mode) or the sum of exp(x - mx) / z.  Elements past the end of the row count
-// for nothing.
+// for nothing.  A search that cuts the interval of keys into 16 at every step (15 thresholds,
+// 15 sums at once), so 8 steps and 8 sums over the cluster instead of 32.
 template <int ITEMS>
 __device__ unsigned cutoff_key_regs(const float (&x)[ITEMS], int first, int V, bool count_mode, float limit, float mx,
-                                    float z, ClusterReducer& cr) {
+                                    float z, ClusterVectorSum& cs) {
   constexpr int STEP = FILTER_CLUSTER * FILTER_THREADS;
+  constexpr int T = FILTER_WAYS - 1;
   unsigned lo = 0u, hi = 0xffffffffu;
+  float above = 0.f;  // the measure of {key > hi}: known from the step that set hi
   while (lo < hi) {
-    const unsigned mid = lo + ((hi - lo) >> 1);
-    float part = 0.f;
+    const unsigned long long span = (unsigned long long)hi - lo;
+    unsigned cut[T];  // non-decreasing, in [lo, hi)
 #pragma unroll
-    for (int k = 0; k < ITEMS; ++k)
-      if (first + k * STEP < V && ordered_key(x[k]) > mid) part += count_mode ? 1.f : expf(x[k] - mx) / z;
-    if (cr.sum(part) <= limit) hi = mid; else lo = mid + 1;
+    for (int j = 0; j < T; ++j) cut[j] = lo + (unsigned)((span * (j + 1)) / FILTER_WAYS);
+    float part[T];
+#pragma unroll
+    for (int j = 0; j < T; ++j) part[j] = 0.f;
+    // only keys in (lo, hi] can tell two thresholds apart; after the first steps that is almost
+    // none of the row, and a warp skips an element that none of its lanes has in that interval
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const unsigned key = ordered_key(x[k]);
+      if (first + k * STEP < V && key > lo && key <= hi) {
+        const float wgt = count_mode ? 1.f : expf(x[k] - mx) / z;
+#pragma unroll
+        for (int j = 0; j < T; ++j)
+          if (key > cut[j]) part[j] += wgt;
+      }
+    }
+    cs.run(part);
+    // the first threshold whose measure is within the limit bounds the answer from above, the
+    // one before it from below
+    int j = 0;
+    while (j < T && !(above + cs.total[j] <= limit)) ++j;
+    const unsigned new_hi = j < T ? cut[j] : hi;
+    const unsigned new_lo = j > 0 ? cut[j - 1] + 1 : lo;
+    if (j < T) above += cs.total[j];
+    hi = new_hi;
+    lo = new_lo;
+    __syncthreads();  // everybody has read the sums before the next step overwrites them
   }
   return lo;
 }
@@ -546,7 +614,11 @@ filter_cluster_kernel(float* __restrict__ logits, int V, const float* __restrict
                       const float* __restrict__ top_p) {
   __shared__ float red[33];
   __shared__ float slots[2];
+  __shared__ float warp_part[FILTER_THREADS / 32][FILTER_WAYS];
+  __shared__ float vector_slots[2][FILTER_WAYS];
+  __shared__ float vector_total[FILTER_WAYS];
   ClusterReducer cr{red, slots, 0u};
+  ClusterVectorSum cs{warp_part, vector_slots, vector_total, 0u};
   const int r = blockIdx.y;
   float* row = logits + (long)r * V;
   const float temp = temperature[r];
@@ -573,7 +645,7 @@ filter_cluster_kernel(float* __restrict__ logits, int V, const float* __restrict
       if (expf(x[k] - mx) < mp) x[k] = -INFINITY;
   }
   if (tk > 0 && tk < V) {  // keep the k largest, ties with the k-th included (sampling.py:96-99)
-    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, true, (float)(tk - 1), 0.f, 1.f, cr);
+    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, true, (float)(tk - 1), 0.f, 1.f, cs);
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k)
       if (ordered_key(x[k]) < cut) x[k] = lowest;
@@ -588,7 +660,7 @@ filter_cluster_kernel(float* __restrict__ logits, int V, const float* __restrict
     for (int k = 0; k < ITEMS; ++k)
       if (first + k * STEP < V) s += expf(x[k] - mx);
     const float z = cr.sum(s);
-    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, false, tp, mx, z, cr);
+    const unsigned cut = cutoff_key_regs<ITEMS>(x, first, V, false, tp, mx, z, cs);
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k)
       if (ordered_key(x[k]) < cut) x[k] = lowest;
