@@ -698,10 +698,16 @@ Q3_EXPORT int q3_filter(float* logits, int num_rows, int V, const float* tempera
   // rows that fit the registers of a cluster of 8 blocks (up to 163,840 elements) and are long
   // enough to be worth it; the others take one block per row and passes over memory
   constexpr int PER_ITEM = FILTER_CLUSTER * FILTER_THREADS;
-  if (V > 4096 && num_rows <= 65535) {
-    if (V <= 8 * PER_ITEM) return launch_filter_cluster<8>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
-    if (V <= 20 * PER_ITEM) return launch_filter_cluster<20>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
-    if (V <= 40 * PER_ITEM) return launch_filter_cluster<40>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+  if (V > 4096 && num_rows <= 65535 && V <= 40 * PER_ITEM) {
+    int status;
+    if (V <= 8 * PER_ITEM)
+      status = launch_filter_cluster<8>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+    else if (V <= 20 * PER_ITEM)
+      status = launch_filter_cluster<20>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+    else
+      status = launch_filter_cluster<40>(logits, num_rows, V, temperature, min_p, top_k, top_p, stream);
+    if (status == Q3_OK) return Q3_OK;
+    // a device that cannot place such a cluster refuses the launch (nothing ran): one block per row
   }
   filter_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, min_p, top_k, top_p);
   return q3_launch_status();
