@@ -65,8 +65,7 @@ class PagedAttention(Part):
     def kernel_groups(self):
         groups = ["rope_kv", "attention_generic", *self.position.kernel_groups()]
         if self.ctx.dtype == torch.bfloat16:
-            groups += ["attention_decode", "attention_prefill", "attention_prefill_tc", "gemm_small_m", "gemm_stream",
-                       "gemm_skinny"]
+            groups += ["attention_decode", "attention_prefill", "attention_prefill_tc", "gemm_small_m", "gemm_stream"]
         if self.ctx.dtype == torch.float32:
             groups.append("gemm_f32")
         return groups

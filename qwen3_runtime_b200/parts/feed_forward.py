@@ -35,7 +35,7 @@ class GatedMLP(Part):
     def kernel_groups(self):
         if self.ctx.dtype == torch.float32:
             return ["norm", "gemm_f32"]
-        return ["norm", "gemm_small_m", "gemm_stream", "gemm_skinny", "gemm_tcgen05"]
+        return ["norm", "gemm_small_m", "gemm_stream", "gemm_tcgen05"]
 
     def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
         mid = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
