@@ -383,7 +383,8 @@ class CudaOps:
         bfloat16, at most 16 tokens: one of this engine's two weight-streaming kernels
         (:meth:`_small_product`).  bfloat16, more tokens: the library product with fp32
         accumulation, as the reference's ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77,
-        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"``.
+        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"`` (17..64 tokens
+        with ``skinny_gemm``: the swapped-operand tcgen05 kernel of csrc/gemm_skinny.cu).
 
         ``partial_sums``: the caller also takes float32 ``[parts, M, N]`` whose sum over the
         first axis is the product (what :meth:`fused_norm` accepts as ``pending``).  It gets
