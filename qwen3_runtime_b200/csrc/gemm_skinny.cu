@@ -10,8 +10,11 @@
 // x one range of K; K is cut into as many ranges as it takes to give every SM an item, and an
 // item with a range of its own writes an fp32 plane out[range][token][feature] -- the sum over
 // the ranges is the product, added up by the norm kernel (csrc/norm.cu) or by
-// q3_sum_planes below.  One block per SM, persistent over its items, 8 stages of 24 KB in
-// flight.  Roles as in gemm_tcgen05.cu: warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the
+// q3_sum_planes below.  One block per SM, persistent over its items.  A stage of the ring holds
+// three k-blocks (three weight boxes of 16 KB and three token boxes of 8 KB) behind one barrier,
+// three stages: a round trip over a stage's barriers costs about 0.7 us here whatever the stage
+// holds, so with one k-block per stage the kernel ran at 3.3 TB/s, with three at 5.0.
+// Roles as in gemm_tcgen05.cu: warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the
 // MMAs (and owns the tensor memory), warps 2..5 read the accumulator (each its 32 lanes =
 // 32 features) and store, one token at a time, 32 consecutive features per warp.
 //
@@ -25,11 +28,13 @@ enum { SK_BF16 = 0, SK_F32 = 1, SK_PLANES = 2 };
 constexpr int SK_BM = 128;     // features per tile
 constexpr int SK_NT = 64;      // token columns of the MMA
 constexpr int SK_BK = 64;
-constexpr int SK_STAGES = 8;
+constexpr int SK_KSUB = 3;      // k-blocks per stage (per barrier round trip)
+constexpr int SK_STAGES = 3;
 constexpr int SK_THREADS = 192;
 constexpr int SK_A_BYTES = SK_BM * SK_BK * 2;
 constexpr int SK_B_BYTES = SK_NT * SK_BK * 2;
-constexpr int SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES;
+constexpr int SK_SUB_BYTES = SK_A_BYTES + SK_B_BYTES;
+constexpr int SK_STAGE_BYTES = SK_KSUB * SK_SUB_BYTES;
 
 template <int MODE>
 __global__ void __launch_bounds__(SK_THREADS, 1)
@@ -82,42 +87,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer -------------------------------------------------------
-      // the g-th k-block of this block's items: which features, which k.  All blocks need the same
-      // token boxes; were they to walk K in step, every SM would ask the same few L2 lines for
-      // them at the same moment, so item i starts at its range's k-block i mod n and wraps around
-      // (the order of additions of a feature depends on its tile only, never on the tokens).
-      auto locate = [&](int g, int& f0, int& kb) -> bool {
+      // the g-th stage of this block's items: which features, which k-blocks (SK_KSUB of them, fewer
+      // at the end of a range)
+      auto locate = [&](int g, int& f0, int& kb, int& cnt) -> bool {
         int base = 0;
         for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
           const int lo = (item / tiles_f) * kb_per_range, n = min(num_kb, lo + kb_per_range) - lo;
-          if (g < base + n) {
+          const int stages_n = (n + SK_KSUB - 1) / SK_KSUB;
+          if (g < base + stages_n) {
             f0 = (item % tiles_f) * SK_BM;
-            kb = lo + (g - base + item) % n;  // each item starts its range somewhere else (see above)
+            kb = lo + (g - base) * SK_KSUB;
+            cnt = min(SK_KSUB, lo + n - kb);
             return true;
           }
-          base += n;
+          base += stages_n;
         }
         return false;
       };
       // The weights do not depend on the kernel before this one: the ring is filled with weight
       // boxes before the wait for it, the token boxes of those stages follow.
-      int f0 = 0, kb = 0, early = 0;
-      for (; early < SK_STAGES && locate(early, f0, kb); ++early) {
-        mbar_expect_tx(full0 + 8 * early, SK_STAGE_BYTES);
-        tma_load_2d(smem_addr(tiles + (size_t)early * SK_STAGE_BYTES), &tmap_w, full0 + 8 * early, kb * SK_BK, f0);
+      int f0 = 0, kb = 0, cnt = 0, early = 0;
+      for (; early < SK_STAGES && locate(early, f0, kb, cnt); ++early) {
+        mbar_expect_tx(full0 + 8 * early, cnt * SK_SUB_BYTES);
+        for (int j = 0; j < cnt; ++j)
+          tma_load_2d(smem_addr(tiles + (size_t)early * SK_STAGE_BYTES + j * SK_SUB_BYTES), &tmap_w, full0 + 8 * early,
+                      (kb + j) * SK_BK, f0);
       }
       pdl_wait();
       for (int g = 0; g < early; ++g) {
-        locate(g, f0, kb);
-        tma_load_2d(smem_addr(tiles + (size_t)g * SK_STAGE_BYTES) + SK_A_BYTES, &tmap_x, full0 + 8 * g, kb * SK_BK, 0);
+        locate(g, f0, kb, cnt);
+        for (int j = 0; j < cnt; ++j)
+          tma_load_2d(smem_addr(tiles + (size_t)g * SK_STAGE_BYTES + j * SK_SUB_BYTES) + SK_A_BYTES, &tmap_x,
+                      full0 + 8 * g, (kb + j) * SK_BK, 0);
       }
-      for (int g = early; locate(g, f0, kb); ++g) {
+      for (int g = early; locate(g, f0, kb, cnt); ++g) {
         const int s = g % SK_STAGES;
         if (!mbar_wait(empty0 + 8 * s, ((g / SK_STAGES) & 1) ^ 1, &abort_flag)) break;
-        const uint32_t a_dst = smem_addr(tiles + (size_t)s * SK_STAGE_BYTES);
-        mbar_expect_tx(full0 + 8 * s, SK_STAGE_BYTES);
-        tma_load_2d(a_dst, &tmap_w, full0 + 8 * s, kb * SK_BK, f0);
-        tma_load_2d(a_dst + SK_A_BYTES, &tmap_x, full0 + 8 * s, kb * SK_BK, 0);
+        mbar_expect_tx(full0 + 8 * s, cnt * SK_SUB_BYTES);
+        for (int j = 0; j < cnt; ++j) {
+          const uint32_t a_dst = smem_addr(tiles + (size_t)s * SK_STAGE_BYTES + j * SK_SUB_BYTES);
+          tma_load_2d(a_dst, &tmap_w, full0 + 8 * s, (kb + j) * SK_BK, f0);
+          tma_load_2d(a_dst + SK_A_BYTES, &tmap_x, full0 + 8 * s, (kb + j) * SK_BK, 0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -133,17 +144,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem_base + buf * ACC_COLS;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++g) {  // (the producer's order of k-blocks; only their number matters here)
+        for (int kb = kb_lo; kb < kb_hi; kb += SK_KSUB, ++g) {
           const int s = g % SK_STAGES;
           ok = mbar_wait(full0 + 8 * s, (g / SK_STAGES) & 1, &abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_addr(tiles + (size_t)s * SK_STAGE_BYTES);
-          const uint64_t a_desc = umma_desc(a_addr);
-          const uint64_t b_desc = umma_desc(a_addr + SK_A_BYTES);
+          const int cnt = min(SK_KSUB, kb_hi - kb);
+          for (int j = 0; j < cnt; ++j) {
+            const uint32_t a_addr = smem_addr(tiles + (size_t)s * SK_STAGE_BYTES + j * SK_SUB_BYTES);
+            const uint64_t a_desc = umma_desc(a_addr);
+            const uint64_t b_desc = umma_desc(a_addr + SK_A_BYTES);
 #pragma unroll
-          for (int k = 0; k < SK_BK / 16; ++k)
-            umma_bf16(acc + k * SK_NT, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > kb_lo ? 1u : 0u);
+            for (int k = 0; k < SK_BK / 16; ++k)
+              umma_bf16(acc + k * SK_NT, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb_lo || j > 0) ? 1u : 0u);
+          }
           umma_commit(empty0 + 8 * s);
         }
         if (ok) umma_commit(acc_full0 + 8 * buf);
