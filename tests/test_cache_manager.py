@@ -27,6 +27,23 @@ def test_span_allocation_grows_tables_in_place():
     m.check_invariants()
 
 
+def test_new_pages_needed_says_what_reserve_will_take():
+    """What the engine asks before it runs ahead: the pages a span would take from each pool."""
+    m = CacheManager([GroupSpec("full"), GroupSpec("window", window=6)], page_size=4, num_pages=[8, 8], num_slots=2)
+    a = m.open("a")
+    assert m.new_pages_needed(a, 1) == [1, 1] and m.new_pages_needed(a, 9) == [3, 3]
+    for _ in range(14):
+        need = m.new_pages_needed(a, 1)
+        free = m.num_free_pages
+        m.reserve(a, 1)
+        after = m.num_free_pages
+        assert [f - g for f, g in zip(free, after)] == need, "exactly what reserve took"
+        m.commit(a, 1)  # a window gives pages back here, never in reserve
+    assert m.new_pages_needed(a, 0) == [0, 0]
+    m.close(a)
+    m.check_invariants()
+
+
 def test_fifo_reuse_and_capacity_queries():
     m = CacheManager([GroupSpec("full")], page_size=4, num_pages=4, num_slots=4)
     a, b = m.open("a"), m.open("b")
