@@ -13,7 +13,8 @@ was already running for it is simply not read for that request (its pages were r
 it finished; work queued later on the same stream comes after the abandoned writes).  Nothing
 runs ahead when the batch is about to change: a request waits for admission, one reaches its
 ``max_tokens``, pages may run out, or a request's sampling needs the token history on the
-host (penalties).  The tokens are the same with and without running ahead.
+host (penalties).  Every request gets the same tokens with and without running ahead; a request
+that is added while a step is already running ahead joins one step later than it would otherwise.
 """
 
 from __future__ import annotations

@@ -277,3 +277,63 @@ def case_run_ahead(tmp_path, name, dtype, ops, device, *, cuda_graph=False):
     first = eng.generate(prompts[0], max_tokens=6, ignore_eos=False, stop_token_ids=(want[1][0][2],))
     again = eng.generate(prompts[2], max_tokens=6)
     assert first == want[1][0][:len(first)] and first[-1] == want[1][0][2] and again == want[1][2][:6], (first, again, want[1])
+
+
+def case_run_ahead_random(tmp_path, name, dtype, ops, device, seed, *, cuda_graph=False):
+    """Random arrivals, lengths, stop tokens, samplers and aborts: the engine that runs ahead gives
+    every request the tokens and the end that the engine that does not gives it, and every page
+    back.  The steps themselves may differ: a request that arrives while a step is already running
+    ahead joins one step later (so an abort at a fixed step cuts it one token earlier)."""
+    import random as _random
+
+    from qwen3_runtime_b200 import SamplingParams
+
+    folder = make_model_dir(tmp_path, name)
+    ps = TINY[name]["page_size"]
+    vocab = TINY[name]["config"].vocab_size
+    rnd = _random.Random(seed)
+    plan = []
+    for i in range(rnd.randint(3, 6)):
+        kind = rnd.choice(["greedy", "greedy", "temperature", "top_k", "penalty"])
+        sampling = {"greedy": SamplingParams(),
+                    "temperature": SamplingParams(temperature=0.8, seed=100 + i),
+                    "top_k": SamplingParams(temperature=0.9, top_k=rnd.randint(2, 30), seed=200 + i),
+                    "penalty": SamplingParams(repetition_penalty=1.3)}[kind]
+        plan.append(dict(arrive=rnd.randint(0, 12), prompt=random_ids(vocab, rnd.randint(1, 40), 1000 * seed + i),
+                         max_tokens=rnd.randint(1, 25), sampling=sampling,
+                         stop=tuple(rnd.sample(range(vocab), rnd.randint(0, vocab // 8))) if rnd.random() < 0.5 else (),
+                         abort=rnd.randint(3, 30) if rnd.random() < 0.25 else None))
+    pages = rnd.choice([6, 12, 64])
+    budget = rnd.choice([8, 16, 64])
+    seqs = rnd.choice([2, 4])
+
+    def run(run_ahead):
+        eng = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps, num_kv_blocks=pages,
+                           max_num_seqs=seqs, max_num_batched_tokens=budget, cuda_graph=cuda_graph,
+                           run_ahead=run_ahead)
+        reqs = {}
+        for step in range(400):
+            for i, p in enumerate(plan):
+                if p["arrive"] == step and eng.cache.fits_at_all(len(p["prompt"]) + p["max_tokens"]):
+                    rid = eng.add_request(p["prompt"], max_tokens=p["max_tokens"], sampling=p["sampling"],
+                                          ignore_eos=not p["stop"], stop_token_ids=p["stop"])
+                    reqs[i] = eng.get_request(rid)
+                if p["abort"] == step and i in reqs:
+                    eng.abort_request(reqs[i].request_id)
+            if not eng.step() and step > max(p["arrive"] for p in plan):
+                break
+        assert eng.is_finished() and eng.cache.num_free_pages == eng.cache.num_pages
+        eng.cache.check_invariants()
+        return {i: (r.output_token_ids, r.finish_reason) for i, r in reqs.items()}, eng.num_run_ahead
+
+    plain, none = run(False)
+    ahead, count = run(True)
+    assert none == 0 and plain.keys() == ahead.keys()
+    for i in plain:
+        (toks_p, why_p), (toks_a, why_a) = plain[i], ahead[i]
+        if "abort" in (why_p, why_a):
+            n = min(len(toks_p), len(toks_a))
+            assert toks_p[:n] == toks_a[:n] and abs(len(toks_p) - len(toks_a)) <= 1, (seed, i, toks_p, toks_a)
+        else:
+            assert (toks_p, why_p) == (toks_a, why_a), (seed, i, plain[i], ahead[i])
+    return count

@@ -45,3 +45,8 @@ def test_without_a_gpu_the_product_path_refuses_loudly():
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_running_ahead_gives_the_same_tokens_step_by_step(tmp_path, name):
     ec.case_run_ahead(tmp_path, name, "float32", OPS, DEV)
+
+
+def test_running_ahead_under_random_arrivals_stops_and_aborts(tmp_path):
+    ran_ahead = sum(ec.case_run_ahead_random(tmp_path, "A", "float32", OPS, DEV, seed) for seed in range(12))
+    assert ran_ahead > 20, "the scenarios were meant to let the engine run ahead now and then"
