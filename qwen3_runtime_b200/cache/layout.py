@@ -86,8 +86,33 @@ class CacheLayout:
         (qwen3_runtime/engine/memory.py:8-10)."""
         return sum(self.page_bytes(1, dtype_bytes))
 
-    def pages_for_budget(self, budget_bytes: int, page_size: int, dtype_bytes: int) -> int:
-        """Pages per paged group (the same for each) that fit in ``budget_bytes``
-        (qwen3_runtime/engine/memory.py:17-27)."""
-        per = sum(self.page_bytes(page_size, dtype_bytes))
-        return 0 if per <= 0 else int(budget_bytes // per)
+    def pages_for_budget(self, budget_bytes: int, page_size: int, dtype_bytes: int, *,
+                         max_num_seqs: int | None = None, max_step_tokens: int | None = None) -> list[int]:
+        """Pages for each paged group that together fit in ``budget_bytes``
+        (qwen3_runtime/engine/memory.py:17-27 for the single group of the reference).
+
+        A group that keeps every key needs pages in proportion to the tokens held, so such
+        groups all get the same count.  A window group never holds more, per request, than
+        its window plus the portion being computed; with ``max_num_seqs`` and
+        ``max_step_tokens`` given it gets no more pages than that, and what it leaves goes to
+        the groups that keep everything."""
+        per = self.page_bytes(page_size, dtype_bytes)
+        if not per or sum(per) <= 0:
+            return [0 for _ in per]
+        equal = int(budget_bytes // sum(per))
+        counts = [equal] * len(per)
+        if max_num_seqs is None or max_step_tokens is None:
+            return counts
+        spent, open_bytes = 0, 0
+        for i, gi in enumerate(self.paged_groups):
+            window = self.groups[gi].spec.window
+            if window:
+                cap = max_num_seqs * (-(-(window + max_step_tokens) // page_size) + 2)
+                counts[i] = min(equal, cap)
+                spent += counts[i] * per[i]
+            else:
+                open_bytes += per[i]
+        if open_bytes:
+            full = int((budget_bytes - spent) // open_bytes)
+            counts = [c if self.groups[gi].spec.window else full for c, gi in zip(counts, self.paged_groups)]
+        return counts

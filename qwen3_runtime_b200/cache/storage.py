@@ -24,19 +24,26 @@ class CacheLayerView:
 
 
 class CacheStorage:
-    def __init__(self, layout: CacheLayout, page_size: int, num_pages: int, num_slots: int,
+    def __init__(self, layout: CacheLayout, page_size: int, num_pages: int | list[int], num_slots: int,
                  dtype: torch.dtype, device: torch.device | str):
+        """``num_pages``: pages of every paged group, or one count per paged group."""
         self.layout = layout
         self.page_size = page_size
-        self.num_pages = num_pages
+        if isinstance(num_pages, int):
+            num_pages = [num_pages] * len(layout.paged_groups)
+        if len(num_pages) != len(layout.paged_groups):
+            raise ValueError("one page count per paged group is required")
+        self.num_pages = list(num_pages)
         self.num_slots = num_slots
-        self.scratch_page = num_pages  # extra page that padded rows write to
+        # the extra page of each paged group, which padded rows write to
+        self.scratch_page = tuple(self.num_pages)
         self.scratch_slot = num_slots
         self.tensors: list[torch.Tensor] = []
-        for g in layout.groups:
+        for gi, g in enumerate(layout.groups):
             s = g.layer_spec
             if isinstance(s, KVLayerSpec):
-                shape = (len(g.cache_ids), 2, num_pages + 1, s.num_kv_heads, page_size, s.head_dim)
+                pages = self.num_pages[layout.paged_groups.index(gi)]
+                shape = (len(g.cache_ids), 2, pages + 1, s.num_kv_heads, page_size, s.head_dim)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
             else:
                 assert isinstance(s, StateLayerSpec)

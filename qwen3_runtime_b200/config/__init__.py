@@ -2,6 +2,8 @@ from .engine_config import EngineConfig, canonical_dtype
 from .model_config import ConfigError, Qwen3Config
 from .registry import (
     Architecture,
+    architecture_for_config,
+    default_architecture,
     load_config,
     read_config_json,
     register_architecture,
@@ -13,6 +15,8 @@ from .spec import LayerRun, ModelSpec, PartSpec
 
 __all__ = [
     "Architecture",
+    "architecture_for_config",
+    "default_architecture",
     "ConfigError",
     "EngineConfig",
     "LayerRun",

@@ -22,15 +22,39 @@ class Architecture:
     name: str
     config_class: type
     build_spec: Callable[[Any], ModelSpec]
+    # a small configuration of this architecture for the model-less mode of the Python entry
+    # point (random weights, no files); None: the architecture offers none
+    tiny_config: Callable[[], Any] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_class: type, build_spec: Callable[[Any], ModelSpec]) -> None:
+def register_architecture(name: str, config_class: type, build_spec: Callable[[Any], ModelSpec], *,
+                          tiny_config: Callable[[], Any] | None = None) -> None:
     if name in _ARCHITECTURES:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, config_class, build_spec)
+    _ARCHITECTURES[name] = Architecture(name, config_class, build_spec, tiny_config)
+
+
+def architecture_for_config(config: Any) -> Architecture:
+    """The registry entry whose typed config class ``config`` is an instance of (the first
+    registered one, if several architectures share a config class)."""
+    _ensure_builtin()
+    for arch in _ARCHITECTURES.values():
+        if type(config) is arch.config_class:
+            return arch
+    raise ConfigError(f"no registered architecture has the config class {type(config).__name__}")
+
+
+def default_architecture() -> Architecture:
+    """The architecture a model-less run uses when none is named: the first registered one
+    that offers a tiny configuration."""
+    _ensure_builtin()
+    for arch in _ARCHITECTURES.values():
+        if arch.tiny_config is not None:
+            return arch
+    raise ConfigError("no registered architecture offers a tiny configuration")
 
 
 def unregister_architecture(name: str) -> None:

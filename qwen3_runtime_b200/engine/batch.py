@@ -108,7 +108,7 @@ class BatchBuilder:
                         return False
                     if bt is None:
                         bt = sec(f"bt{g}").reshape(B, width)
-                    bt[b, :] = scratch_page
+                    bt[b, :] = scratch_page[g]
                     bt[b, :size] = e.cache.table_array(g)
                     last["table_lens"][b][g] = size
         last["starts"] = starts
@@ -128,16 +128,22 @@ class BatchBuilder:
         return True
 
     def build(self, entries: list[StepEntry], *, pad_to: int | None = None, table_width: int | None = None,
-              scratch_page: int = 0, scratch_slot: int = 0, device_buffer: torch.Tensor | None = None,
+              scratch_page: int | tuple[int, ...] = 0, scratch_slot: int = 0,
+              device_buffer: torch.Tensor | None = None,
               all_rows: bool = False, need_context: bool = True) -> StepContext | None:
         """Pack a step.  ``pad_to`` appends dummy one-token sequences (writing to the
-        scratch page) so that a decode batch fills a captured batch size; ``table_width``
+        scratch page and the scratch state slot) so that a decode batch fills a captured batch
+        size; with no entries at all the step consists of such rows only.  ``table_width``
         fixes the block-table width; ``device_buffer`` is a preallocated int32 buffer that
         the metadata is copied into (captured steps read from fixed addresses).
+        ``scratch_page``: the page that padded rows and unused block-table entries name, one id
+        for every paged group or one per group.
         ``need_context=False``: the caller only wants the device buffer filled (a replayed
         graph reads it) and gets no :class:`StepContext`."""
-        if not entries:
+        if not entries and not pad_to:
             raise BatchError("a step needs at least one entry")
+        if not isinstance(scratch_page, tuple):  # one scratch page id per paged group
+            scratch_page = (int(scratch_page),) * len(self.cache.paged_groups)
         if not need_context and device_buffer is not None and all_rows:
             if self._continue_decode(entries, pad_to, table_width, scratch_page, scratch_slot, device_buffer):
                 return None
@@ -214,7 +220,7 @@ class BatchBuilder:
                 rows.extend(first + w for w in e.want)
         for g in range(n_paged):
             bt = sec(f"bt{g}").reshape(B, width)
-            bt[:] = scratch_page
+            bt[:] = scratch_page[g]
             for b, e in enumerate(entries):
                 arr = e.cache.table_array(g)
                 bt[b, : arr.size] = arr
@@ -241,7 +247,7 @@ class BatchBuilder:
             ev.record()
             self._events[self._turn] = ev
         self._last_decode = None
-        if device_buffer is not None and all_rows and T_real == B_real:
+        if device_buffer is not None and all_rows and T_real == B_real and B_real > 0:
             windowed = [self.cache.groups[g].window is not None for g in self.cache.paged_groups]
             self._last_decode = dict(
                 caches=[e.cache for e in entries], key=(pad_to, table_width, scratch_page, scratch_slot),
@@ -261,7 +267,7 @@ class BatchBuilder:
             kv_lens=dsec("kv"), state_slots=dsec("slot"),
             block_tables=[dsec(f"bt{g}").view(B, width) for g in range(n_paged)],
             logit_rows=dsec("rows", R), num_logit_rows=R,
-            max_query_len=max(lens), max_kv_len=int(kv[:B].max()),
+            max_query_len=max(lens, default=1), max_kv_len=int(kv[:B].max()),
             decode_only=all(n == 1 for n in lens),
             single_seqs=dsec("single", len(singles)), num_single=len(singles),
             host_cu_seqlens=[int(x) for x in cu], host_kv_lens=[int(x) for x in kv[:B]],

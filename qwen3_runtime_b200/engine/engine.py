@@ -53,6 +53,21 @@ class Engine:
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, token_ids: list[int], max_tokens: int = 16, *, ignore_eos: bool = True,
                     sampling: SamplingParams | None = None, stop_token_ids: tuple[int, ...] = ()) -> int:
+        """Queue a request.  Refused here, before it can take part in a step: token ids outside
+        the vocabulary, and a prompt that leaves no room for a single new token within the
+        positions the model serves.  ``max_tokens`` is cut to the positions that are left, so
+        such a request ends with ``length`` at the limit instead of failing in a later step."""
+        builder = getattr(self.runner, "builder", None)
+        if builder is not None:
+            vocab, limit = builder.vocab_size, builder.max_positions
+            bad = next((int(t) for t in token_ids if not 0 <= int(t) < vocab), None)
+            if bad is not None:
+                raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
+            # the last sampled token is never fed back, so prompt + max_tokens - 1 positions are used
+            if len(token_ids) > limit:
+                raise ValueError(f"a prompt of {len(token_ids)} tokens leaves no room for a new token: the "
+                                 f"model's position encoding covers {limit} positions")
+            max_tokens = min(max_tokens, limit - len(token_ids) + 1)
         req = Request(token_ids, max_tokens=max_tokens, ignore_eos=ignore_eos, sampling=sampling,
                       stop_token_ids=stop_token_ids)
         self.scheduler.add(req)
@@ -85,9 +100,18 @@ class Engine:
                 return []
             launched = self._launch(reqs, preempt_before)
         self.last_step_stats = launched.stats
+        failure = None
         if self.config.run_ahead and self._may_run_ahead(launched):
-            self._ahead = self._launch_next_decode(launched)
-        return self._read(launched)
+            try:
+                self._ahead = self._launch_next_decode(launched)
+            except Exception as exc:  # noqa: BLE001 - re-raised below, after this step was read
+                # the step that is on the device is still read, so that its tokens are not lost
+                # and every request's counters stay consistent with its cache
+                self._ahead, failure = None, exc
+        out = self._read(launched)
+        if failure is not None:
+            raise failure
+        return out
 
     def _launch(self, reqs: list[Request], preempt_before: int) -> _Launched:
         entries, sampling = [], []

@@ -13,7 +13,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.engine_config import EngineConfig, canonical_dtype
-from ..config.registry import load_config, read_config_json, resolve_architecture
+from ..config.registry import architecture_for_config, load_config, read_config_json
 from ..parts.base import BuildContext
 from ..parts.model import DecoderModel
 from ..sampling.sampler import Sampler
@@ -32,7 +32,7 @@ def default_ops(groups=None):
 
 def build_model(config, source, *, dtype: str = "bfloat16", device="cuda", ops=None) -> DecoderModel:
     """A loaded :class:`DecoderModel` for a typed config and a tensor source."""
-    arch = resolve_architecture({"architectures": [config.architecture]})
+    arch = architecture_for_config(config)
     ops = ops if ops is not None else default_ops()
     ctx = BuildContext(dtype=_TORCH_DTYPE[canonical_dtype(dtype)], device=torch.device(device), ops=ops)
     model = DecoderModel(arch.build_spec(config), ctx)
@@ -63,9 +63,19 @@ class Runtime:
     max_positions: int
 
 
-def build_runtime(model: DecoderModel, *, max_positions: int, block_size: int, num_kv_blocks: int | None,
-                  max_num_seqs: int, cuda_graph: bool = False, kv_budget: int | None = None,
-                  kv_memory_fraction: float = 0.85) -> Runtime:
+UNLIMITED_POSITIONS = 1 << 30  # a model none of whose parts limits the positions
+
+
+def build_runtime(model: DecoderModel, *, max_positions: int | None = None, block_size: int,
+                  num_kv_blocks: int | list[int] | None, max_num_seqs: int, cuda_graph: bool = False,
+                  kv_budget: int | None = None, kv_memory_fraction: float = 0.85,
+                  max_num_batched_tokens: int | None = None) -> Runtime:
+    """Cache and step function for a loaded model.  ``max_positions`` defaults to what the
+    model's own parts can serve (the shortest position table among them).  ``num_kv_blocks``:
+    pages of every paged group, one count per paged group, or None to size the pools from
+    ``kv_budget`` bytes (default: ``kv_memory_fraction`` of the free device memory)."""
+    if max_positions is None:
+        max_positions = model.position_limit() or UNLIMITED_POSITIONS
     layout = model.cache_layout()
     ctx = model.ctx
     dtype_bytes = torch.empty((), dtype=ctx.dtype).element_size()
@@ -78,7 +88,9 @@ def build_runtime(model: DecoderModel, *, max_positions: int, block_size: int, n
                 kv_budget = int(free * kv_memory_fraction)
         elif kv_budget <= 0:
             raise ValueError(f"kv_budget must be positive, got {kv_budget!r}")
-        num_kv_blocks = max(32, layout.pages_for_budget(kv_budget, block_size, dtype_bytes))
+        counts = layout.pages_for_budget(kv_budget, block_size, dtype_bytes, max_num_seqs=max_num_seqs,
+                                         max_step_tokens=max_num_batched_tokens)
+        num_kv_blocks = [max(32, n) for n in counts]
     cache = CacheManager(layout.group_specs, block_size, num_kv_blocks, max_num_seqs)
     storage = CacheStorage(layout, block_size, num_kv_blocks, max_num_seqs, ctx.dtype, ctx.device)
     runner = ModelRunner(model, cache, storage, max_positions=max_positions, cuda_graph=cuda_graph)
@@ -98,25 +110,26 @@ def build_engine(model_dir: str | Path | None = None, *, max_num_seqs: int = 8, 
                  kv_budget: int | None = None, cuda_graph: bool | None = None, eos_token_id: int | None = None,
                  device="cuda", ops=None, model: DecoderModel | None = None, config=None,
                  max_positions: int | None = None, pin_path: str | Path | None = None,
-                 run_ahead: bool = True) -> Engine:
-    """An :class:`Engine` for a model folder (or an already built ``model`` with its ``config``)."""
+                 run_ahead: bool = True, kv_memory_fraction: float = 0.85) -> Engine:
+    """An :class:`Engine` for a model folder (or an already built ``model``; its ``config`` is
+    kept on the engine for the caller's reference only)."""
     dtype = canonical_dtype(dtype)
     raw: dict = {}
     if model is None:
         if model_dir is None:
             raise ValueError("give a model folder or a built model")
         model, config, raw = load_model(model_dir, dtype=dtype, device=device, ops=ops, pin_path=pin_path)
-    if max_positions is None:
-        max_positions = int(getattr(config, "max_position_embeddings"))
     if cuda_graph is None:
         cuda_graph = model.ctx.device.type == "cuda"
     if eos_token_id is None:
         eos_token_id = eos_from_config(raw)
     rt = build_runtime(model, max_positions=max_positions, block_size=block_size, num_kv_blocks=num_kv_blocks,
-                       max_num_seqs=max_num_seqs, cuda_graph=cuda_graph, kv_budget=kv_budget)
-    cfg = EngineConfig(block_size=block_size, num_kv_blocks=rt.cache.num_pages[0] if rt.cache.num_pages else 0,
+                       max_num_seqs=max_num_seqs, cuda_graph=cuda_graph, kv_budget=kv_budget,
+                       kv_memory_fraction=kv_memory_fraction, max_num_batched_tokens=max_num_batched_tokens)
+    cfg = EngineConfig(block_size=block_size, num_kv_blocks=min(rt.cache.num_pages) if rt.cache.num_pages else None,
                        max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
-                       eos_token_id=eos_token_id, cuda_graph=bool(cuda_graph), dtype=dtype, run_ahead=bool(run_ahead))
+                       eos_token_id=eos_token_id, cuda_graph=bool(cuda_graph), dtype=dtype, run_ahead=bool(run_ahead),
+                       kv_memory_fraction=kv_memory_fraction)
     engine = Engine(cfg, rt.runner, rt.cache, Sampler(model.ops, model.ctx.device))
     engine.runtime = rt
     engine.model_config = config

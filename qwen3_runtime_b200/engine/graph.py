@@ -56,7 +56,7 @@ class DecodeGraphs:
         key = (bucket, width)
         cap = self.captured.get(key)
         if cap is None:
-            cap = self._capture(key, entries)
+            cap = self._capture(key)
         self._fill(cap, entries, bucket, width, need_context=False)
         if device_tokens is not None:  # ids that only the device knows, over the placeholders
             self.runner.builder.last_token_ids.copy_(device_tokens)
@@ -75,14 +75,19 @@ class DecodeGraphs:
                                scratch_slot=r.storage.scratch_slot, device_buffer=cap.meta, all_rows=True,
                                need_context=need_context)
 
-    def _capture(self, key, entries) -> _Captured:
+    def _capture(self, key) -> _Captured:
+        """Warm up and capture a step made of padding rows only: every row reads and writes the
+        scratch page and the scratch state slot, so neither the warm-up run nor the capture
+        touches a live request's keys, values or state (a state layer advanced by the warm-up
+        and again by the first replay would count that token twice).  The real step's metadata
+        is copied into ``meta`` afterwards, by :meth:`try_run`, and only then replayed."""
         bucket, width = key
         r = self.runner
         n_paged = len(r.cache.paged_groups)
         meta = torch.zeros(8 * bucket + 64 + n_paged * bucket * width, dtype=torch.int32, device=r.device)
         cap = _Captured(torch.cuda.CUDAGraph(), meta, None)
-        step = self._fill(cap, entries, bucket, width)
-        step.extras["captured_width"] = width
+        step = self._fill(cap, [], bucket, width)
+        step.captured_width = width
         # warm up on a side stream (loads kernels, builds shared tables), then capture
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream(r.device))

@@ -59,4 +59,12 @@ def qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
     )
 
 
-register_architecture(Qwen3Config.architecture, Qwen3Config, qwen3_spec)
+def tiny_qwen3_config() -> Qwen3Config:
+    """The sizes of the reference's built-in tiny model (qwen3_runtime/llm.py:168-181), with a
+    head size the attention kernels accept."""
+    return Qwen3Config(vocab_size=32, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=16, intermediate_size=64, rms_norm_eps=1e-6,
+                       rope_theta=10000.0, max_position_embeddings=128, tie_word_embeddings=True)
+
+
+register_architecture(Qwen3Config.architecture, Qwen3Config, qwen3_spec, tiny_config=tiny_qwen3_config)

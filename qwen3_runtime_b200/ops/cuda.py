@@ -259,7 +259,7 @@ class CudaOps:
                 q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, k_pages=k_pages,
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
-                max_kv_len=step.extras.get("captured_width", 0) * page_size or step.max_kv_len)
+                max_kv_len=step.captured_width * page_size or step.max_kv_len)
         if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel

@@ -73,6 +73,9 @@ class PagedAttention(Part):
     def cache_spec(self):
         return KVLayerSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def position_limit(self):
+        return self.position.position_limit()
+
     def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
         ops = self.ops
         T = h.shape[0]
@@ -88,7 +91,7 @@ class PagedAttention(Part):
                 and fusable(qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                             cos=cos, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight)):
             # one kernel: norm and rotation of the newest q and k, cache write, split-KV attention
-            width = step.extras.get("captured_width", 0)
+            width = step.captured_width
             ops.paged_attention_decode(
                 qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
                 head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,

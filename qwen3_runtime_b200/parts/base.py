@@ -65,6 +65,11 @@ class StepContext:
     # host copies (lists) for parts that need them without a device read
     host_cu_seqlens: list[int] = field(default_factory=list)
     host_kv_lens: list[int] = field(default_factory=list)
+    # Non-zero in a step that is being captured into (or replayed from) a CUDA graph: the
+    # block-table width the graph is made for.  A part whose launch shape depends on the
+    # longest sequence has to size it from ``captured_width * page_size`` then, not from
+    # ``max_kv_len``, because the graph is replayed for longer sequences of the same width.
+    captured_width: int = 0
     extras: dict = field(default_factory=dict)  # per-step scratch shared by the layers of a step
 
 
@@ -92,6 +97,12 @@ class Part:
     def kernel_groups(self) -> list[str]:
         """CUDA source groups this part launches (compiled before the first step)."""
         return []
+
+    def position_limit(self) -> int | None:
+        """Positions this part can serve (``0 .. limit - 1``), or None when any position will do.
+        A position encoding with a table says its length; a part made of parts passes on the
+        smallest limit among them."""
+        return None
 
 
 _REGISTRY: dict[tuple[str, str], Callable[[PartSpec, BuildContext], Part]] = {}

@@ -44,6 +44,10 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    def position_limit(self):
+        limits = [n for n in (part.position_limit() for part in self.children.values()) if n is not None]
+        return min(limits) if limits else None
+
     def forward(self, stream: ResidualStream, step: StepContext, cache) -> None:
         h = self.mixer_norm.add_norm(stream)
         stream.pending = self.mixer.forward(h, step, cache)

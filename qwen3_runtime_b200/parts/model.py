@@ -57,14 +57,19 @@ class DecoderModel:
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         """``tensors``: every expected name -> tensor already on the device."""
+        self.load_from(tensors.__getitem__)
+
+    def load_from(self, fetch) -> None:
+        """``fetch(name)`` returns the named tensor on the device.  Tensors are asked for part by
+        part and let go as soon as the part has taken (and possibly fused) them, so that beside
+        the model's own tensors only one block's stored tensors are alive at any time."""
         s = self.spec
-        self.embed = tensors[s.embed_name].contiguous()
+        self.embed = fetch(s.embed_name).contiguous()
         for i, block in enumerate(self.blocks):
             prefix = s.block_prefix.format(index=i)
-            block.load({n[len(prefix):]: t for n, t in tensors.items() if n.startswith(prefix)})
-        fp = s.final_norm_prefix
-        self.final_norm.load({n[len(fp):]: t for n, t in tensors.items() if n.startswith(fp)})
-        self.head = self.embed if s.tie_word_embeddings else tensors[s.head_name].contiguous()
+            block.load({name: fetch(prefix + name) for name in block.param_specs()})
+        self.final_norm.load({name: fetch(s.final_norm_prefix + name) for name in self.final_norm.param_specs()})
+        self.head = self.embed if s.tie_word_embeddings else fetch(s.head_name).contiguous()
         self.loaded = True
 
     def kernel_groups(self) -> list[str]:
@@ -72,6 +77,11 @@ class DecoderModel:
         for part in [*self.blocks, self.final_norm]:
             groups.update(part.kernel_groups())
         return sorted(groups)
+
+    def position_limit(self) -> int | None:
+        """The longest sequence every part can serve (None: no part sets a limit)."""
+        limits = [n for n in (b.position_limit() for b in self.blocks) if n is not None]
+        return min(limits) if limits else None
 
     # ---- cache ------------------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:

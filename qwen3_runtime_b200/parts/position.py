@@ -36,6 +36,9 @@ class RotaryNeox(Part):
     def kernel_groups(self):
         return ["rope_kv"]
 
+    def position_limit(self):
+        return self.max_positions
+
     def inverse_frequencies(self) -> torch.Tensor:
         """inv_j = 1 / theta^(2j / rotary_dim), computed on the host in float32 exactly as
         the reference does (layers/rope.py:18), so both sides rotate by the same angles."""

@@ -54,7 +54,7 @@ def main(argv: list[str] | None = None) -> int:
     model, config, _raw = load_model(args.model, dtype=dtype)
     num_pages = max(1, -(-args.max_tokens // args.page_size))
     cuda_graph = (dtype == "bfloat16") if args.cuda_graph is None else args.cuda_graph
-    rt = build_runtime(model, max_positions=config.max_position_embeddings, block_size=args.page_size,
+    rt = build_runtime(model, block_size=args.page_size,
                        num_kv_blocks=num_pages, max_num_seqs=args.max_live, cuda_graph=cuda_graph)
     live = {}
     for line in sys.stdin:

@@ -26,16 +26,23 @@ class SamplingParams:
     logprobs: bool = False
 
     def __post_init__(self) -> None:
-        if not math.isfinite(self.temperature):
-            raise ValueError("temperature must be finite")
-        if not math.isfinite(self.top_p) or not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must satisfy 0 < top_p <= 1")
-        if not math.isfinite(self.min_p) or not 0.0 <= self.min_p <= 1.0:
-            raise ValueError("min_p must satisfy 0 <= min_p <= 1")
+        # the same values are refused as in qwen3_runtime/sampling_params.py:31-46
+        problems = []
+        for name in ("temperature", "top_p", "min_p", "repetition_penalty", "presence_penalty",
+                     "frequency_penalty"):
+            if not math.isfinite(getattr(self, name)):
+                problems.append(f"{name} must be finite")
+        if not problems:
+            if not 0.0 < self.top_p <= 1.0:
+                problems.append("top_p must satisfy 0 < top_p <= 1")
+            if not 0.0 <= self.min_p <= 1.0:
+                problems.append("min_p must satisfy 0 <= min_p <= 1")
+            if self.repetition_penalty <= 0.0:
+                problems.append("repetition_penalty must be positive and finite")
         if self.min_tokens < 0:
-            raise ValueError("min_tokens must be non-negative")
-        if self.repetition_penalty <= 0 or not math.isfinite(self.repetition_penalty):
-            raise ValueError("repetition_penalty must be positive and finite")
+            problems.append("min_tokens must be non-negative")
+        if problems:
+            raise ValueError("invalid sampling parameters: " + "; ".join(problems))
 
     def is_greedy(self) -> bool:
         return self.temperature <= 0.0

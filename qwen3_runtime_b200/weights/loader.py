@@ -117,9 +117,10 @@ def place(tensor: torch.Tensor, spec: ParamSpec, dtype: torch.dtype, device) -> 
 
 
 def load_into(model, source: TensorSource) -> None:
-    """Check ``source`` against ``model.expected_tensors()`` and load every tensor."""
+    """Check ``source`` against ``model.expected_tensors()`` and load every tensor.  Each tensor
+    is moved to the device when the part that owns it asks for it, so a part that fuses stored
+    tensors (q/k/v, gate/up) holds the separate copies only while it fuses them."""
     expected = model.expected_tensors()
     check_tensors(expected, source, model.ignorable_tensors())
     ctx = model.ctx
-    placed = {name: place(source.get(name), ps, ctx.dtype, ctx.device) for name, ps in expected.items()}
-    model.load(placed)
+    model.load_from(lambda name: place(source.get(name), expected[name], ctx.dtype, ctx.device))

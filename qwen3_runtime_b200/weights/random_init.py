@@ -16,7 +16,7 @@ from pathlib import Path
 
 import torch
 
-from ..config.registry import resolve_architecture
+from ..config.registry import architecture_for_config
 from ..parts.base import BuildContext, ParamSpec
 from ..parts.model import DecoderModel
 
@@ -25,7 +25,7 @@ _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 def expected_tensors_for(config) -> dict[str, ParamSpec]:
     """Checkpoint names and shapes of the model a typed config describes (no device needed)."""
-    arch = resolve_architecture({"architectures": [config.architecture]})
+    arch = architecture_for_config(config)
     ctx = BuildContext(dtype=torch.float32, device=torch.device("cpu"), ops=None)
     return DecoderModel(arch.build_spec(config), ctx).expected_tensors()
 

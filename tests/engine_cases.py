@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 import plain_model as pm
-from helpers import (TINY, first_mismatch, make_model_dir, peak_tokens, random_ids, run_trace, 
+from helpers import (TINY, first_mismatch, make_model_dir, peak_live, peak_tokens, random_ids, run_trace,
                      trace_mixed, trace_portions, trace_tail_decode, trace_whole)
 from qwen3_runtime_b200.engine.factory import build_engine, build_runtime, load_model
 
@@ -26,16 +26,17 @@ def tolerance(dtype: str, scale: float) -> float:
     return TOL_F32 * max(1.0, scale / 4.0) if dtype == "float32" else REL_TOL_BF16 * scale
 
 
-def check_greedy_within_rounding(raw, w, prompt, tokens, what):
+def check_greedy_within_rounding(raw, w, prompt, tokens, what, dtype="bfloat16"):
     """bfloat16 greedy tokens: two logits within rounding of each other may swap, after which a
     recomputed sequence goes another way, so whole sequences are not compared.  Instead every
     token is checked at its own place: given the tokens the engine chose before it, the plain
     model's logit for it is the largest, or below the largest by no more than the two logits'
     tolerances together."""
-    logits = pm.forward_logits(raw, w, list(prompt) + list(tokens[:-1]), act_dtype=torch.bfloat16)
-    rows = logits[len(prompt) - 1:]
+    rows = pm.forward_logits(raw, w, list(prompt) + list(tokens[:-1]),
+                             rows=list(range(len(prompt) - 1, len(prompt) + len(tokens) - 1)),
+                             act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
     assert rows.shape[0] == len(tokens)
-    tol = 2 * tolerance("bfloat16", float(logits.abs().max()))
+    tol = 2 * tolerance(dtype, float(rows.abs().max()))
     for i, tok in enumerate(tokens):
         gap = float(rows[i].max() - rows[i][tok])
         assert gap <= tol, f"{what}: token {i} ({tok}) is {gap:.3g} below the plain argmax (allowed {tol:.3g})"
@@ -54,18 +55,22 @@ def requests_for(name, lengths, seed=0):
 
 def make_runtime(folder, name, dtype, ops, device, *, num_pages, max_live=4, cuda_graph=False):
     model, cfg, _ = load_model(folder, dtype=dtype, device=device, ops=ops)
-    return build_runtime(model, max_positions=cfg.max_position_embeddings, block_size=TINY[name]["page_size"],
-                         num_kv_blocks=num_pages, max_num_seqs=max_live, cuda_graph=cuda_graph)
+    rt = build_runtime(model, block_size=TINY[name]["page_size"], num_kv_blocks=num_pages, max_num_seqs=max_live,
+                       cuda_graph=cuda_graph)
+    assert rt.max_positions == cfg.max_position_embeddings  # taken from the model's own position part
+    return rt
 
 
-def check_against(got, want, dtype, what):
+def check_against(got, want, dtype, what, positions=None):
+    """``positions``: how many logit rows ``got`` has to hold (default: every position of ``want``)."""
     scale = max(float(v.abs().max()) for v in want.values())
     tol = tolerance(dtype, scale)
     bad = first_mismatch(got, want, tol)
     assert bad is None, (f"{what}: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g} "
                          f"(tolerance {tol:.3g}, logits up to {scale:.3g})")
     n = sum(len(v) for v in got.values())
-    assert n == sum(v.shape[0] for v in want.values()), f"{what}: {n} positions compared"
+    expect = sum(v.shape[0] for v in want.values()) if positions is None else positions
+    assert n == expect, f"{what}: {n} positions compared, {expect} expected"
 
 
 def case_four_schedules(tmp_path, name, dtype, ops, device, lengths=(100, 37, 61, 150, 45, 83)):
@@ -97,6 +102,66 @@ def case_four_schedules(tmp_path, name, dtype, ops, device, lengths=(100, 37, 61
         bad = first_mismatch(results[kind], whole, cut_tol)
         assert bad is None, f"{name} {dtype} {kind} vs whole: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g}"
     return results
+
+
+def case_many_live(tmp_path, name, dtype, ops, device, max_live, *, cuda_graph=False, seed=0):
+    """The mixed schedule with ``max_live`` requests live at once (portions of some beside single
+    tokens of many others), in a pool of exactly the peak so that pages are handed on, every
+    returned page poisoned; and the same requests' last tokens decoded together, one token per
+    request and step, which is the batch a captured decode step of that size serves."""
+    import random as _random
+
+    folder = make_model_dir(tmp_path, name)
+    rnd = _random.Random(1000 * max_live + seed)
+    requests = requests_for(name, [rnd.randint(14, 60) for _ in range(2 * max_live + 3)], seed=seed + 20)
+    want = plain_logits(folder, requests, dtype)
+    ps = TINY[name]["page_size"]
+    steps = trace_mixed(requests, seed=seed + 3, max_live=max_live)
+    assert peak_live(steps) == max_live, f"the trace was meant to hold {max_live} requests at once"
+    rt = make_runtime(folder, name, dtype, ops, device, num_pages=peak_tokens(steps, 64) // ps, max_live=max_live,
+                      cuda_graph=cuda_graph)
+    got = run_trace(rt, steps, poison=True)
+    check_against(got, want, dtype, f"{name} {dtype} mixed with {max_live} live")
+    assert rt.cache.num_free_pages == rt.cache.num_pages
+    # max_live requests decoding side by side: prompts whole (one step each), then 6 steps of
+    # one token for every request at once
+    batch = dict(list(requests.items())[:max_live])
+    together = []
+    for i, (rid, toks) in enumerate(batch.items()):
+        head = len(toks) - 6
+        together.append({"step": i, "entries": [{"id": rid, "tokens": toks[:head], "want": [head - 1]}], "end": []})
+    for j in range(6):
+        together.append({"step": max_live + j, "end": list(batch) if j == 5 else [],
+                         "entries": [{"id": rid, "tokens": [toks[len(toks) - 6 + j]], "want": [0]}
+                                     for rid, toks in batch.items()]})
+    rt = make_runtime(folder, name, dtype, ops, device, num_pages=peak_tokens(together, 64) // ps, max_live=max_live,
+                      cuda_graph=cuda_graph)
+    got = run_trace(rt, together)
+    check_against(got, want, dtype, f"{name} {dtype} {max_live} requests decoding together", positions=7 * max_live)
+    if cuda_graph and rt.runner.graphs is not None and max_live <= max(rt.runner.graphs.sizes):
+        assert rt.runner.graphs.replays == 6, "the six decode steps were meant to replay a captured graph"
+    return got
+
+
+def case_greedy_many(tmp_path, name, dtype, ops, device, num_requests, *, cuda_graph=True, max_tokens=6):
+    """Greedy generation of ``num_requests`` requests side by side under the scheduler (a token
+    budget that cuts the prompts, a decode batch of that size, captured or not)."""
+    folder = make_model_dir(tmp_path, name)
+    raw, w = pm.read_model_dir(folder)
+    ps = TINY[name]["page_size"]
+    prompts = list(requests_for(name, [5 + (7 * i) % 23 for i in range(num_requests)], seed=31).values())
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    eng = build_engine(folder, dtype=dtype, device=device, ops=ops, block_size=ps,
+                       num_kv_blocks=num_requests * (-(-40 // ps) + 1), max_num_seqs=num_requests,
+                       max_num_batched_tokens=48, cuda_graph=cuda_graph)
+    got = eng.generate_batch(prompts, max_tokens=max_tokens)
+    assert eng.cache.num_free_pages == eng.cache.num_pages
+    for p, toks in zip(prompts, got):
+        if dtype == "float32":
+            assert toks == pm.greedy_generate(raw, w, p, max_tokens, act_dtype=act)
+        else:
+            check_greedy_within_rounding(raw, w, p, toks, f"{name} {num_requests} side by side")
+    return eng
 
 
 def case_first_tokens(tmp_path, name, dtype, ops, device):

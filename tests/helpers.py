@@ -28,6 +28,19 @@ TINY = {
                            num_key_value_heads=3, head_dim=48, intermediate_size=112, rms_norm_eps=3e-5,
                            rope_theta=5e5, max_position_embeddings=512, tie_word_embeddings=False),
         page_size=4, vector_std=0.1, seed=13),
+    # head sizes 64 and 128: the only tiny models whose bfloat16 steps take the split-KV decode
+    # kernel (with the newest token's q/k/v made inside it), the tensor-core prefill kernels and,
+    # with rows of 16-byte multiples, the weight-streaming products
+    "D": dict(
+        config=Qwen3Config(vocab_size=320, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=64, intermediate_size=192, rms_norm_eps=1e-6,
+                           rope_theta=1e6, max_position_embeddings=1024, tie_word_embeddings=True),
+        page_size=16, vector_std=0.05, seed=14),
+    "E": dict(
+        config=Qwen3Config(vocab_size=411, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=1, head_dim=128, intermediate_size=320, rms_norm_eps=1e-5,
+                           rope_theta=1e6, max_position_embeddings=1024, tie_word_embeddings=False),
+        page_size=16, vector_std=0.05, seed=15),
 }
 
 # Random N(0, 0.02) weights at these widths give almost flat logits that hide faults;
@@ -123,6 +136,31 @@ def trace_mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4
             steps.append({"step": s, "entries": entries, "end": end})
             s += 1
     return steps
+
+
+def peak_live(steps: list[dict]) -> int:
+    """The most requests that are live at the same time in a trace."""
+    live: set[str] = set()
+    peak = 0
+    for st in steps:
+        live.update(e["id"] for e in st["entries"])
+        peak = max(peak, len(live))
+        live.difference_update(st["end"])
+    return peak
+
+
+def thin_wants(steps: list[dict], keep: int = 2) -> list[dict]:
+    """The same trace asking for fewer logits: of every entry's wanted places only the first
+    and the last ``keep - 1`` (large vocabularies make every wanted row expensive to compare)."""
+    out = []
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            w = sorted(e["want"])
+            w = w if len(w) <= keep else [w[0], *w[len(w) - keep + 1:]]
+            entries.append({**e, "want": w})
+        out.append({**st, "entries": entries})
+    return out
 
 
 def peak_tokens(steps: list[dict], round_to: int = 64) -> int:

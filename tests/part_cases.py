@@ -333,8 +333,16 @@ class DecayStateMixer(Part):
         return StateLayerSpec((self.width,), "float32")
 
     def forward(self, h, step, cache):
-        out = torch.empty_like(h)
         u = h.float() @ self.w_in.t()
+        if step.decode_only and h.is_cuda:
+            # one token per sequence: device-side gather and scatter of the slots, nothing read
+            # back to the host, so the step can be captured into a CUDA graph
+            slots = step.state_slots.long()
+            s = self.decay * cache.state.index_select(0, slots) + u
+            if cache.writes:
+                cache.state.index_copy_(0, slots, s)
+            return (s @ self.w_out.t()).to(h.dtype)
+        out = torch.empty_like(h)
         slots = step.state_slots.tolist()
         for b in range(step.num_seqs):
             lo, hi = step.host_cu_seqlens[b], step.host_cu_seqlens[b + 1]
@@ -391,6 +399,43 @@ def case_toy_state_mixer(dtype, ops, device):
             assert float((whole[k] - mixed[k]).abs().max()) <= t
         # and the state matters: with another decay the logits move
         assert float((whole["a"][5:] - whole["a"][:-5]).abs().max()) > 1e-3
+    finally:
+        unregister_part("mixer", "toy_decay_state")
+
+
+def case_toy_state_mixer_in_captured_steps(dtype, ops, device):
+    """A model with a state layer decodes through captured graphs, with the engine running ahead
+    and not: the same tokens as without graphs.  A graph is warmed up and captured on padding
+    rows only, so the state of a live request is advanced exactly once per token; were it
+    advanced by the warm-up as well, the first decode step of every new graph would count its
+    token twice and the tokens would differ."""
+    from qwen3_runtime_b200.engine.factory import build_engine
+
+    cfg = TINY["A"]["config"]
+    base = qwen3_spec(cfg)
+    register_part("mixer", "toy_decay_state", DecayStateMixer)
+    try:
+        toy = PartSpec("toy_decay_state", dict(hidden_size=cfg.hidden_size, state_size=24, decay=0.8))
+        blocks = (base.blocks[0], PartSpec("pre_norm", {**base.blocks[1].params, "mixer": toy}))
+        spec = ModelSpec(base.vocab_size, base.hidden_size, blocks, base.order, base.final_norm, True)
+        model, _ = _toy_model(spec, cfg, dtype, ops, device)
+        prompts = [random_ids(cfg.vocab_size, n, 40 + n) for n in (9, 21, 4)]
+
+        def tokens(cuda_graph, run_ahead):
+            eng = build_engine(model=model, config=cfg, dtype=dtype, device=device, block_size=4, num_kv_blocks=60,
+                               max_num_seqs=3, max_num_batched_tokens=16, cuda_graph=cuda_graph, run_ahead=run_ahead)
+            out = eng.generate_batch(prompts, max_tokens=40)  # 40 tokens: the block tables outgrow a graph's width
+            replays = eng.runner.graphs.replays if eng.runner.graphs is not None else 0
+            return out, replays, eng.num_run_ahead
+
+        want, _, _ = tokens(False, False)
+        for run_ahead in (False, True):
+            got, replays, ahead = tokens(True, run_ahead)
+            assert replays >= 30 and (ahead >= 30) == run_ahead
+            if dtype == "float32":
+                assert got == want, f"captured steps (run_ahead={run_ahead}) changed the tokens"
+            else:  # a logit within rounding may swap; the first steps after each capture must agree
+                assert [g[:3] for g in got] == [w[:3] for w in want]
     finally:
         unregister_part("mixer", "toy_decay_state")
 

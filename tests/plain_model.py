@@ -156,10 +156,13 @@ def forward_hidden(raw, w, ids, *, compute=torch.float32, act_dtype=None, order=
     return h, w
 
 
-def forward_logits(raw, w, ids, **kw):
+def forward_logits(raw, w, ids, rows=None, **kw):
     """Logits at every position, [T, V] (qwen3_runtime/models/qwen3.py:263-266): final
-    RMSNorm, then the tied embedding or ``lm_head.weight``."""
+    RMSNorm, then the tied embedding or ``lm_head.weight``.  ``rows``: only those positions
+    (the reference, too, gives the head only the rows that sample, :262-264)."""
     h, wc = forward_hidden(raw, w, ids, **kw)
+    if rows is not None:
+        h = h[torch.as_tensor(rows, dtype=torch.long)]
     n = _round(rmsnorm(h, wc["model.norm.weight"], raw["rms_norm_eps"]), kw.get("act_dtype"))
     head = wc["model.embed_tokens.weight"] if raw["tie_word_embeddings"] else wc["lm_head.weight"]
     return n @ head.T
@@ -171,7 +174,7 @@ def greedy_generate(raw, w, prompt, max_tokens, **kw):
     ids = list(prompt)
     out = []
     for _ in range(max_tokens):
-        tok = int(torch.argmax(forward_logits(raw, w, ids, **kw)[-1]).item())
+        tok = int(torch.argmax(forward_logits(raw, w, ids, rows=[len(ids) - 1], **kw)[0]).item())
         ids.append(tok)
         out.append(tok)
     return out

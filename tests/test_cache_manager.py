@@ -149,4 +149,11 @@ def test_layout_groups_layers_by_need():
     assert layout.paged_groups == [0, 1]
     assert layout.page_bytes(4, 2) == [2 * 2 * 2 * 16 * 4 * 2, 1 * 2 * 2 * 16 * 4 * 2]
     assert layout.token_bytes(2) == 3 * 2 * 2 * 16 * 2
-    assert layout.pages_for_budget(10_000, 4, 2) == 10_000 // sum(layout.page_bytes(4, 2))
+    equal = 10_000 // sum(layout.page_bytes(4, 2))
+    assert layout.pages_for_budget(10_000, 4, 2) == [equal, equal]
+    # a window group is capped at what its requests can hold; the rest goes to the full group
+    full_b, win_b = layout.page_bytes(4, 2)
+    counts = layout.pages_for_budget(100_000, 4, 2, max_num_seqs=2, max_step_tokens=8)
+    cap = 2 * (-(-(8 + 8) // 4) + 2)
+    assert counts[1] == cap and counts[0] == (100_000 - cap * win_b) // full_b
+    assert counts[0] * full_b + counts[1] * win_b <= 100_000 and counts[0] > 100_000 // (full_b + win_b)

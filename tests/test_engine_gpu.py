@@ -85,3 +85,52 @@ def test_running_ahead_under_random_arrivals_stops_and_aborts(tmp_path, ops, dty
     ran_ahead = sum(ec.case_run_ahead_random(tmp_path, "A", dtype, ops, "cuda", seed, cuda_graph=True)
                     for seed in range(6))
     assert ran_ahead > 10
+
+
+# ---- head sizes 64 and 128: the split-KV decode kernel with the newest token made inside it, the
+# ---- ticket merge, the weight-streaming products with partial sums, captured graphs over them
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_four_schedules_at_head_sizes_64_and_128(tmp_path, ops, name):
+    before = ops.launches
+    ec.case_four_schedules(tmp_path, name, "bfloat16", ops, "cuda", lengths=(100, 37, 61, 150, 45, 83))
+    assert ops.launches > before
+    ops.raise_if_kernel_error()
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_greedy_generation_at_head_sizes_64_and_128_with_graphs(tmp_path, ops, name):
+    ec.case_greedy_generation(tmp_path, name, "bfloat16", ops, "cuda", cuda_graph=True)
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_running_ahead_at_head_sizes_64_and_128_with_graphs(tmp_path, ops, name):
+    """Stop tokens found one step late (the abandoned step writes keys and values into pages that
+    were already returned), aborts, late arrivals, a pool so small that a request is preempted."""
+    ec.case_run_ahead(tmp_path, name, "bfloat16", ops, "cuda", cuda_graph=True)
+
+
+def test_running_ahead_under_random_scenarios_at_head_size_128(tmp_path, ops):
+    ran_ahead = sum(ec.case_run_ahead_random(tmp_path, "E", "bfloat16", ops, "cuda", seed, cuda_graph=True)
+                    for seed in range(6))
+    assert ran_ahead > 10
+
+
+# ---- as many live requests as the benchmark's batches: graph buckets 8..64, the streaming
+# ---- kernels' variant for more than 8 tokens, 17..64-token steps, more sequences than any bucket
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("max_live,name", [(8, "E"), (12, "A"), (16, "D"), (24, "B"), (33, "E"), (48, "D"),
+                                           (64, "E"), (70, "C"), (70, "E")])
+def test_mixed_schedule_and_decoding_together_with_many_live_requests(tmp_path, ops, max_live, name, dtype):
+    ec.case_many_live(tmp_path, name, dtype, ops, "cuda", max_live, cuda_graph=(dtype == "bfloat16"))
+    ops.raise_if_kernel_error()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cuda_graph", [False, True])
+@pytest.mark.parametrize("num,name", [(8, "E"), (16, "D"), (24, "A"), (33, "E"), (64, "D"), (70, "E")])
+def test_greedy_generation_of_many_requests_side_by_side(tmp_path, ops, num, name, dtype, cuda_graph):
+    eng = ec.case_greedy_many(tmp_path, name, dtype, ops, "cuda", num, cuda_graph=cuda_graph)
+    if cuda_graph and num <= 64:
+        assert eng.runner.graphs.replays > 0

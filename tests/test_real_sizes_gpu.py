@@ -52,3 +52,125 @@ def test_four_schedules_at_real_layer_sizes(real, dtype):
         whole = {rid: torch.stack([rows[p] for p in sorted(rows)]) for rid, rows in results["whole"].items()}
         for kind in ("tail", "portions", "mixed"):
             assert first_mismatch(results[kind], whole, 0.0) is None, f"{kind}: float32 logits are not bit-identical"
+
+
+def _wanted_positions(steps):
+    """{request: sorted positions whose logits the trace asks for}."""
+    pos, out = {}, {}
+    for st in steps:
+        for e in st["entries"]:
+            start = pos.get(e["id"], 0)
+            out.setdefault(e["id"], set()).update(start + w for w in e["want"])
+            pos[e["id"]] = start + len(e["tokens"])
+    return {rid: sorted(p) for rid, p in out.items()}
+
+
+@pytest.fixture(scope="module")
+def real_fp32_weights(real):
+    folder, _, _ = real
+    raw, w = pm.read_model_dir(folder)
+    return raw, {k: v.float() for k, v in w.items()}  # converted once; the plain model converts per call
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("max_live", [8, 33])
+def test_mixed_schedule_with_many_live_requests_at_real_layer_sizes(real, real_fp32_weights, max_live, dtype):
+    """Portions beside decode tokens with 8 and with 33 requests live at once: steps of a few
+    tokens up to a hundred, so every range of the products' dispatch is crossed (at most 16
+    tokens, 17..64, more), in a pool of exactly the peak with returned pages poisoned; then all
+    of them decoding side by side through a captured graph (bfloat16)."""
+    import random
+
+    from helpers import peak_live, thin_wants
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    folder, _, _ = real
+    raw, w32 = real_fp32_weights
+    rnd = random.Random(max_live)
+    requests = {f"m{i}": random_ids(CFG.vocab_size, rnd.randint(14, 40), 900 + i) for i in range(2 * max_live + 3)}
+    steps = thin_wants(trace_mixed(requests, seed=9, max_live=max_live, decode_tail=4))
+    assert peak_live(steps) == max_live
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = {}
+    for rid, positions in _wanted_positions(steps).items():
+        rows = pm.forward_logits(raw, w32, requests[rid], rows=positions, act_dtype=act)
+        want[rid] = dict(zip(positions, rows))
+    ops = CudaOps()
+    model, _cfg, _ = load_model(folder, dtype=dtype, ops=ops)
+    rt = build_runtime(model, block_size=16, num_kv_blocks=peak_tokens(steps, 64) // 16, max_num_seqs=max_live,
+                       cuda_graph=(dtype == "bfloat16"))
+    got = run_trace(rt, steps, poison=True)
+    ops.raise_if_kernel_error()
+    scale = max(float(r.abs().max()) for rows in want.values() for r in rows.values())
+    tol = ec.tolerance(dtype, scale)
+    bad = first_mismatch(got, want, tol)
+    assert bad is None, f"request {bad[0]} position {bad[1]} differs by {bad[2]:.3g} (tolerance {tol:.3g})"
+    assert sum(len(v) for v in got.values()) == sum(len(v) for v in want.values())
+    sizes = sorted({sum(len(e["tokens"]) for e in st["entries"]) for st in steps})
+    assert sizes[0] <= 16 and (max_live < 17 or any(17 <= n <= 64 for n in sizes))
+
+
+def test_a_long_prompt_takes_the_tcgen05_swiglu_product_on_the_default_path(real, real_fp32_weights):
+    """A request of 640 tokens, whole and in portions of 512 + 128: with the default choice of
+    products the fused gate_up + SwiGLU product of 512 tokens and more runs on this engine's paired
+    tcgen05 kernel (seen by a spy on the kernel table), and the logits match the plain model."""
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    folder, _, _ = real
+    raw, w32 = real_fp32_weights
+    ids = random_ids(CFG.vocab_size, 640, 77)
+    positions = [0, 1, 127, 128, 300, 511, 512, 638, 639]
+    want = pm.forward_logits(raw, w32, ids, rows=positions, act_dtype=torch.bfloat16)
+    ops = CudaOps()
+    assert ops.large_gemm == "auto"
+    seen = []
+    real_tc = ops.linear_tcgen05
+
+    def spy(x, weight, out=None, out_dtype=None, mode=None, pair=None):
+        seen.append((x.shape[0], mode))
+        return real_tc(x, weight, out=out, out_dtype=out_dtype, mode=mode, pair=pair)
+
+    ops.linear_tcgen05 = spy
+    model, _cfg, _ = load_model(folder, dtype="bfloat16", ops=ops)
+    tol = ec.tolerance("bfloat16", float(want.abs().max()))
+    for cuts in ((640,), (512, 128)):
+        seen.clear()
+        rt = build_runtime(model, block_size=16, num_kv_blocks=40, max_num_seqs=2)
+        rc = rt.cache.open("long")
+        rows, start = [], 0
+        for n in cuts:
+            rt.cache.reserve(rc, n)
+            wanted = [p - start for p in positions if start <= p < start + n]
+            from qwen3_runtime_b200.engine.batch import StepEntry
+
+            rows.append(rt.runner.run([StepEntry(rc, ids[start:start + n], wanted)]).float().cpu())
+            start += n
+        rt.cache.close(rc)
+        ops.raise_if_kernel_error()
+        got = torch.cat(rows)
+        assert (cuts[0], 2) in seen, f"the SwiGLU product of {cuts[0]} tokens did not reach the tcgen05 kernel: {seen}"
+        assert float((got - want).abs().max()) <= tol, f"cuts {cuts}: {float((got - want).abs().max()):.3g} > {tol:.3g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_scheduler_drives_a_model_of_real_layer_sizes(real, real_fp32_weights, dtype):
+    """Six prompts through ``build_engine(...).generate_batch`` with a 256-token budget (prompts cut
+    into portions that share steps with decode tokens), captured decode steps, running ahead, and
+    so few pages that a request is preempted and recomputed: every generated token is, at its
+    place, the plain model's argmax up to rounding."""
+    from qwen3_runtime_b200.engine.factory import build_engine
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+
+    folder, _, _ = real
+    raw, w32 = real_fp32_weights
+    prompts = [random_ids(CFG.vocab_size, n, 500 + n) for n in (40, 300, 25, 120, 60, 18)]
+    ops = CudaOps()
+    eng = build_engine(folder, dtype=dtype, ops=ops, block_size=16, num_kv_blocks=30, max_num_seqs=6,
+                       max_num_batched_tokens=256, cuda_graph=True, run_ahead=True)
+    got = eng.generate_batch(prompts, max_tokens=6)
+    ops.raise_if_kernel_error()
+    assert eng.scheduler.num_preemptions >= 1, "the pool was meant to be too small for all six"
+    assert eng.cache.num_free_pages == eng.cache.num_pages
+    for p, toks in zip(prompts, got):
+        assert len(toks) == 6
+        ec.check_greedy_within_rounding(raw, w32, p, toks, f"4B sizes {dtype}, prompt of {len(p)}", dtype=dtype)
