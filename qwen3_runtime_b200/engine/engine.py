@@ -193,7 +193,9 @@ class Engine:
 
     def _collect_step_stats(self, reqs: list[Request], preempt_before: int) -> dict:
         stats = dict(req_ids=[r.request_id for r in reqs], prefill_tokens=0, decode_tokens=0, prefill_reqs=0,
-                     decode_reqs=0, preempts=self.scheduler.num_preemptions - preempt_before)
+                     decode_reqs=0, preempts=self.scheduler.num_preemptions - preempt_before,
+                     # per request: (tokens already in the cache, tokens this step runs)
+                     spans=[(r.num_computed_tokens, r.num_scheduled_tokens) for r in reqs])
         for r in reqs:
             kind = "decode" if r.is_prefill_complete else "prefill"
             stats[kind + "_tokens"] += r.num_scheduled_tokens

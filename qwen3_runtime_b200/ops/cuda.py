@@ -117,6 +117,25 @@ _SIGNATURES = {
 }
 
 
+class _Span:
+    """CUDA events around one launch, appended to the kernel table's timing records."""
+
+    def __init__(self, ops, what: str):
+        self.ops, self.what = ops, what
+
+    def __enter__(self):
+        self.start, self.stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.record()
+        nbytes, flops, tag = self.ops._cost
+        self.ops._cost = (0, 0, "")
+        self.ops.timing.append((self.what + tag, self.start, self.stop, nbytes, flops))
+        return False
+
+
 class CudaOps:
     """Kernels on the current CUDA device.  ``groups`` are compiled up front (in
     parallel); any other group is compiled when first used."""
@@ -169,6 +188,10 @@ class CudaOps:
         self.SM_COUNT = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self._fn: dict[str, ctypes._CFuncPtr] = {}
         self.launches = 0  # kernels of this engine launched (or captured) through this table
+        # Per-kernel timing, off by default: a list makes every launch through this table record
+        # (kernel, start event, stop event, algorithmic bytes, flops) into it; see timed_kernels().
+        self.timing: list | None = None
+        self._cost = (0, 0, "")
         if groups:
             build.compile_groups([g for g in groups])
 
@@ -193,7 +216,34 @@ class CudaOps:
 
     def _call(self, group: str, name: str, what: str, *args) -> None:
         self.launches += 1
+        if self.timing is not None:
+            with self._timed(what):
+                _check(self._get(group, name)(*args, self._stream()), what)
+            return
         _check(self._get(group, name)(*args, self._stream()), what)
+
+    # ---- per-kernel timing (a debugging and reporting aid; never on in a timed run) ------------
+    def _costs(self, nbytes: float, flops: float = 0.0, tag: str = "") -> None:
+        """What the next launch has to move and compute (and a tag that tells launches of one
+        kernel apart, e.g. the sizes of a product), for the timing records."""
+        self._cost = (float(nbytes), float(flops), tag)
+
+    def _timed(self, what: str):
+        return _Span(self, what)
+
+    def timed_kernels(self) -> list[dict]:
+        """Sum the records of :attr:`timing` per kernel: launches, microseconds (CUDA events around
+        each launch, so kernels do not overlap their neighbours as they do in a captured step),
+        algorithmic bytes and flops.  Waits for the device."""
+        torch.cuda.synchronize()
+        table: dict[str, dict] = {}
+        for what, start, stop, nbytes, flops in self.timing or []:
+            row = table.setdefault(what, dict(name=what, launches=0, us=0.0, bytes=0.0, flops=0.0))
+            row["launches"] += 1
+            row["us"] += start.elapsed_time(stop) * 1e3
+            row["bytes"] += nbytes
+            row["flops"] += flops
+        return sorted(table.values(), key=lambda r: -r["us"])
 
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
@@ -211,13 +261,20 @@ class CudaOps:
             parts, stride = pending.shape[0], pending.stride(0)
         elif pending is not None and pending.dtype != out.dtype:
             raise KernelError(f"fused_norm: pending is {pending.dtype}, the output {out.dtype}")
-        self._call("norm", "q3_fused_norm", f"fused_norm(H={H})",
+        if self.timing is not None:
+            e = out.element_size()
+            self._costs(n * H * (e + (4 if resid is not None else 0) + (4 if write_resid else 0)
+                                 + (4 * parts if parts else (e if pending is not None else 0))
+                                 + (table.element_size() if table is not None else 0)))
+        self._call("norm", "q3_fused_norm", "fused_norm",
                    _dtype_code(out.dtype), _ptr(pending), parts, stride, _ptr(resid), _ptr(ids), _ptr(table), _ptr(rows),
                   _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab)
         return out
 
     def silu_mul(self, gate_up, out):
         I = out.shape[-1]
+        if self.timing is not None:
+            self._costs(3 * out.shape[0] * I * out.element_size())
         self._call("norm", "q3_silu_mul", "silu_mul",
                    _dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I)
         return out
@@ -239,6 +296,8 @@ class CudaOps:
         max_pages = block_table.shape[1] if block_table is not None else 0
         if head_dim * 16 > 48 * 1024:
             raise KernelError(f"qk_norm_rope_store: head_dim={head_dim} is too large (limit 3072)")
+        if self.timing is not None:
+            self._costs(2 * T * (num_heads + 2 * num_kv_heads) * head_dim * qkv.element_size())
         self._call("rope_kv", "q3_qk_norm_rope_store", "qk_norm_rope_store",
                    _dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads, head_dim,
                   _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
@@ -259,7 +318,7 @@ class CudaOps:
                 q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, k_pages=k_pages,
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
-                max_kv_len=step.captured_width * page_size or step.max_kv_len)
+                max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step)
         if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
@@ -273,17 +332,25 @@ class CudaOps:
                 # tcgen05/TMEM kernel; it answers "unsupported" for what it does not take
                 self.launches += 1
                 pairs = sum(-(-(-(-n * group // 128)) // 2) for n in qlens if n > 1)  # two row blocks per work item
-                code = self._get("attention_prefill_tc", "q3_paged_attention_prefill_tc")(
+                launch = lambda: self._get("attention_prefill_tc", "q3_paged_attention_prefill_tc")(  # noqa: E731
                     _ptr(q), q_stride, q.shape[0], _ptr(k_pages), _ptr(v_pages),
                     k_pages.shape[0] * num_kv_heads * page_size, _ptr(block_table), block_table.shape[1],
                     _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out), step.num_seqs, pairs, num_heads,
                     num_kv_heads, head_dim, page_size, float(scale), 1, _ptr(self._error_word(out.device)),
                     self._stream())
+                if self.timing is not None:
+                    self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=True))
+                    with self._timed("paged_attention_prefill_tc"):
+                        code = launch()
+                else:
+                    code = launch()
                 if code == 0:
                     done = True
                 elif code != 1:
                     _check(code, "paged_attention_prefill_tc")
             if work and not done:
+                if self.timing is not None:
+                    self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=True))
                 self._call("attention_prefill", "q3_paged_attention_prefill", "paged_attention_prefill",
                            _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                            block_table.shape[1], _ptr(step.kv_lens), _ptr(step.cu_seqlens), _ptr(out),
@@ -295,13 +362,34 @@ class CudaOps:
                     q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                     k_pages=k_pages, v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens,
                     cu_seqlens=step.cu_seqlens, out=out, page_size=page_size, scale=scale, window=window,
-                    num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs)
+                    num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs, step=step)
             return out
+        if self.timing is not None and step is not None:
+            self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out))
         self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                   block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,
                   head_dim, page_size, float(scale), int(window or 0))
         return out
+
+    @staticmethod
+    def _attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=None):
+        """(bytes, flops) of a step's attention: every key and value of each sequence read once, q
+        read and the result written; 4 * heads * head_dim flops per (query, key) pair.
+        ``prompts``: True counts only sequences that bring more than one token, False only those
+        that bring one, None all."""
+        e = out.element_size()
+        keys = pairs = rows = 0
+        cu = step.host_cu_seqlens
+        for b, kv in enumerate(step.host_kv_lens):
+            n = cu[b + 1] - cu[b] if len(cu) > b + 1 else 1
+            if prompts is not None and (n > 1) != prompts:
+                continue
+            keys += kv
+            rows += n
+            pairs += n * kv - n * (n - 1) // 2
+        return (2 * keys * num_kv_heads * head_dim * e + 2 * rows * num_heads * head_dim * e,
+                4 * num_heads * head_dim * pairs)
 
     SM_COUNT = 148  # of a B200; replaced by the device's own count when the table is built
     TICKETS = 1 << 16  # ticket words for the merge by the last block: sequences x kv heads of one launch
@@ -337,7 +425,7 @@ class CudaOps:
 
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
-                               max_kv_len, seq_list=None, num_splits=None, new_token=None):
+                               max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
         ``new_token`` (q_weight, k_weight, eps, cos, sin): ``q`` is the raw q/k/v projection and
         the kernel also does the work of :meth:`qk_norm_rope_store` for the newest position of
@@ -361,6 +449,8 @@ class CudaOps:
         # rows of head_dim in the page tensors: lets the kernel fetch page boxes by TMA
         kv_rows = k_pages.shape[0] * num_kv_heads * page_size if self.decode_page_boxes else 0
         err = _ptr(self._error_word(out.device))
+        if self.timing is not None and step is not None:
+            self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=False))
         if new_token is not None:
             cos, sin = new_token["cos"], new_token["sin"]
             self._call("attention_decode", "q3_paged_attention_decode_fused", "paged_attention_decode_fused",
@@ -394,6 +484,10 @@ class CudaOps:
         N = weight.shape[0]
         if weight.shape[1] != K:
             raise KernelError(f"linear: x is [{M},{K}] but weight is {list(weight.shape)}")
+        if self.timing is not None:
+            e = x.element_size()
+            oe = 4 if out_dtype == torch.float32 else e
+            self._costs(N * K * e + M * K * e + M * N * oe, 2.0 * M * N * K, f" {M}x{K}->{N}")
         if (partial_sums and self.partial_sums and out is None and out_dtype is None and M > 0
                 and self.small_gemm != "registers" and self._small_m_ok(x, weight)):
             parts = self._stream_parts(M, N, K)
@@ -420,6 +514,13 @@ class CudaOps:
             return self._skinny_product(x, weight, out, out_dtype, partial_sums and self.partial_sums)
         if self.large_gemm == "tcgen05" and self._tcgen05_ok(x, weight):
             return self.linear_tcgen05(x, weight, out=out, out_dtype=out_dtype)
+        if self.timing is not None:
+            with self._timed("library_mm"):
+                return self._library_mm(x, weight, out, out_dtype)
+        return self._library_mm(x, weight, out, out_dtype)
+
+    @staticmethod
+    def _library_mm(x, weight, out, out_dtype):
         if out_dtype is not None and out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         if out is None:
@@ -543,11 +644,17 @@ class CudaOps:
         register-streaming one (csrc/gemm_small_m.cu) for what the first refuses."""
         if self.small_gemm != "registers":
             self.launches += 1
+            cost, span = self._cost, None
+            if self.timing is not None:
+                span = self._timed("gemm_stream").__enter__()
             code = self._get("gemm_stream", "q3_gemm_stream")(
                 mode, _ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
                 int(self.small_gemm == "auto"), _ptr(self._error_word(x.device)), self._stream())
             if code == 0:
+                if span is not None:
+                    span.__exit__()
                 return
+            self._cost = cost  # refused before any launch: the register kernel takes the product
             self.launches -= 1
             if code != 1:
                 _check(code, "gemm_stream")
@@ -564,6 +671,9 @@ class CudaOps:
         one kernel for a handful of tokens, else the product followed by the SwiGLU kernel."""
         M, K = x.shape
         I = out.shape[1]
+        if self.timing is not None:
+            e = x.element_size()
+            self._costs((2 * I * K + M * K + M * I) * e, 4.0 * M * I * K, f" {M}x{K}->2x{I} swiglu")
         if self._small_m_ok(x, gate_up_weight):
             self._small_product(2, x, gate_up_weight, out, M, I, K)
             return out
@@ -576,6 +686,8 @@ class CudaOps:
     # ---- sampling ---------------------------------------------------------------------
     def argmax(self, logits, want_logprob=False):
         R, V = logits.shape
+        if self.timing is not None:
+            self._costs(R * V * 4)
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
         slices, scratch, tickets = self._row_slices(logits)
@@ -600,6 +712,8 @@ class CudaOps:
         token = torch.empty(R, dtype=torch.int32, device=logits.device)
         logprob = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprob else None
         slices, scratch, tickets = self._row_slices(logits)
+        if self.timing is not None:
+            self._costs(R * V * 4)
         self._call("sampling", "q3_sample", "sample", _ptr(logits), R, V, _ptr(temperature), _ptr(uniform),
                    _ptr(token), _ptr(logprob), _ptr(scratch), _ptr(tickets), slices)
         return token, logprob

@@ -116,7 +116,7 @@ def case_many_live(tmp_path, name, dtype, ops, device, max_live, *, cuda_graph=F
     requests = requests_for(name, [rnd.randint(14, 60) for _ in range(2 * max_live + 3)], seed=seed + 20)
     want = plain_logits(folder, requests, dtype)
     ps = TINY[name]["page_size"]
-    steps = trace_mixed(requests, seed=seed + 3, max_live=max_live)
+    steps = trace_mixed(requests, seed=seed + 3, max_live=max_live, admit=0.97)
     assert peak_live(steps) == max_live, f"the trace was meant to hold {max_live} requests at once"
     rt = make_runtime(folder, name, dtype, ops, device, num_pages=peak_tokens(steps, 64) // ps, max_live=max_live,
                       cuda_graph=cuda_graph)

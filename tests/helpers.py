@@ -105,16 +105,18 @@ def trace_portions(requests: dict[str, list[int]], seed: int = 0) -> list[dict]:
     return steps
 
 
-def trace_mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12) -> list[dict]:
+def trace_mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12,
+                admit: float = 0.7) -> list[dict]:
     """Up to ``max_live`` requests live at a time; every step holds portions of some beside
     single tokens of others; a request is sometimes left out of a step; requests end at
-    different times so that their pages are handed to later ones."""
+    different times so that their pages are handed to later ones.  ``admit``: the chance that
+    one more pending request starts in a step that has room for it."""
     rnd = random.Random(seed)
     pending = list(requests.items())
     live: dict[str, int] = {}
     steps, s = [], 0
     while pending or live:
-        while pending and len(live) < max_live and (not live or rnd.random() < 0.7):
+        while pending and len(live) < max_live and (not live or rnd.random() < admit):
             rid, _ = pending.pop(0)
             live[rid] = 0
         entries, end = [], []
