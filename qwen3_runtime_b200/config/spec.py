@@ -55,8 +55,13 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     block_prefix: str = "model.layers.{index}."
     final_norm_prefix: str = "model.norm."
+    # the head's epilogue: logits * logit_scale, then (if set) softcap * tanh(logits / softcap)
+    logit_scale: float = 1.0
+    logit_softcap: float | None = None
 
     def __post_init__(self) -> None:
+        if self.logit_softcap is not None and not self.logit_softcap > 0:
+            raise ValueError("logit_softcap must be positive (or None)")
         writers: set[int] = set()
         for run in self.order:
             if not 0 <= run.block < len(self.blocks):

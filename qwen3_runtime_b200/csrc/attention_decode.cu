@@ -19,30 +19,18 @@
 // draws the last ticket, reads all partials back and writes the result, so no kernel has to
 // start, wait for this one to drain and run just for the merge.  Slices are cut at multiples
 // of 64 keys counted from the first visible key, so an empty slice writes lse = -inf.
-#include <string.h>
-
-#define Q3_WAIT_LIMIT_CYCLES 400000000ll
-#include "async_tiles.cuh"
+#include "common.cuh"
 #include "mma_tiles.cuh"
+#include "rotary.cuh"
+
+#define Q3_ERR_POSITION 16  // error word: a newest position outside the rotation tables
 
 namespace {
 
-// ---- TMA variant: page boxes instead of 16-byte copies ------------------------------------------
-// A 64-key tile of K (and of V) is fetched as boxes of [rows of one page] x [64 dims] through a
-// tensor map with the 128-byte swizzle, issued by the lanes of warp 0 in parallel and counted on
-// one mbarrier per stage.  A box asks memory for whole 128-byte lines of a page at once, which
-// keeps DRAM far busier than 16-byte copies spread over threads.  Tile layout: D/64 slabs of
-// [64 keys][128 bytes]; chunk c of key r of slab h sits at h*8192 + r*128 + ((c ^ (r & 7)) * 16).
-constexpr int MAX_STAGES = 4;
-
-template <int D, bool TMA> __device__ __forceinline__ int kv_off(int row, int chunk) {
-  if (TMA) return (chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-  return swz<D>(row, chunk);
-}
-
 // What the fused variant needs to make q, k and v of the newest token itself, from the raw
 // output of the q/k/v projection (row layout: nq q heads, nkv k heads, nkv v heads of D):
-// per-head RMSNorm weights (null: no norm), rotation tables [max_pos, D/2] (null: none).
+// per-head RMSNorm weights (null: no norm), rotation tables [max_pos, D/2] (null: none) and which
+// elements form a rotation pair (rotary.cuh).
 struct NewToken {
   const float* q_w;
   const float* k_w;
@@ -52,6 +40,7 @@ struct NewToken {
   bf16* vpages;
   float eps;
   int max_pos;
+  int pairing;
 };
 
 constexpr int TILE = 64;     // keys per pipeline stage
@@ -132,31 +121,23 @@ __device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, cons
 // operations, so both ways give the same bits).  Nothing the block reads before pdl_wait() is
 // written by a kernel of the same step, so the first key tiles are in flight while the
 // projection before this kernel is still finishing.
-template <int D, bool FUSED, bool TMA>
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kpages,
                         const bf16* vpages, const int* __restrict__ block_table, int max_pages,
                         const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
-                        int num_splits, int stages, NewToken nt, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, int* __restrict__ error_word, int* __restrict__ tickets) {
+                        int num_splits, int stages, NewToken nt, int* __restrict__ error_word,
+                        int* __restrict__ tickets) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
   unsigned char* q_s = smem;                  // [16][D] bf16
   unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile); 1024-byte aligned
   unsigned char* new_s = kv_s + (size_t)stages * 2 * TILE_BYTES;  // FUSED: the newest key, then value, [2][D]
   // after the last tile the ring is reused: the warps' results [WARPS][16][D] + [WARPS][16][2]
 
-  if (TMA) {
-    if (threadIdx.x == 0) {
-      for (int i = 0; i < stages; ++i) mbar_init(smem_u32(full_bar + i), 1);
-      mbar_init_fence();
-    }
-    __syncthreads();
-  }
   if (!FUSED) pdl_wait();  // keys and values of the newest token come from the kernel before this one
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int slot = blockIdx.z;                // index into the partial buffers
@@ -213,36 +194,6 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     unsigned char* k_dst = kv_s + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* v_dst = k_dst + TILE_BYTES;
     const int base = k_begin + tile * TILE;
-    if (TMA) {
-      if (warp != 0) return;
-      // boxes of this tile: (page part j, slab h, K or V); a box holds `box_rows` keys of one page
-      const int box_rows = ps < TILE ? ps : TILE;
-      const int parts = TILE / box_rows;
-      const int boxes = parts * (D / 64) * 2;
-      const uint32_t bar = smem_u32(full_bar + stage);
-      int live_total = 0;
-      for (int b0 = 0; b0 < boxes; b0 += 32) {
-        const int b = b0 + lane;
-        const int j0 = base + (b / (2 * (D / 64))) * box_rows;
-        const bool live = b < boxes && j0 < k_end && j0 + box_rows > lo && bt[j0 / ps] >= 0;
-        live_total += __popc(__ballot_sync(0xffffffffu, live));
-      }
-      if (lane == 0) mbar_expect_tx(bar, (uint32_t)live_total * box_rows * 128);
-      __syncwarp();
-      for (int b0 = 0; b0 < boxes; b0 += 32) {
-        const int b = b0 + lane;
-        if (b >= boxes) break;
-        const int which = b & 1, h = (b >> 1) % (D / 64), j = b / (2 * (D / 64));
-        const int j0 = base + j * box_rows;
-        if (!(j0 < k_end && j0 + box_rows > lo)) continue;
-        const int page = bt[j0 / ps];
-        if (page < 0) continue;
-        const int y = (page * nkv + kvh) * ps + (j0 % ps);
-        unsigned char* dst = (which ? v_dst : k_dst) + h * (TILE * 128) + j * box_rows * 128;
-        tma_load_2d(smem_u32(dst), which ? &map_v : &map_k, bar, h * 64, y);
-      }
-      return;
-    }
     const int chunk = tid % CHUNKS;
     for (int r0 = (tid / CHUNKS) * 8; r0 < TILE; r0 += ROWS_PER_PASS) {
       const int j0 = base + r0;
@@ -256,7 +207,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + i;
           const bool valid = j >= lo && j < k_end && j != skip;
-          const int off = kv_off<D, false>(r0 + i, chunk);
+          const int off = swz<D>(r0 + i, chunk);
           cp_async16(smem_u32(k_dst + off), kpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
           cp_async16(smem_u32(v_dst + off), vpages + (valid ? src + (long)i * D : 0), valid ? 16 : 0);
         }
@@ -293,7 +244,9 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       const int page = bt[p / ps];
       if (page >= 0) cache_row = (((long)page * nkv + kvh) * ps + (p % ps)) * D;
     }
-    const int pc = p >= nt.max_pos ? nt.max_pos - 1 : p;
+    // a position beyond the tables is reported, not rotated with another position's angles
+    const bool rotate = nt.cos_t && p < nt.max_pos;
+    if (nt.cos_t && !rotate && tid == 0 && error_word) atomicExch(error_word, Q3_ERR_POSITION);
     for (int base = 0; base < items; base += PER_PASS) {
       const int item = base + tid / TPH, c = tid % TPH;
       const bool live = item < items;
@@ -327,17 +280,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
             b[e] = (b[e] * rstd) * wb[e];
           }
         }
-        if (nt.cos_t) {
-          float cs[8], sn[8];
-          load8(nt.cos_t + (long)pc * HALF + 8 * c, cs);
-          load8(nt.sin_t + (long)pc * HALF + 8 * c, sn);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float ya = a[e], yb = b[e];
-            a[e] = ya * cs[e] - yb * sn[e];
-            b[e] = yb * cs[e] + ya * sn[e];
-          }
-        }
+        if (rotate)
+          rotate_chunks(a, b, nt.cos_t + (long)p * HALF, nt.sin_t + (long)p * HALF, c, HALF, nt.pairing);
       }
       if (is_q) {
         store8(reinterpret_cast<bf16*>(q_s + swz<D>(item, c)), a);
@@ -368,11 +312,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
 
   for (int tile = 0; tile < num_tiles; ++tile) {
-    if (TMA) {
-      mbar_wait_report(smem_u32(full_bar + tile % stages), (tile / stages) & 1, error_word, 4);
-    } else {
-      if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
-    }
+    if (stages == 2) cp_async_wait<0>(); else cp_async_wait<1>();
     __syncthreads();
     {
       const int nxt = tile + stages - 1;
@@ -383,27 +323,13 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     unsigned char* v_t = k_t + TILE_BYTES;
     {
       const int base = k_begin + tile * TILE;
-      const bool patch = FUSED && owner && tile == (p - k_begin) / TILE;
-      // page boxes bring whole pages: values of keys outside [lo, k_end) are cleared, since a
-      // probability of zero does not silence a NaN (their scores are masked below)
-      const bool ragged = TMA && (base < lo || base + TILE > k_end);
-      if (patch || ragged) {  // (uniform over the block)
-        if (ragged) {
-          for (int c = tid; c < TILE * CHUNKS; c += THREADS) {
-            const int row = c / CHUNKS, j = base + row;
-            if (j < lo || j >= k_end)
-              *reinterpret_cast<uint4*>(v_t + kv_off<D, TMA>(row, c % CHUNKS)) = make_uint4(0, 0, 0, 0);
-          }
+      if (FUSED && owner && tile == (p - k_begin) / TILE) {  // (uniform over the block)
+        const int r = p - base;
+        for (int c = tid; c < 2 * CHUNKS; c += THREADS) {
+          const int chunk = c % CHUNKS;
+          const uint4 v = *reinterpret_cast<const uint4*>(new_s + (c / CHUNKS) * D * 2 + chunk * 16);
+          *reinterpret_cast<uint4*>((c < CHUNKS ? k_t : v_t) + swz<D>(r, chunk)) = v;
         }
-        if (patch) {
-          const int r = p - base;
-          for (int c = tid; c < 2 * CHUNKS; c += THREADS) {
-            const int chunk = c % CHUNKS;
-            const uint4 v = *reinterpret_cast<const uint4*>(new_s + (c / CHUNKS) * D * 2 + chunk * 16);
-            *reinterpret_cast<uint4*>((c < CHUNKS ? k_t : v_t) + kv_off<D, TMA>(r, chunk)) = v;
-          }
-        }
-        if (TMA) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before the stage is refilled
         __syncthreads();
       }
     }
@@ -417,7 +343,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t kb[4];
       const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-      ldmatrix_x4(kb, smem_u32(k_t + kv_off<D, TMA>(row, 2 * ks + ((lane >> 3) & 1))));
+      ldmatrix_x4(kb, smem_u32(k_t + swz<D>(row, 2 * ks + ((lane >> 3) & 1))));
       mma_bf16(s[0], qa[ks], kb[0], kb[1]);
       mma_bf16(s[1], qa[ks], kb[2], kb[3]);
     }
@@ -468,7 +394,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     for (int i = 0; i < D / 16; ++i) {
       uint32_t vb[4];
       const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-      ldmatrix_x4_trans(vb, smem_u32(v_t + kv_off<D, TMA>(row, 2 * i + (lane >> 4))));
+      ldmatrix_x4_trans(vb, smem_u32(v_t + swz<D>(row, 2 * i + (lane >> 4))));
       mma_bf16(o[2 * i], pa, vb[0], vb[1]);
       mma_bf16(o[2 * i + 1], pa, vb[2], vb[3]);
     }
@@ -476,7 +402,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
 
   // ---- merge the 4 warps ------------------------------------------------------------------
   pdl_launch_dependents();
-  if (!TMA) cp_async_wait<0>();
+  cp_async_wait<0>();
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -544,12 +470,11 @@ decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__
   merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
 }
 
-template <int D, bool FUSED, bool TMA>
+template <int D, bool FUSED>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
-                  int num_splits, const NewToken& nt, long num_rows_kv, int* error_word, int* tickets,
-                  cudaStream_t stream) {
+                  int num_splits, const NewToken& nt, int* error_word, int* tickets, cudaStream_t stream) {
   const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
   const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
@@ -560,20 +485,10 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
   static bool configured_on[Q3_MAX_DEVICES];
   bool& configured = configured_on[q3_current_device()];
   if (!configured) {
-    if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(decode_attention_kernel<D, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return Q3_ERR_LAUNCH;
     configured = true;
-  }
-  CUtensorMap map_k, map_v;
-  memset(&map_k, 0, sizeof map_k);
-  memset(&map_v, 0, sizeof map_v);
-  if (TMA) {
-    const int box_rows = ps < TILE ? ps : TILE;
-    // pages as a matrix [rows of all pages and kv heads][D]; a box is [box_rows][64 dims], swizzled
-    if (!q3_bf16_map(&map_k, kpages, num_rows_kv, D, D, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
-        !q3_bf16_map(&map_v, vpages, num_rows_kv, D, D, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
-      return Q3_ERR_LAUNCH;
   }
   dim3 grid(num_splits, nkv, num_seqs);
   {
@@ -592,9 +507,9 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     cfg.attrs = attr;
     cfg.numAttrs = n;
     const float scale_log2 = scale * 1.4426950408889634f;
-    if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED, TMA>, q, q_stride, kpages, vpages, block_table,
+    if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED>, q, q_stride, kpages, vpages, block_table,
                            max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps, scale_log2,
-                           window, num_splits, stages, nt, map_k, map_v, error_word, tickets) != cudaSuccess)
+                           window, num_splits, stages, nt, error_word, tickets) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   if (num_splits > 1 && !tickets) {
@@ -610,29 +525,19 @@ template <bool FUSED>
 int dispatch_decode(const void* q, int q_stride, const void* kpages, const void* vpages, const int* block_table,
                     int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
                     float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
-                    int window, int num_splits, const NewToken& nt, long num_rows_kv, int* error_word,
-                    int* tickets, cudaStream_t stream) {
+                    int window, int num_splits, const NewToken& nt, int* error_word, int* tickets,
+                    cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
   if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
   if (num_seqs == 0) return Q3_OK;
   if (num_seqs > 65535 || nkv > 65535) return Q3_ERR_UNSUPPORTED;
-  // page boxes: pages of 8, 16, 32 keys or a multiple of 64, all rows addressable with an int
-  const bool tma = num_rows_kv > 0 && num_rows_kv < (1L << 31) && error_word &&
-                   (ps == 8 || ps == 16 || ps == 32 || ps % 64 == 0) &&
-                   (((uintptr_t)kpages | (uintptr_t)vpages) & 15) == 0;
-#define Q3_DECODE_CASE(DIM)                                                                                      \
-  case DIM:                                                                                                      \
-    return tma ? launch_decode<DIM, FUSED, true>((const bf16*)q, q_stride, (const bf16*)kpages,                  \
-                                                 (const bf16*)vpages, block_table, max_pages, kv_lens,           \
-                                                 cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs, nq, \
-                                                 nkv, ps, scale, window, num_splits, nt, num_rows_kv,            \
-                                                 error_word, tickets, stream)                              \
-               : launch_decode<DIM, FUSED, false>((const bf16*)q, q_stride, (const bf16*)kpages,                 \
-                                                  (const bf16*)vpages, block_table, max_pages, kv_lens,          \
-                                                  cu_seqlens, seq_list, (bf16*)out, mid_o, mid_lse, num_seqs,    \
-                                                  nq, nkv, ps, scale, window, num_splits, nt, num_rows_kv,       \
-                                                  error_word, tickets, stream)
+#define Q3_DECODE_CASE(DIM)                                                                                       \
+  case DIM:                                                                                                       \
+    return launch_decode<DIM, FUSED>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages,          \
+                                     block_table, max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o,    \
+                                     mid_lse, num_seqs, nq, nkv, ps, scale, window, num_splits, nt, error_word,   \
+                                     tickets, stream)
   switch (D) {
     Q3_DECODE_CASE(64);
     Q3_DECODE_CASE(128);
@@ -649,10 +554,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
 // kv_lens / cu_seqlens / block_table rows), or sequences 0..num_seqs-1 when it is null.
 // Scratch: mid_o needs num_seqs*nq*num_splits*D floats and mid_lse num_seqs*nq*num_splits
 // floats when num_splits > 1 (both may be null otherwise).  head_dim 64, 128 or 256;
-// group size nq/nkv at most 16; bfloat16 only.  num_rows_kv: rows of D in each of kpages and
-// vpages (pages x kv heads x page size); when it is given (> 0) together with `error_word`
-// (a device int that is set non-zero if a bounded wait expires) and the page size is 8, 16, 32
-// or a multiple of 64, keys and values are fetched as page boxes by TMA, else by 16-byte copies.
+// group size nq/nkv at most 16; bfloat16 only.
 // tickets: null, or num_seqs * nkv ints that are zero before the call (and again after it): with
 // them the slices of a sequence and kv head are merged by whichever of their blocks finishes
 // last, without them by a second kernel; the bits are the same.  Calls that share ticket words
@@ -661,34 +563,35 @@ Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void*
                                         const int* block_table, int max_pages, const int* kv_lens,
                                         const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                         float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
-                                        int window, int num_splits, long num_rows_kv, int* error_word,
-                                        int* tickets, cudaStream_t stream) {
+                                        int window, int num_splits, int* tickets, cudaStream_t stream) {
   return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                 out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
-                                num_rows_kv, error_word, tickets, stream);
+                                nullptr, tickets, stream);
 }
 
 // The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the
 // q/k/v projection (rows of nq + 2*nkv heads); each sequence's newest position is
 // kv_lens[seq] - 1.  q_w / k_w (per-head RMSNorm weights, fp32 [D]) and cos_t / sin_t
-// ([max_pos, D/2], rotation over the whole head) may be null.  The key and value of the newest
-// token are written to their pages; q is not written back.
+// ([max_pos, D/2], rotation over the whole head; `pairing` as in q3_qk_norm_rope_store) may be
+// null.  The key and value of the newest token are written to their pages; q is not written
+// back.  `error_word` (may be null) is set to Q3_ERR_POSITION if a newest position lies beyond
+// the tables; that token is then left unrotated and the result is invalid.
 Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, void* kpages, void* vpages,
                                               const int* block_table, int max_pages, const int* kv_lens,
                                               const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                               float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps,
                                               float scale, int window, int num_splits, const float* q_w,
                                               const float* k_w, float eps, const float* cos_t, const float* sin_t,
-                                              int max_pos, long num_rows_kv, int* error_word, int* tickets,
+                                              int max_pos, int pairing, int* error_word, int* tickets,
                                               cudaStream_t stream) {
-  if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w)) return Q3_ERR_ARGUMENT;
+  if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
                          (uintptr_t)cos_t | (uintptr_t)sin_t;
   if (bits & 15) return Q3_ERR_UNSUPPORTED;
-  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos};
+  NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
   return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
-                               num_rows_kv, error_word, tickets, stream);
+                               error_word, tickets, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -741,7 +644,13 @@ Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, co
                                                  int nq, int nkv, int D, int ps, float scale, int window,
                                                  int num_splits, cudaStream_t stream) {
   g_no_alloc_error[0] = '\0';
-  if (num_seqs < 0 || nq < 1 || D < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
+  if (num_seqs < 0 || nq < 1 || nkv < 1 || nq % nkv || D < 1 || ps < 1 || window < 0 || num_splits < 1) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error,
+             "decode attention without allocation: bad sizes (num_seqs=%d nq=%d nkv=%d D=%d page_size=%d window=%d "
+             "num_splits=%d): counts must be positive, nq a multiple of nkv, the window zero (none) or positive",
+             num_seqs, nq, nkv, D, ps, window, num_splits);
+    return Q3_ERR_ARGUMENT;
+  }
   const long long partials = (long long)num_seqs * nq * num_splits;
   const long long need = partials * ((long long)D + 1);
   if (need > Q3_NO_ALLOC_SCRATCH_FLOATS) {
@@ -758,5 +667,5 @@ Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, co
   float* mid_lse = scratch + partials * D; // [num_seqs, nq, num_splits]
   return q3_paged_attention_decode(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens,
                                    seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window,
-                                   num_splits, 0, nullptr, nullptr, stream);
+                                   num_splits, nullptr, stream);
 }

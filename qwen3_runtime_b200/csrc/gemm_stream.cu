@@ -19,17 +19,12 @@
 // use the same permutation of k.  After a stage the 16 warps' partial tiles are summed
 // through shared memory in warp order.
 //
-// parts > 1: the blocks that share a panel form a thread-block cluster (block rank = range).
-// For unit u the block of rank u % parts leads: the others store their [16 tokens x 8 rows]
-// partial into a slot of the leader's shared memory (st.shared::cluster) and arrive on the
-// slot's mbarrier there; the leader adds the partials in range order and runs the epilogue.
-// A slot is used once, so nobody ever waits for a slot to become free.
-//
-// Partial sums (mode 3): no exchange and no cluster at all.  The block of range p writes
-// its fp32 partial of every unit to out[p][token][feature], and whoever reads the product
-// adds the `parts` planes in order; in a decode step that is the norm kernel that folds the
-// product into the residual sum, which reads a few fp32 rows more and saves the products
-// the wait of every block for its cluster.
+// A finished product (modes 0..2) is made with one range of K (parts = 1): a block owns whole
+// rows of the result and nobody waits for anybody.  K is cut into ranges only for partial sums
+// (mode 3): the block of range p writes its fp32 partial of every unit to
+// out[p][token][feature], and whoever reads the product adds the `parts` planes in order; in a
+// decode step that is the norm kernel that folds the product into the residual sum, which
+// reads a few fp32 rows more and saves the blocks any exchange among themselves.
 //
 // Every mbarrier wait is bounded; on expiry the waiter sets the error word and carries on
 // (the result is then invalid, and the host raises), so no barrier is ever abandoned.
@@ -43,7 +38,6 @@ constexpr int CONSUMER_WARPS = 16;
 constexpr int CONSUMERS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMERS + 32;
 constexpr int MAX_STAGES = 8;
-constexpr int MAX_LED = 16;                // units a block may lead in a cluster (slots are used once)
 constexpr int SMEM_LIMIT = 226 * 1024;     // dynamic; the barriers are static
 constexpr int RED_BYTES = 2 * CONSUMER_WARPS * 4 * 32 * 4;  // two buffers of the warps' tiles
 
@@ -63,7 +57,6 @@ struct Plan {
   int stages;
   int blocks;      // multiple of parts
   int panels;
-  int led;         // slots for the units a block leads (parts > 1)
 };
 
 // k-blocks of 32 per consumer warp: what its registers hold of the tokens' values
@@ -78,11 +71,9 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   constexpr int XB = Blocks<HI>::value;
   constexpr int FPP = MODE == OUT_SWIGLU ? 4 : 8;  // output features per panel
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + MAX_LED];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES];
   const int stage_bytes = ROWS * plan.pitch;
   float* red = reinterpret_cast<float*>(smem + (size_t)plan.stages * stage_bytes);  // [2][warps][4][32]
-  float* slots = red + RED_BYTES / 4;                                                // [led][parts - 1][128]
-  const uint32_t slot_bar0 = smem_addr(bars + 2 * MAX_STAGES);
   const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + MAX_STAGES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int part = blockIdx.x % plan.parts;
@@ -96,7 +87,6 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
     }
-    for (int i = 0; i < plan.led; ++i) mbar_init(slot_bar0 + 8 * i, 128 * (plan.parts - 1));
     mbar_init_fence();
   }
   if (K & 31) {  // the tail of the last k-block is read but never copied: keep it finite
@@ -105,7 +95,6 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
-  if (plan.parts > 1) cluster_sync_all();  // every block of the cluster has its barriers ready
 
   if (warp == CONSUMER_WARPS) {
     // ---- producer: weights do not depend on the kernel before this one, so it starts at once ----
@@ -168,41 +157,12 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       float v = 0.f;
 #pragma unroll
       for (int w = 0; w < CONSUMER_WARPS; ++w) v += rbuf[(w * 4 + e) * 32 + lane];
-      bool emit = true;
-      if (MODE != OUT_PARTIAL && plan.parts > 1) {
-        const int leader = u % plan.parts, li = u / plan.parts;
-        if (part != leader) {
-          const int idx = part < leader ? part : part - 1;
-          const uint32_t dst = map_to_cta(smem_addr(slots + ((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x),
-                                           leader);
-          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(v) : "memory");
-          remote_arrive(map_to_cta(slot_bar0 + 8 * li, leader));
-          emit = false;
-        } else {
-          const uint32_t bar = slot_bar0 + 8 * li;
-          if (!mbar_try_wait_cluster(bar, 0)) {
-            const long long start = clock64();
-            while (!mbar_try_wait_cluster(bar, 0)) {
-              if (clock64() - start > Q3_WAIT_LIMIT_CYCLES) {
-                atomicExch(error_word, 3);
-                break;
-              }
-            }
-          }
-          const float own = v;
-          v = 0.f;
-          for (int p = 0; p < plan.parts; ++p) {
-            const int idx = p < leader ? p : p - 1;
-            v += p == leader ? own : slots[((size_t)li * (plan.parts - 1) + idx) * 128 + threadIdx.x];
-          }
-        }
-      }
       // SwiGLU: rows 0..3 of the panel are gate rows, rows 4..7 the up rows of the same features,
       // held two lanes further on
       const float up = MODE == OUT_SWIGLU ? __shfl_down_sync(0xffffffffu, v, 2) : 0.f;
       const int token = g + 8 * (e >> 1);
       const int feature = panel * FPP + 2 * t + (e & 1);
-      if (emit && token < M && feature < N && (MODE != OUT_SWIGLU || t < 2)) {
+      if (token < M && feature < N && (MODE != OUT_SWIGLU || t < 2)) {
         float r = v;
         if (MODE == OUT_SWIGLU) r = (r / (1.f + expf(-r))) * up;
         if (MODE == OUT_PARTIAL)
@@ -219,21 +179,14 @@ gemm_stream_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   pdl_launch_dependents();
 }
 
-cudaError_t launch_stream(const void* kernel, int blocks, int cluster, size_t smem, cudaStream_t stream, void** args) {
+cudaError_t launch_stream(const void* kernel, int blocks, size_t smem, cudaStream_t stream, void** args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[1];
   int n = 0;
-  if (cluster > 1) {
-    attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = cluster;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = 1;
-    ++n;
-  }
   if (q3_pdl_enabled()) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
@@ -244,57 +197,25 @@ cudaError_t launch_stream(const void* kernel, int blocks, int cluster, size_t sm
   return cudaLaunchKernelExC(&cfg, kernel, args);
 }
 
-// How many clusters of `cluster` blocks (one block per SM, all of its shared memory) the device
-// runs at once; clusters live inside one GPC, so this can be less than SMs / cluster.
-int resident_clusters(const void* kernel, int cluster, int sm_count) {
-  if (cluster == 1) return sm_count;
-  static int cached_on[Q3_MAX_DEVICES][9];
-  int* cached = cached_on[q3_current_device()];
-  if (!cached[cluster]) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(sm_count / cluster * cluster);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM_LIMIT;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
-      cudaGetLastError();
-      n = -1;
-    }
-    cached[cluster] = n;
-  }
-  return cached[cluster];
-}
-
 // Ranges of K: as few as keep a range within what a warp's registers hold and the ring at two
 // stages or more; more only while that shortens the longest block's work (units x (range +
 // a fixed part worth 256 k-values)).
-// exchange: the blocks of a panel form a cluster and sum their partials there; without it
-// every block stands alone and writes its partial.
-bool make_plan(const void* kernel, bool exchange, int N, int K, int features_per_panel, int max_range, int sm_count,
-               Plan* plan) {
+// finished: the product is wanted whole, so K is not cut at all.
+bool make_plan(bool finished, int N, int K, int features_per_panel, int max_range, int sm_count, Plan* plan) {
   const int panels = (N + features_per_panel - 1) / features_per_panel;
   long best_cost = 0;
   plan->parts = 0;
-  for (int parts = 1; parts <= 8; parts *= 2) {
+  for (int parts = 1; parts <= (finished ? 1 : 8); parts *= 2) {
     int range = (K + parts - 1) / parts;
     range = (range + 31) & ~31;
     if (range > max_range) continue;
     if ((long)(parts - 1) * range >= K) continue;  // an empty range
-    const int clusters = exchange ? resident_clusters(kernel, parts, sm_count) : sm_count / parts;
-    if (clusters < 1) continue;
-    const int groups = clusters < panels ? clusters : panels;  // clusters launched
+    const int sets = sm_count / parts;                   // sets of `parts` blocks that share panels
+    if (sets < 1) continue;
+    const int groups = sets < panels ? sets : panels;  // sets launched
     const int units = (panels + groups - 1) / groups;
-    const int led = exchange && parts > 1 ? (units + parts - 1) / parts : 0;
-    if (led > MAX_LED) continue;
     const int pitch = ((range * 2 + 127) & ~127) + 64;
-    int stages = (SMEM_LIMIT - RED_BYTES - led * (parts - 1) * 512) / (8 * pitch);
+    int stages = (SMEM_LIMIT - RED_BYTES) / (8 * pitch);
     if (stages < 2) continue;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     const long cost = (long)units * (range + 256);
@@ -306,7 +227,6 @@ bool make_plan(const void* kernel, bool exchange, int N, int K, int features_per
       plan->stages = stages;
       plan->blocks = groups * parts;
       plan->panels = panels;
-      plan->led = led;
     }
   }
   return plan->parts != 0;
@@ -324,18 +244,16 @@ int launch(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, i
     configured = true;
   }
   Plan plan;
-  if (!make_plan(kernel, MODE != OUT_PARTIAL, N, K, MODE == OUT_SWIGLU ? 4 : 8,
+  if (!make_plan(MODE != OUT_PARTIAL, N, K, MODE == OUT_SWIGLU ? 4 : 8,
                  CONSUMER_WARPS * 32 * Blocks<HI>::value, sm_count, &plan))
     return Q3_ERR_UNSUPPORTED;
   if (MODE == OUT_PARTIAL && plan.parts != planes) return Q3_ERR_ARGUMENT;
   // A block owns its SM, so kernels do not overlap at their ends: short products (few units
-  // per block) and products that need the exchange between blocks are faster on the kernel
-  // that streams through registers.
-  if (MODE != OUT_PARTIAL && only_large && (plan.parts > 1 || plan.panels < 8 * plan.blocks))
-    return Q3_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)plan.stages * 8 * plan.pitch + RED_BYTES + (size_t)plan.led * (plan.parts - 1) * 512;
+  // per block) are faster on the kernel that streams through registers.
+  if (MODE != OUT_PARTIAL && only_large && plan.panels < 8 * plan.blocks) return Q3_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)plan.stages * 8 * plan.pitch + RED_BYTES;
   void* args[] = {&x, &ldx, &W, &ldw, &out, &ldo, &M, &N, &K, &up_offset, &plan, &error_word};
-  return launch_stream(kernel, plan.blocks, MODE == OUT_PARTIAL ? 1 : plan.parts, smem, stream, args) == cudaSuccess
+  return launch_stream(kernel, plan.blocks, smem, stream, args) == cudaSuccess
              ? Q3_OK
              : Q3_ERR_LAUNCH;
 }
@@ -386,7 +304,7 @@ Q3_EXPORT int q3_gemm_stream_parts(int M, int N, int K) {
   if (N < 1 || K < 1 || M < 1 || M > 16 || K % 8) return 0;
   const int sms = sm_count_of_current_device();
   Plan plan;
-  if (!sms || !make_plan(nullptr, false, N, K, 8, CONSUMER_WARPS * 32 * Blocks<true>::value, sms, &plan)) return 0;
+  if (!sms || !make_plan(false, N, K, 8, CONSUMER_WARPS * 32 * Blocks<true>::value, sms, &plan)) return 0;
   return plan.parts;
 }
 

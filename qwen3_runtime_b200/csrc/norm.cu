@@ -246,3 +246,44 @@ Q3_EXPORT int q3_silu_mul(int dtype, const void* gu, void* out, int num_rows, in
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();
 }
+
+// ---- small epilogues that an architecture may ask for (Qwen3 dense uses neither) ---------------------
+// out[r][c] += bias[c]: the bias of a projection, added in fp32 to the product's rounded value.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, long ld, const float* __restrict__ bias, long total, int N) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long r = idx / N;
+  const int c = (int)(idx - r * N);
+  out[r * ld + c] = from_f32<T>(to_f32(out[r * ld + c]) + bias[c]);
+}
+
+Q3_EXPORT int q3_add_bias(int dtype, void* out, long ld, const float* bias, int num_rows, int N, cudaStream_t stream) {
+  if (!out || !bias || N < 1 || ld < N) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * N;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == Q3_DTYPE_F32)
+    add_bias_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, ld, bias, total, N);
+  else if (dtype == Q3_DTYPE_BF16)
+    add_bias_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)out, ld, bias, total, N);
+  else
+    return Q3_ERR_ARGUMENT;
+  return q3_launch_status();
+}
+
+// logits = logits * scale, then (cap > 0) cap * tanh(logits / cap), in place on fp32 logits.
+__global__ void logit_scale_cap_kernel(float* __restrict__ logits, long total, float scale, float cap) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float v = logits[idx] * scale;
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  logits[idx] = v;
+}
+
+Q3_EXPORT int q3_logit_scale_cap(float* logits, long total, float scale, float cap, cudaStream_t stream) {
+  if (!logits || total < 0 || cap < 0.f) return Q3_ERR_ARGUMENT;
+  if (total == 0) return Q3_OK;
+  logit_scale_cap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(logits, total, scale, cap);
+  return q3_launch_status();
+}

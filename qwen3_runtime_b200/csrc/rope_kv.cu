@@ -3,12 +3,21 @@
 //
 // One warp handles one (token, head).  For a q or k head (models/qwen3.py:101-103):
 //   y = (x * rsqrt(mean(x^2) + eps)) * w          over the head's D values, fp32
-//   rotate-half on the first 2*rot_half dims with cos/sin[position] (layers/rope.py:7-11)
+//   rotation of the first 2*rot_half dims by cos/sin[position][i]; which two elements form
+//   pair i is the position part's choice: `pairing` 0 = halves, (i, i + rot_half)
+//   (layers/rope.py:7-11, what Qwen3 uses); 1 = interleaved, (2i, 2i + 1)
 // q is written back in place (the attention kernels read it from the QKV buffer);
 // k goes to its slot of the key pages; v heads are copied to the value pages
 // unchanged (kv/paged.py:74-84).  Slot of position p: page = block_table[seq][p / ps],
 // row p % ps.  Page layout [pages, kv_heads, page_size, D].
+//
+// A position outside the rotation tables (p < 0 or p >= max_pos) is never rotated with another
+// position's angles: the (token, head) is left untouched and `error_word` (if given) is set to
+// Q3_ERR_POSITION, which the host reads with the step's other error reports.
 #include "common.cuh"
+#include "rotary.cuh"
+
+#define Q3_ERR_POSITION 16
 
 template <typename T, int WARPS>
 __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, int nq, int nkv, int D,
@@ -18,7 +27,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
                                           const int* __restrict__ positions, const int* __restrict__ token_seq,
                                           const int* __restrict__ block_table, int max_pages,
                                           T* __restrict__ kpages, T* __restrict__ vpages, int ps,
-                                          int num_tokens, int write_kv) {
+                                          int num_tokens, int write_kv, int pairing, int* __restrict__ error_word) {
   extern __shared__ float stage[];  // WARPS * D
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = write_kv ? nq + 2 * nkv : nq;
@@ -27,7 +36,11 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   const int t = (int)(item / heads);
   const int hi = (int)(item - (long)t * heads);
   T* x = qkv + (long)t * row_stride + (long)hi * D;
-  int p = positions[t];
+  const int p = positions[t];
+  if (cos_t && hi < nq + nkv && (p < 0 || p >= max_pos)) {
+    if (error_word && lane == 0) atomicExch(error_word, Q3_ERR_POSITION);
+    return;
+  }
   long cache_row = 0;
   if (hi >= nq) {
     const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
@@ -51,17 +64,17 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   const float* w = hi < nq ? q_w : k_w;
   const float rstd = w ? rsqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
   __syncwarp();
-  if (p >= max_pos) p = max_pos - 1;
   const float* cs = cos_t ? cos_t + (long)p * rot_half : nullptr;
   const float* sn = cos_t ? sin_t + (long)p * rot_half : nullptr;
   T* dst = hi < nq ? x : kpages + cache_row;
   for (int d = lane; d < D; d += 32) {
     float y = w ? (xs[d] * rstd) * w[d] : xs[d];
     if (cs && d < 2 * rot_half) {
-      const int i = d < rot_half ? d : d - rot_half;
-      const int pd = d < rot_half ? d + rot_half : d - rot_half;
+      const bool first = pairing ? (d & 1) == 0 : d < rot_half;  // the pair's first element
+      const int i = pairing ? d >> 1 : (first ? d : d - rot_half);
+      const int pd = pairing ? d ^ 1 : (first ? d + rot_half : d - rot_half);
       const float yp = w ? (xs[pd] * rstd) * w[pd] : xs[pd];
-      y = d < rot_half ? y * cs[i] - yp * sn[i] : y * cs[i] + yp * sn[i];
+      y = first ? y * cs[i] - yp * sn[i] : y * cs[i] + yp * sn[i];
     }
     dst[d] = from_f32<T>(y);
   }
@@ -69,7 +82,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
 
 // The same with 16-byte accesses, for head sizes 16, 32, 64, 128, 256 with the rotation over
 // the whole head (or none): D/16 threads per (token, head); a thread owns elements
-// [8c, 8c+8) and their rotation partners [8c + D/2, 8c + D/2 + 8).
+// [8c, 8c+8) and [8c + D/2, 8c + D/2 + 8): with the halves pairing each element's partner is in
+// the other chunk, with the interleaved pairing it is its neighbour in the same chunk.
 template <typename T>
 __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_stride, int nq, int nkv, int D,
                                               const float* __restrict__ q_w, const float* __restrict__ k_w,
@@ -79,7 +93,8 @@ __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_strid
                                               const int* __restrict__ token_seq,
                                               const int* __restrict__ block_table, int max_pages,
                                               T* __restrict__ kpages, T* __restrict__ vpages, int ps,
-                                              int num_tokens, int write_kv) {
+                                              int num_tokens, int write_kv, int pairing,
+                                              int* __restrict__ error_word) {
   const int tph = D / 16;  // threads per head: a power of two, at most 16
   const int heads = write_kv ? nq + 2 * nkv : nq;
   pdl_wait();
@@ -92,7 +107,7 @@ __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_strid
   const int hi = live ? (int)(item - (long)t * heads) : 0;
   const int half = D / 2;
   T* x = qkv + (long)t * row_stride + (long)hi * D;
-  int p = positions[t];
+  const int p = positions[t];
   long cache_row = -1;
   if (live && hi >= nq && p >= 0 && p / ps < max_pages) {
     const int kvh = hi < nq + nkv ? hi - nq : hi - nq - nkv;
@@ -133,16 +148,11 @@ __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_strid
     }
   }
   if (cos_t) {
-    if (p >= max_pos) p = max_pos - 1;
-    float cs[8], sn[8];
-    load8(cos_t + (long)p * half + 8 * c, cs);
-    load8(sin_t + (long)p * half + 8 * c, sn);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float ya = a[e], yb = b[e];
-      a[e] = ya * cs[e] - yb * sn[e];
-      b[e] = yb * cs[e] + ya * sn[e];
+    if (p < 0 || p >= max_pos) {
+      if (error_word && c == 0) atomicExch(error_word, Q3_ERR_POSITION);
+      return;
     }
+    rotate_chunks(a, b, cos_t + (long)p * half, sin_t + (long)p * half, c, half, pairing);
   }
   if (hi < nq) {
     store8(x + 8 * c, a);
@@ -159,8 +169,10 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
                                     const float* q_w, const float* k_w, float eps, const float* cos_t,
                                     const float* sin_t, int rot_half, int max_pos, const int* positions,
                                     const int* token_seq, const int* block_table, int max_pages, void* kpages,
-                                    void* vpages, int ps, int num_tokens, int write_kv, cudaStream_t stream) {
-  if (!qkv || !positions || nq < 1 || nkv < 1 || D < 1) return Q3_ERR_ARGUMENT;
+                                    void* vpages, int ps, int num_tokens, int write_kv, int pairing,
+                                    int* error_word, cudaStream_t stream) {
+  if (!qkv || !positions || nq < 1 || nkv < 1 || D < 1 || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
+  if (cos_t && max_pos < 1) return Q3_ERR_ARGUMENT;
   if (write_kv && (!token_seq || !block_table || !kpages || !vpages || ps < 1)) return Q3_ERR_ARGUMENT;
   if (cos_t && (!sin_t || rot_half < 1 || 2 * rot_half > D)) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
@@ -176,11 +188,13 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
     if (dtype == Q3_DTYPE_F32)
       err = launch_pdl(qk_norm_rope_store_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (float*)qkv,
                        row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-                       block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+                       block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv, pairing,
+                       error_word);
     else if (dtype == Q3_DTYPE_BF16)
       err = launch_pdl(qk_norm_rope_store_vec_kernel<bf16>, dim3(vblocks), dim3(256), 0, stream, (bf16*)qkv,
                        row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-                       block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+                       block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv, pairing,
+                       error_word);
     else
       return Q3_ERR_ARGUMENT;
     return err == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
@@ -193,11 +207,13 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
   if (dtype == Q3_DTYPE_F32)
     qk_norm_rope_store_kernel<float, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (float*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, rot_half, max_pos, positions,
-        token_seq, block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv);
+        token_seq, block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv, pairing,
+                       error_word);
   else if (dtype == Q3_DTYPE_BF16)
     qk_norm_rope_store_kernel<bf16, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (bf16*)qkv, row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, rot_half, max_pos, positions,
-        token_seq, block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv);
+        token_seq, block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv, pairing,
+                       error_word);
   else
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();

@@ -50,11 +50,13 @@ _SIGNATURES = {
         "q3_fused_norm": [c_int, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "q3_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "q3_add_bias": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
+        "q3_logit_scale_cap": [c_void_p, c_long, c_float, c_float, c_void_p],
     },
     "rope_kv": {
         "q3_qk_norm_rope_store": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                                   c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                  c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "q3_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
     "attention_generic": {
@@ -65,11 +67,11 @@ _SIGNATURES = {
     "attention_decode": {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_float, c_int, c_int, c_long, c_void_p, c_void_p, c_void_p],
+                                      c_float, c_int, c_int, c_void_p, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
-                                            c_void_p, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p],
+                                            c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -153,12 +155,6 @@ class CudaOps:
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         self.tcgen05_pairs = True           # False: the tcgen05 product never pairs SMs (cta_group::1 only)
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
-        # A variant of the split-KV kernel that is correct and tested but measured slower inside a
-        # whole decode step on a B200 (batch 8, context 4096: 3.36 ms against 3.19 ms), so off:
-        self.decode_page_boxes = False      # True: keys and values as TMA page boxes instead of 16-byte copies
-        # True: the slices of a sequence and kv head are merged by whichever of their blocks finishes
-        # last (a ticket word per pair); False: by a second kernel.  The bits are the same.
-        self.decode_merge_by_last_block = True
         self._tickets: torch.Tensor | None = None
         self._argmax_tickets: torch.Tensor | None = None
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
@@ -271,6 +267,23 @@ class CudaOps:
                   _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)), vocab)
         return out
 
+    def add_bias(self, out, bias):
+        """``out[r] += bias`` in place (``bias`` float32): the bias of a projection."""
+        N = out.shape[-1]
+        if bias.dtype != torch.float32 or bias.numel() != N or out.stride(-1) != 1:
+            raise KernelError("add_bias: a float32 bias of the output's width, rows dense")
+        self._call("norm", "q3_add_bias", "add_bias", _dtype_code(out.dtype), _ptr(out), out.stride(0), _ptr(bias),
+                   out.shape[0], N)
+        return out
+
+    def logit_scale_cap(self, logits, scale=1.0, cap=0.0):
+        """``logits *= scale`` and, with ``cap > 0``, ``cap * tanh(logits / cap)``, in place (float32)."""
+        if logits.dtype != torch.float32 or not logits.is_contiguous():
+            raise KernelError("logit_scale_cap: contiguous float32 logits")
+        self._call("norm", "q3_logit_scale_cap", "logit_scale_cap", _ptr(logits), logits.numel(), float(scale),
+                   float(cap))
+        return logits
+
     def silu_mul(self, gate_up, out):
         I = out.shape[-1]
         if self.timing is not None:
@@ -288,8 +301,14 @@ class CudaOps:
                    _ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half)
         return cos, sin
 
+    PAIRINGS = {"half": 0, "interleaved": 1}
+
     def qk_norm_rope_store(self, qkv, *, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
-                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv,
+                           pairing="half"):
+        """Per-head q/k norm, rotation by ``cos/sin[position]`` and the write of k and v into their
+        pages (csrc/rope_kv.cu).  ``pairing`` says which two elements of a head rotation pair i
+        is made of: ``"half"`` (i, i + rotary_dim/2) or ``"interleaved"`` (2i, 2i + 1)."""
         T = qkv.shape[0]
         rot_half = cos.shape[1] if cos is not None else 0
         max_pos = cos.shape[0] if cos is not None else 0
@@ -302,7 +321,7 @@ class CudaOps:
                    _dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads, head_dim,
                   _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
                   _ptr(positions), _ptr(token_seq), _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages),
-                  page_size, T, int(bool(write_kv)))
+                  page_size, T, int(bool(write_kv)), self.PAIRINGS[pairing], _ptr(self._error_word(qkv.device)))
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
@@ -425,11 +444,14 @@ class CudaOps:
 
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
-                               max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None):
+                               max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None,
+                               merge_kernel=False):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
-        ``new_token`` (q_weight, k_weight, eps, cos, sin): ``q`` is the raw q/k/v projection and
-        the kernel also does the work of :meth:`qk_norm_rope_store` for the newest position of
-        each sequence, ``kv_lens - 1``."""
+        ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing): ``q`` is the raw q/k/v
+        projection and the kernel also does the work of :meth:`qk_norm_rope_store` for the newest
+        position of each sequence, ``kv_lens - 1``.  The slices of a sequence and kv head are merged
+        by whichever of their blocks finishes last (a ticket word per pair); ``merge_kernel=True``
+        asks for the second kernel that callers without ticket words get (the bits are the same)."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
         if window:
@@ -440,14 +462,12 @@ class CudaOps:
         if splits > 1:
             mid_o = torch.empty((num_seqs, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
             mid_lse = torch.empty((num_seqs, num_heads, splits), dtype=torch.float32, device=out.device)
-            if self.decode_merge_by_last_block and num_seqs * num_kv_heads <= self.TICKETS:
+            if not merge_kernel and num_seqs * num_kv_heads <= self.TICKETS:
                 if self._tickets is None:  # zero between launches: the kernel leaves them so
                     self._tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=out.device)
                 tickets = self._tickets
             else:
                 self.launches += 1  # the merge kernel
-        # rows of head_dim in the page tensors: lets the kernel fetch page boxes by TMA
-        kv_rows = k_pages.shape[0] * num_kv_heads * page_size if self.decode_page_boxes else 0
         err = _ptr(self._error_word(out.device))
         if self.timing is not None and step is not None:
             self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out, prompts=False))
@@ -458,17 +478,25 @@ class CudaOps:
                        _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                        num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
                        splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
-                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0, kv_rows, err, _ptr(tickets))
+                       _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
+                       self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets))
             return out
         self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                    num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
-                   kv_rows, err, _ptr(tickets))
+                   _ptr(tickets))
         return out
 
     # ---- matrix products ----------------------------------------------------------------
-    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False):
+    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False, bias=None):
+        """See :meth:`_product`; ``bias`` (float32 ``[N]``) is added to the finished product, which
+        then never comes as partial sums."""
+        if bias is None:
+            return self._product(x, weight, out, out_dtype, partial_sums)
+        return self.add_bias(self._product(x, weight, out, out_dtype, False), bias)
+
+    def _product(self, x, weight, out=None, out_dtype=None, partial_sums=False):
         """``x[M, K] @ weight[N, K]^T``.  float32: this engine's FMA kernel (no TF32).
         bfloat16, at most 16 tokens: one of this engine's two weight-streaming kernels
         (:meth:`_small_product`).  bfloat16, more tokens: the library product with fp32
@@ -571,6 +599,8 @@ class CudaOps:
                 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
+    ERR_POSITION = 16  # csrc/rope_kv.cu, csrc/attention_decode.cu: a position outside the rotation tables
+
     def _error_word(self, device) -> torch.Tensor:
         if getattr(self, "_err", None) is None:
             self._err = torch.zeros(1, dtype=torch.int32, device=device)
@@ -580,7 +610,12 @@ class CudaOps:
         """A bounded wait inside a kernel expired (it gave up and returned).  Reads one int from
         the device, so call it where the host waits for the device anyway."""
         err = getattr(self, "_err", None)
-        if err is not None and int(err.item()) != 0:
+        code = int(err.item()) if err is not None else 0
+        if code == self.ERR_POSITION:
+            err.zero_()
+            raise KernelError("a token's position lies outside the rotation tables of the position encoding: "
+                              "its query and key were left unrotated and the step's output is invalid")
+        if code != 0:
             err.zero_()
             if self._tickets is not None:  # a kernel that gave up may have left tickets drawn
                 self._tickets.zero_()

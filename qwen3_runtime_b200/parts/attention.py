@@ -36,8 +36,13 @@ class PagedAttention(Part):
                 f"head_dim={self.head_dim} is not supported: the attention kernels take multiples of 16 up to 256")
         pos_spec = spec.get("position") or PartSpec("none")
         self.position = build_part("position", pos_spec, ctx)
-        if self.position.style not in ("none", "neox"):
+        if self.position.style not in ("none", "rotary"):
             raise ValueError(f"the fused q/k kernel has no {self.position.style!r} position encoding")
+        self.pairing = getattr(self.position, "pairing", "half")
+        if self.pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotation pairs are 'half' or 'interleaved', not {self.pairing!r}")
+        self.qkv_bias = bool(spec.get("qkv_bias", False))
+        self.o_bias = bool(spec.get("o_bias", False))
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
         self.qkv_weight = self.o_weight = self.q_norm_weight = self.k_norm_weight = None
@@ -52,6 +57,12 @@ class PagedAttention(Part):
         if self.qk_norm_eps is not None:
             specs["q_norm.weight"] = ParamSpec((self.head_dim,), "vector")
             specs["k_norm.weight"] = ParamSpec((self.head_dim,), "vector")
+        if self.qkv_bias:
+            specs["q_proj.bias"] = ParamSpec((self.q_size,), "vector")
+            specs["k_proj.bias"] = ParamSpec((self.kv_size,), "vector")
+            specs["v_proj.bias"] = ParamSpec((self.kv_size,), "vector")
+        if self.o_bias:
+            specs["o_proj.bias"] = ParamSpec((self.hidden_size,), "vector")
         return specs
 
     def load(self, tensors):
@@ -61,6 +72,9 @@ class PagedAttention(Part):
         self.o_weight = tensors["o_proj.weight"].contiguous()
         self.q_norm_weight = tensors.get("q_norm.weight")
         self.k_norm_weight = tensors.get("k_norm.weight")
+        self.qkv_bias_vec = (torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]])
+                             if self.qkv_bias else None)
+        self.o_bias_vec = tensors.get("o_proj.bias")
 
     def kernel_groups(self):
         groups = ["rope_kv", "attention_generic", *self.position.kernel_groups()]
@@ -80,7 +94,10 @@ class PagedAttention(Part):
         ops = self.ops
         T = h.shape[0]
         weight = self.qkv_weight if cache.writes else self.qkv_weight[: self.q_size]
-        qkv = ops.linear(h, weight)
+        if self.qkv_bias_vec is None:
+            qkv = ops.linear(h, weight)
+        else:
+            qkv = ops.linear(h, weight, bias=self.qkv_bias_vec[: weight.shape[0]])
         tables = self.position.rotation_tables()
         cos, sin = tables if tables is not None else (None, None)
         block_table = step.block_tables[cache.paged_index]
@@ -98,20 +115,28 @@ class PagedAttention(Part):
                 kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens, out=ctx_out, page_size=cache.page_size,
                 scale=self.scale, window=self.window, num_seqs=step.num_seqs,
                 max_kv_len=width * cache.page_size or step.max_kv_len,
-                new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin))
-            return ops.linear(ctx_out, self.o_weight, partial_sums=self.partial_sums_ok)
+                new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin,
+                               pairing=self.pairing),
+                step=step)
+            return self._project_out(ctx_out)
         ops.qk_norm_rope_store(
             qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
             eps=eps, cos=cos, sin=sin,
             positions=step.positions, token_seq=step.token_seq, block_table=block_table,
-            k_pages=cache.k_pages, v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes)
+            k_pages=cache.k_pages, v_pages=cache.v_pages, page_size=cache.page_size, write_kv=cache.writes,
+            pairing=self.pairing)
         ops.paged_attention(
             qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
             head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,
             token_seq=step.token_seq, positions=step.positions, out=ctx_out, page_size=cache.page_size,
             scale=self.scale, window=self.window, step=step)
-        return ops.linear(ctx_out, self.o_weight, partial_sums=self.partial_sums_ok)
+        return self._project_out(ctx_out)
+
+    def _project_out(self, ctx_out: torch.Tensor) -> torch.Tensor:
+        if self.o_bias_vec is not None:
+            return self.ops.linear(ctx_out, self.o_weight, bias=self.o_bias_vec)
+        return self.ops.linear(ctx_out, self.o_weight, partial_sums=self.partial_sums_ok)
 
 
 register_part("mixer", "paged_attention", PagedAttention)

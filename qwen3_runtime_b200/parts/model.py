@@ -105,4 +105,7 @@ class DecoderModel:
         if step.num_logit_rows == 0:
             return None
         h = self.final_norm.add_norm(stream, rows=step.logit_rows, num_rows=step.num_logit_rows)
-        return self.ops.linear(h, self.head, out_dtype=torch.float32)
+        logits = self.ops.linear(h, self.head, out_dtype=torch.float32)
+        if s.logit_scale != 1.0 or s.logit_softcap is not None:
+            self.ops.logit_scale_cap(logits, s.logit_scale, s.logit_softcap or 0.0)
+        return logits

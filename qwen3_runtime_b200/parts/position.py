@@ -2,8 +2,18 @@
 (qwen3_runtime/layers/rope.py:7-27).  ``none``: no position encoding.
 
 A position part does not run a kernel of its own: the mixer applies it inside its
-fused q/k kernel and asks the part for what that kernel needs
-(:meth:`rotation_tables`, :attr:`style`).
+fused q/k kernel and asks the part for what that kernel needs.  The interface is
+
+* ``style``: ``"none"`` or ``"rotary"``;
+* for ``"rotary"``: :meth:`rotation_tables` -> ``(cos, sin)``, float32 ``[positions, pairs]``
+  with the angle of rotation pair ``i`` at position ``p`` in ``[p, i]``; and ``pairing``, which
+  two elements of a head pair ``i`` is: ``"half"`` -- ``(i, i + pairs)`` -- or
+  ``"interleaved"`` -- ``(2i, 2i + 1)``.  ``2 * pairs`` may be less than the head size
+  (partial rotary: the rest of the head is left as it is).
+
+Any encoding that rotates pairs of elements by angles that depend on the absolute position
+only (other frequency schedules, scaled or slowed positions, partial rotation, either
+pairing) is such a part and needs no kernel change.
 """
 
 from __future__ import annotations
@@ -23,7 +33,8 @@ class NoPosition(Part):
 
 class RotaryNeox(Part):
     category = "position"
-    style = "neox"
+    style = "rotary"
+    pairing = "half"
 
     def __init__(self, spec, ctx: BuildContext):
         super().__init__(spec, ctx)

@@ -52,7 +52,8 @@ class TorchOps:
         return ang.cos(), ang.sin()
 
     def qk_norm_rope_store(self, qkv, *, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
-                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv):
+                           positions, token_seq, block_table, k_pages, v_pages, page_size, write_kv,
+                           pairing="half"):
         T = qkv.shape[0]
         D = head_dim
         pos = positions.long()
@@ -63,8 +64,14 @@ class TorchOps:
             if cos is not None:
                 half = cos.shape[1]
                 c, s = cos[pos][:, None, :], sin[pos][:, None, :]
-                x1, x2, rest = x[..., :half], x[..., half:2 * half], x[..., 2 * half:]
-                x = torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
+                rest = x[..., 2 * half:]
+                if pairing == "interleaved":  # pair i = elements (2i, 2i + 1)
+                    x1, x2 = x[..., 0:2 * half:2], x[..., 1:2 * half:2]
+                    rot = torch.stack((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1).flatten(-2)
+                    x = torch.cat((rot, rest), dim=-1)
+                else:  # pair i = elements (i, i + half)
+                    x1, x2 = x[..., :half], x[..., half:2 * half]
+                    x = torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
             return x
 
         nq, nkv = num_heads, num_kv_heads
@@ -106,7 +113,18 @@ class TorchOps:
     # ---- matrix products ----------------------------------------------------------------
     partial_parts = 0  # > 1: linear(partial_sums=True) answers with that many planes
 
-    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False):
+    def add_bias(self, out, bias):
+        out.copy_((out.float() + bias.float()).to(out.dtype))
+        return out
+
+    def logit_scale_cap(self, logits, scale=1.0, cap=0.0):
+        v = logits * scale
+        logits.copy_(cap * torch.tanh(v / cap) if cap > 0 else v)
+        return logits
+
+    def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False, bias=None):
+        if bias is not None:
+            return self.add_bias(self.linear(x, weight, out, out_dtype), bias)
         if partial_sums and self.partial_parts > 1 and out is None and out_dtype is None:
             cuts = torch.linspace(0, x.shape[1], self.partial_parts + 1).long().tolist()
             return torch.stack([x[:, a:b].float() @ weight[:, a:b].float().t() for a, b in zip(cuts, cuts[1:])])

@@ -560,12 +560,17 @@ class SlowedRotary(Part):
     its own tables; nothing else in the framework knows about it."""
 
     category = "position"
-    style = "neox"
+    style = "rotary"
+    pairing = "half"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.dim, self.theta = int(spec["rotary_dim"]), float(spec["theta"])
         self.rate, self.max_positions = float(spec["rate"]), int(spec["max_positions"])
+        self.pairing = spec.get("pairing", "half")
+
+    def position_limit(self):
+        return self.max_positions
 
     def kernel_groups(self):
         return ["rope_kv"]
@@ -602,5 +607,70 @@ def case_toy_position_encoding(dtype, ops, device):
         scale = max(1.0, float(want.abs().max()))
         assert float((got - want).abs().max()) <= (3e-5 if dtype == "float32" else 0.03) * scale
         assert float((want - ordinary).abs().max()) > 1e-2, "the encoding has to matter for the test to mean anything"
+    finally:
+        unregister_part("position", "toy_slowed_rotary")
+
+
+def case_interleaved_pairs_biases_and_capped_logits(dtype, ops, device):
+    """Three seams as parameters, with toy parts: a position encoding that rotates neighbouring
+    elements (2i, 2i + 1) instead of halves; projections with biases (q/k/v, o, down); a head
+    whose logits are scaled and soft-capped.  Whole prompt, cut into portions, and decoded token
+    by token (the decode kernel makes the newest token's q and k itself, with the same pairing)
+    against plain arithmetic written out here."""
+    cfg = TINY["D"]["config"]  # head size 64: bfloat16 decode steps take the fused split-KV kernel
+    base = qwen3_spec(cfg)
+    register_part("position", "toy_slowed_rotary", SlowedRotary)
+    try:
+        toy = PartSpec("toy_slowed_rotary", dict(rotary_dim=cfg.head_dim, theta=cfg.rope_theta, rate=1.0,
+                                                 max_positions=cfg.max_position_embeddings, pairing="interleaved"))
+        blocks = tuple(PartSpec("pre_norm", {
+            **b.params,
+            "mixer": PartSpec("paged_attention", {**b["mixer"].params, "position": toy, "qkv_bias": True, "o_bias": True}),
+            "feed_forward": PartSpec("gated_mlp", {**b["feed_forward"].params, "down_bias": True})}) for b in base.blocks)
+        spec = ModelSpec(base.vocab_size, base.hidden_size, blocks, base.order, base.final_norm, True,
+                         logit_scale=0.5, logit_softcap=3.0)
+        model, tensors = _toy_model(spec, cfg, dtype, ops, device)
+        assert "model.layers.0.self_attn.q_proj.bias" in tensors and "model.layers.1.mlp.down_proj.bias" in tensors
+        assert model.position_limit() == cfg.max_position_embeddings
+        # the biases drawn by _toy_model are "vectors" around 1: make them ordinary small offsets
+        for name in [n for n in tensors if n.endswith(".bias")]:
+            tensors[name] = (tensors[name].float() - 1.0).to(torch.bfloat16)
+        load_into(model, DictSource(tensors))
+        ids = random_ids(cfg.vocab_size, 40, 43)
+        whole, _ = _run_cut(model, cfg, ids, page_size=16, cuts=(40,))
+        cut, _ = _run_cut(model, cfg, ids, page_size=16, cuts=(5, 2, 9, 1, 1, 1, 1, 30))
+        act = torch.bfloat16 if dtype == "bfloat16" else None
+        r = lambda x: pm._round(x, act)  # noqa: E731
+        wf = {k: v.float() for k, v in tensors.items()}
+        nq, nkv, D, eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps
+        T = len(ids)
+        cos, sin = pm.rope_tables(D, cfg.rope_theta, torch.arange(T))
+
+        def rotate_neighbours(x):  # x [T, heads, D]: pair i = (2i, 2i + 1)
+            x1, x2 = x[..., 0::2], x[..., 1::2]
+            c, s = cos[:, None, :], sin[:, None, :]
+            return torch.stack((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1).flatten(-2)
+
+        h = wf["model.embed_tokens.weight"][torch.as_tensor(ids)]
+        for layer in range(cfg.num_hidden_layers):
+            p = f"model.layers.{layer}."
+            n = r(pm.rmsnorm(h, wf[p + "input_layernorm.weight"], eps))
+            proj = lambda name: r(r(n @ wf[p + f"self_attn.{name}.weight"].T) + wf[p + f"self_attn.{name}.bias"])  # noqa: E731
+            q, k, v = proj("q_proj").view(T, nq, D), proj("k_proj").view(T, nkv, D), proj("v_proj").view(T, nkv, D)
+            q = r(rotate_neighbours(pm.rmsnorm(q, wf[p + "self_attn.q_norm.weight"], eps)))
+            k = r(rotate_neighbours(pm.rmsnorm(k, wf[p + "self_attn.k_norm.weight"], eps)))
+            ctx_ = r(pm.causal_attention(q, k, v, act_dtype=act))
+            h = h + r(r(ctx_ @ wf[p + "self_attn.o_proj.weight"].T) + wf[p + "self_attn.o_proj.bias"])
+            n = r(pm.rmsnorm(h, wf[p + "post_attention_layernorm.weight"], eps))
+            g, u = n @ wf[p + "mlp.gate_proj.weight"].T, n @ wf[p + "mlp.up_proj.weight"].T
+            if act is not None:
+                g, u = r(g), r(u)
+            m = r(g * torch.sigmoid(g) * u)
+            h = h + r(r(m @ wf[p + "mlp.down_proj.weight"].T) + wf[p + "mlp.down_proj.bias"])
+        logits = r(pm.rmsnorm(h, wf["model.norm.weight"], eps)) @ wf["model.embed_tokens.weight"].T
+        want = 3.0 * torch.tanh(0.5 * logits / 3.0)
+        tol = 3e-5 if dtype == "float32" else 0.03 * max(1.0, float(want.abs().max()))
+        assert float((whole - want).abs().max()) <= tol and float((cut - want).abs().max()) <= tol
+        assert float(want.abs().max()) < 3.0 and float((want - 0.5 * logits).abs().max()) > 1e-3, "the cap has to bite"
     finally:
         unregister_part("position", "toy_slowed_rotary")

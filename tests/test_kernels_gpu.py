@@ -96,10 +96,12 @@ def make_cache(num_pages, nkv, ps, D, dtype, seed):
     return k, v
 
 
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,D,ps,rot,write", [(32, 8, 128, 16, 128, True), (6, 3, 48, 7, 48, True),
-                                                    (5, 5, 80, 1, 32, True), (4, 1, 16, 32, 16, False)])
-def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write):
+                                                    (5, 5, 80, 1, 32, True), (4, 1, 16, 32, 16, False),
+                                                    (3, 1, 64, 8, 64, True), (2, 2, 256, 4, 256, True)])
+def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write, pairing):
     T, B = 37, 3
     maxp = (21 + T) // ps + 1  # every position below has a page in the table
     g = torch.Generator().manual_seed(7)
@@ -124,7 +126,7 @@ def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write):
         k, v = make_cache(B * maxp, nkv, ps, D, dtype, 9)
         impl.qk_norm_rope_store(x, num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=qw, k_weight=kw, eps=1e-6,
                                 cos=cos, sin=sin, positions=pos.cuda(), token_seq=seq.cuda(), block_table=bt.cuda(),
-                                k_pages=k, v_pages=v, page_size=ps, write_kv=write)
+                                k_pages=k, v_pages=v, page_size=ps, write_kv=write, pairing=pairing)
         outs.append((x, k, v))
     (x1, k1, v1), (x2, k2, v2) = outs
     close(x1[:, : nq * D], x2[:, : nq * D], dtype, "q")
@@ -133,6 +135,38 @@ def test_qk_norm_rope_store(ops, dtype, nq, nkv, D, ps, rot, write):
     if write:  # slots that no token of the step owns are untouched
         k0, _ = make_cache(B * maxp, nkv, ps, D, dtype, 9)
         assert int((k1 != k0).any(dim=-1).any(dim=1).sum()) == T
+    ops.raise_if_kernel_error()
+
+
+def test_a_position_beyond_the_rotation_tables_is_reported_not_rotated(ops):
+    """The store kernels never rotate a token with another position's angles: a position outside
+    the tables leaves that token's q and k as they were and sets the error word, which the host
+    turns into an exception.  A table of no rows at all is refused before any launch."""
+    from qwen3_runtime_b200.ops.cuda import KernelError
+
+    nq, nkv, ps = 2, 1, 4
+    for D in (32, 48):  # the 16-byte kernel and the scalar one
+        T = 3
+        qkv = rand((T, (nq + 2 * nkv) * D), torch.bfloat16, 12)
+        pos = torch.tensor([0, 1, 9], dtype=torch.int32).cuda()   # the table below has 8 rows
+        seq = torch.zeros(T, dtype=torch.int32).cuda()
+        bt = torch.tensor([[0, 1, 2]], dtype=torch.int32).cuda()
+        k, v = make_cache(3, nkv, ps, D, torch.bfloat16, 13)
+        inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+        cos, sin = ops.rope_table(inv.cuda(), 8)
+        x = qkv.clone()
+        ops.qk_norm_rope_store(x, num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=None, k_weight=None, eps=0.0,
+                               cos=cos, sin=sin, positions=pos, token_seq=seq, block_table=bt, k_pages=k, v_pages=v,
+                               page_size=ps, write_kv=True)
+        with pytest.raises(KernelError, match="outside the rotation tables"):
+            ops.raise_if_kernel_error()
+        assert torch.equal(x[2, : nq * D], qkv[2, : nq * D]), "the out-of-range token's q is untouched"
+        assert not torch.equal(x[1, : nq * D], qkv[1, : nq * D]), "the others were rotated"
+        ops.raise_if_kernel_error()  # the word was cleared
+        with pytest.raises(KernelError, match="bad argument"):
+            ops.qk_norm_rope_store(x, num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=None, k_weight=None,
+                                   eps=0.0, cos=cos[:0], sin=sin[:0], positions=pos, token_seq=seq, block_table=bt,
+                                   k_pages=k, v_pages=v, page_size=ps, write_kv=True)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -365,27 +399,28 @@ def decode_problem(nq, nkv, D, ps, lens, seed):
     return pr
 
 
-def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list=None, out=None):
+MERGE_KERNEL = False  # set by the decode_loader fixture: the slices are merged by a second kernel
+
+
+def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list=None, out=None, merge_kernel=None):
     out = out if out is not None else torch.zeros((pr["T"], nq * D), dtype=torch.bfloat16, device="cuda")
     n = len(lens) if seq_list is None else seq_list.numel()
     ops.paged_attention_decode(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D,
                                k_pages=pr["k"], v_pages=pr["v"], block_table=pr["bt"], kv_lens=pr["kv_lens"],
                                cu_seqlens=pr["cu"], out=out, page_size=ps, scale=1 / math.sqrt(D), window=window,
-                               num_seqs=n, max_kv_len=max(lens), seq_list=seq_list, num_splits=splits)
+                               num_seqs=n, max_kv_len=max(lens), seq_list=seq_list, num_splits=splits,
+                               merge_kernel=MERGE_KERNEL if merge_kernel is None else merge_kernel)
     return out
 
 
-@pytest.fixture(params=["page boxes, last block merges", "16-byte copies, last block merges",
-                        "16-byte copies, merge kernel"])
+@pytest.fixture(params=["last block merges", "merge kernel"])
 def decode_loader(ops, request):
-    """The split-KV kernel fetches keys and values as TMA page boxes where the page size allows it
-    (8, 16, 32, multiples of 64) or with 16-byte copies, and the slices are merged by the block
-    that finishes last or by a second kernel."""
-    before = ops.decode_page_boxes, ops.decode_merge_by_last_block
-    ops.decode_page_boxes = request.param.startswith("page boxes")
-    ops.decode_merge_by_last_block = "last block" in request.param
+    """The slices of a sequence and kv head are merged by the block that finishes last, or by a
+    second kernel (what callers without ticket words get)."""
+    global MERGE_KERNEL
+    MERGE_KERNEL = request.param == "merge kernel"
     yield request.param
-    ops.decode_page_boxes, ops.decode_merge_by_last_block = before
+    MERGE_KERNEL = False
     ops.raise_if_kernel_error()
     assert ops._tickets is None or not bool(ops._tickets.any()), "every ticket word is zero again after a launch"
 
@@ -412,24 +447,19 @@ def test_decode_attention_merge_by_last_block_gives_the_bits_of_the_merge_kernel
     also with empty slices (windows, lengths far below the slice count)."""
     lens = [1, 63, 64, 65, 700, 129, 2, 1000, 4096, 333]
     pr = decode_problem(nq, nkv, D, ps, lens, 81)
-    before = ops.decode_merge_by_last_block
-    try:
-        for splits in (2, 6, 13):
-            for window in (None, 100):
-                ops.decode_merge_by_last_block = False
-                want = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
-                ops.decode_merge_by_last_block = True
-                for _ in range(3):
-                    got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits)
-                    assert torch.equal(got, want), (splits, window)
-                assert not bool(ops._tickets.any())
-    finally:
-        ops.decode_merge_by_last_block = before
+    for splits in (2, 6, 13):
+        for window in (None, 100):
+            want = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits, merge_kernel=True)
+            for _ in range(3):
+                got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits, merge_kernel=False)
+                assert torch.equal(got, want), (splits, window)
+            assert not bool(ops._tickets.any())
 
 
 @pytest.mark.parametrize("nq,nkv,D,ps", [(32, 8, 128, 64), (8, 8, 64, 8), (16, 1, 128, 32), (6, 2, 256, 16),
                                           (14, 2, 64, 3), (32, 8, 128, 16)])
-@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False), (False, False),
+                                         (True, "interleaved")])
 def test_decode_attention_makes_the_newest_token_itself(ops, decode_loader, nq, nkv, D, ps, norm, rotate):
     """One kernel (per-head norm, rotation, cache write, attention) against the two kernels it
     replaces: the same bits in the output and in the pages, for every split count and window."""
@@ -438,6 +468,7 @@ def test_decode_attention_makes_the_newest_token_itself(ops, decode_loader, nq, 
     qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if norm else None
     kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if norm else None
     cos = sin = None
+    pairing = rotate if isinstance(rotate, str) else "half"
     if rotate:
         inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
         cos, sin = ops.rope_table(inv.cuda(), 1024)
@@ -448,7 +479,8 @@ def test_decode_attention_makes_the_newest_token_itself(ops, decode_loader, nq, 
         two = dict(pr, q=pr["q"].clone(), k=pr["k"].clone(), v=pr["v"].clone())
         ops.qk_norm_rope_store(two["q"], num_heads=nq, num_kv_heads=nkv, head_dim=D, q_weight=qw, k_weight=kw,
                                eps=1e-6, cos=cos, sin=sin, positions=pr["pos"], token_seq=pr["seq"],
-                               block_table=pr["bt"], k_pages=two["k"], v_pages=two["v"], page_size=ps, write_kv=True)
+                               block_table=pr["bt"], k_pages=two["k"], v_pages=two["v"], page_size=ps, write_kv=True,
+                               pairing=pairing)
         want = run_decode(ops, two, nq, nkv, D, ps, lens, window=window, splits=splits)
         one = dict(pr, q=pr["q"].clone(), k=pr["k"].clone(), v=pr["v"].clone())
         raw = one["q"].clone()
@@ -457,7 +489,8 @@ def test_decode_attention_makes_the_newest_token_itself(ops, decode_loader, nq, 
                                    k_pages=one["k"], v_pages=one["v"], block_table=pr["bt"], kv_lens=pr["kv_lens"],
                                    cu_seqlens=pr["cu"], out=got, page_size=ps, scale=1 / math.sqrt(D), window=window,
                                    num_seqs=len(lens), max_kv_len=max(lens), num_splits=splits,
-                                   new_token=dict(q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin))
+                                   new_token=dict(q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin,
+                                                  pairing=pairing), merge_kernel=MERGE_KERNEL)
         what = f"splits={splits} window={window}"
         assert torch.equal(got, want), what
         assert torch.equal(one["k"], two["k"]) and torch.equal(one["v"], two["v"]), what

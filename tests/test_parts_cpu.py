@@ -44,3 +44,7 @@ def test_toy_position_encoding_registers_builds_and_steps():
 
 def test_partial_sums_are_allowed_by_the_run_order_and_added_by_the_norm():
     pc.case_partial_sums(DT, OPS, DEV)
+
+
+def test_interleaved_pairs_biases_and_capped_logits():
+    pc.case_interleaved_pairs_biases_and_capped_logits(DT, OPS, DEV)

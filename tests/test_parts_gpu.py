@@ -19,7 +19,8 @@ def ops():
                                   pc.case_feed_forward_part, pc.case_run_order_layer_twice_and_shared_cache,
                                   pc.case_window_attention, pc.case_toy_state_mixer,
                                   pc.case_toy_routed_feed_forward, pc.case_toy_position_encoding,
-                                  pc.case_partial_sums, pc.case_toy_state_mixer_in_captured_steps],
+                                  pc.case_partial_sums, pc.case_toy_state_mixer_in_captured_steps,
+                                  pc.case_interleaved_pairs_biases_and_capped_logits],
                          ids=lambda f: f.__name__[5:])
 def test_part(ops, case, dtype):
     case(dtype, ops, "cuda")
