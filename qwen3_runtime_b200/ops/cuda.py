@@ -313,6 +313,9 @@ class CudaOps:
         rot_half = cos.shape[1] if cos is not None else 0
         max_pos = cos.shape[0] if cos is not None else 0
         max_pages = block_table.shape[1] if block_table is not None else 0
+        if cos is not None and (max_pos < 1 or sin is None or sin.shape != cos.shape):
+            raise KernelError("qk_norm_rope_store: bad argument: rotation tables need at least one position "
+                              "and cos and sin of one shape")
         if head_dim * 16 > 48 * 1024:
             raise KernelError(f"qk_norm_rope_store: head_dim={head_dim} is too large (limit 3072)")
         if self.timing is not None:

@@ -15,15 +15,33 @@ from qwen3_runtime_b200.engine.factory import build_engine, build_runtime, load_
 
 # Tolerances, fixed in advance.  float32: the engine and the plain implementation do the
 # same arithmetic in different orders; observed differences are a few 1e-6 on logits of
-# magnitude ~4.  bfloat16: activations are rounded to 8 bits of mantissa between kernels,
-# which moves logits by about a percent of their range; the plain side rounds at the same
-# places, so what is left is rounding that fell the other way.
+# magnitude ~4.  bfloat16: activations are rounded to 8 bits of mantissa between kernels, which
+# moves the logits; how far is measured for every case, as the distance between the plain
+# implementation with bfloat16 activations and the plain implementation in float32 on the same
+# tokens (the rounding noise of that case).  The engine rounds at the same places, with sums in
+# other orders, so its logits are another draw of the same noise: it has to stay within
+# BF16_NOISE_FACTOR times the measured noise of the plain bfloat16 logits.  (On the two golden
+# models the reference's own bfloat16 model lies 0.027..0.049 from its float32 logits, the plain
+# bfloat16 logits 0.019..0.036, and the two 0.031..0.046 from each other: tests/test_plain_model.py.)
 TOL_F32 = 3e-5
-REL_TOL_BF16 = 0.03  # of max |logit|
+BF16_NOISE_FACTOR = 3.0
 
 
-def tolerance(dtype: str, scale: float) -> float:
-    return TOL_F32 * max(1.0, scale / 4.0) if dtype == "float32" else REL_TOL_BF16 * scale
+class Expected(dict):
+    """``{request: plain logits}`` with the tolerance that goes with them."""
+
+    tol: float = 0.0
+    noise: float | None = None
+
+
+def tolerance_f32(scale: float) -> float:
+    return TOL_F32 * max(1.0, scale / 4.0)
+
+
+def bf16_tolerance(rounded, exact) -> tuple[float, float]:
+    """(tolerance, noise) from the plain logits with bfloat16 activations and in float32."""
+    noise = max(float((a.double() - b.double()).abs().max()) for a, b in zip(rounded, exact))
+    return BF16_NOISE_FACTOR * noise, noise
 
 
 def check_greedy_within_rounding(raw, w, prompt, tokens, what, dtype="bfloat16"):
@@ -36,16 +54,35 @@ def check_greedy_within_rounding(raw, w, prompt, tokens, what, dtype="bfloat16")
                              rows=list(range(len(prompt) - 1, len(prompt) + len(tokens) - 1)),
                              act_dtype=torch.bfloat16 if dtype == "bfloat16" else None)
     assert rows.shape[0] == len(tokens)
-    tol = 2 * tolerance(dtype, float(rows.abs().max()))
+    if dtype == "bfloat16":  # two logits may each be off by the tolerance, in opposite directions
+        exact = pm.forward_logits(raw, w, list(prompt) + list(tokens[:-1]),
+                                  rows=list(range(len(prompt) - 1, len(prompt) + len(tokens) - 1)))
+        tol = 2 * bf16_tolerance([rows], [exact])[0]
+    else:
+        tol = 2 * tolerance_f32(float(rows.abs().max()))
     for i, tok in enumerate(tokens):
         gap = float(rows[i].max() - rows[i][tok])
         assert gap <= tol, f"{what}: token {i} ({tok}) is {gap:.3g} below the plain argmax (allowed {tol:.3g})"
 
 
-def plain_logits(folder, requests, dtype):
+def plain_logits(folder, requests, dtype, rows=None):
+    """The plain implementation's logits for every request (``rows``: {request: positions}, default
+    all) and the tolerance the engine is held to."""
     raw, w = pm.read_model_dir(folder)
-    act = torch.bfloat16 if dtype == "bfloat16" else None
-    return {rid: pm.forward_logits(raw, w, toks, act_dtype=act) for rid, toks in requests.items()}
+    return expected_logits(raw, w, requests, dtype, rows)
+
+
+def expected_logits(raw, w, requests, dtype, rows=None):
+    pick = (lambda rid: None) if rows is None else (lambda rid: rows[rid])
+    exact = {rid: pm.forward_logits(raw, w, toks, rows=pick(rid)) for rid, toks in requests.items()}
+    if dtype == "float32":
+        out = Expected(exact)
+        out.tol = tolerance_f32(max(float(v.abs().max()) for v in exact.values()))
+        return out
+    out = Expected({rid: pm.forward_logits(raw, w, toks, rows=pick(rid), act_dtype=torch.bfloat16)
+                    for rid, toks in requests.items()})
+    out.tol, out.noise = bf16_tolerance(list(out.values()), [exact[rid] for rid in out])
+    return out
 
 
 def requests_for(name, lengths, seed=0):
@@ -64,10 +101,15 @@ def make_runtime(folder, name, dtype, ops, device, *, num_pages, max_live=4, cud
 def check_against(got, want, dtype, what, positions=None):
     """``positions``: how many logit rows ``got`` has to hold (default: every position of ``want``)."""
     scale = max(float(v.abs().max()) for v in want.values())
-    tol = tolerance(dtype, scale)
+    tol = want.tol
     bad = first_mismatch(got, want, tol)
     assert bad is None, (f"{what}: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g} "
-                         f"(tolerance {tol:.3g}, logits up to {scale:.3g})")
+                         f"(tolerance {tol:.3g}, logits up to {scale:.3g}, rounding noise {want.noise})")
+    if want.noise:
+        from helpers import max_abs_diff
+
+        print(f"{what}: worst difference {max_abs_diff(got, want) / want.noise:.2f} x the rounding noise "
+              f"{want.noise:.3g} (allowed {BF16_NOISE_FACTOR})")
     n = sum(len(v) for v in got.values())
     expect = sum(v.shape[0] for v in want.values()) if positions is None else positions
     assert n == expect, f"{what}: {n} positions compared, {expect} expected"
@@ -95,9 +137,9 @@ def case_four_schedules(tmp_path, name, dtype, ops, device, lengths=(100, 37, 61
     scale = max(float(v.abs().max()) for v in whole.values())
     if dtype == "float32":
         # the float32 kernels reduce in an order that depends on the position only: bit-identical
-        cut_tol = 0.0 if getattr(ops, "name", "").startswith("cuda") else tolerance(dtype, scale)
+        cut_tol = 0.0 if getattr(ops, "name", "").startswith("cuda") else tolerance_f32(scale)
     else:
-        cut_tol = REL_TOL_BF16 * scale
+        cut_tol = want.tol
     for kind in ("tail", "portions", "mixed"):
         bad = first_mismatch(results[kind], whole, cut_tol)
         assert bad is None, f"{name} {dtype} {kind} vs whole: request {bad[0]} position {bad[1]} differs by {bad[2]:.3g}"

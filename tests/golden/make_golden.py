@@ -8,8 +8,10 @@ For the tiny configurations A and B it builds the seeded random model of
 tests/helpers.py, loads those tensors into the reference's ``Qwen3ForCausalLM``
 through its own ``load_hf_state_dict`` (qwen3_runtime/utils/loader.py:33-54), and
 stores (a) float32 logits of whole prompts from one packed forward
-(qwen3_runtime/models/qwen3.py:222-266) and (b) greedy token ids from the reference's
-paged engine with chunked prefill (qwen3_runtime/engine/engine.py:359-366).
+(qwen3_runtime/models/qwen3.py:222-266), (b) greedy token ids from the reference's
+paged engine with chunked prefill (qwen3_runtime/engine/engine.py:359-366) and (c) the
+logits of the same forward with the model converted to bfloat16 (``model.to(bfloat16)``:
+bfloat16 weights, activations and residual stream, layers/ops.py:17-49), as float32.
 tests/test_plain_model.py compares the plain implementation with these files.
 """
 
@@ -57,6 +59,13 @@ def main() -> None:
                 engine = Engine(Config(block_size=TINY[name]["page_size"], num_kv_blocks=64, max_num_seqs=4,
                                        max_num_batched_tokens=6), PagedRunner(model))
                 out[f"prompt{i}.greedy"] = torch.tensor(engine.generate(ids, max_tokens=8), dtype=torch.int32)
+            low = Qwen3ForCausalLM(cfg).eval()
+            load_hf_state_dict(low, {k: v.float() for k, v in tensors.items()})
+            low = low.to(torch.bfloat16)
+            for i, n in enumerate(lens):
+                ids = out[f"prompt{i}.ids"].tolist()
+                logits = low(torch.tensor(ids), torch.arange(n), cu_seqlens=[0, n])
+                out[f"prompt{i}.logits_bf16"] = logits.float().contiguous()
         save_file(out, str(HERE / f"tiny_{name}.safetensors"))
         print(name, {k: tuple(v.shape) for k, v in out.items()})
 

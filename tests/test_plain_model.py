@@ -40,6 +40,36 @@ def test_plain_greedy_matches_reference_engine(tmp_path):
             i += 1
 
 
+def test_plain_bfloat16_against_the_reference_model_in_bfloat16(tmp_path):
+    """The reference converted to bfloat16 (``model.to(bfloat16)``) also keeps its residual stream in
+    bfloat16 (layers/ops.py:28-37); the plain implementation with ``act_dtype=bfloat16`` rounds
+    where this engine stores and keeps the residual sum in float32.  Measured here, on the
+    reference's own logits: both are rounding-noise away from the float32 logits, the plain
+    variant no further than the reference's own, and they are as far from each other as two
+    draws of that noise are."""
+    worst = dict(ref=0.0, plain=0.0, apart=0.0)
+    for name in ("A", "B"):
+        raw, w = pm.read_model_dir(make_model_dir(tmp_path, name))
+        g = _golden(name)
+        i = 0
+        while f"prompt{i}.ids" in g:
+            ids = g[f"prompt{i}.ids"].tolist()
+            exact, ref16 = g[f"prompt{i}.logits"], g[f"prompt{i}.logits_bf16"]
+            plain16 = pm.forward_logits(raw, w, ids, act_dtype=torch.bfloat16)
+            ref_err = float((ref16 - exact).abs().max())
+            plain_err = float((plain16 - exact).abs().max())
+            apart = float((plain16 - ref16).abs().max())
+            scale = float(exact.abs().max())
+            assert 0.002 * scale < ref_err < 0.02 * scale      # bfloat16 noise: about a percent of the range
+            assert plain_err <= 1.1 * ref_err                  # the float32 residual sum is no worse
+            assert apart <= ref_err + plain_err and apart <= 1.5 * ref_err
+            worst = dict(ref=max(worst["ref"], ref_err), plain=max(worst["plain"], plain_err),
+                         apart=max(worst["apart"], apart))
+            i += 1
+    print("bfloat16 distances from the float32 logits: reference", worst["ref"], "plain", worst["plain"],
+          "between them", worst["apart"])
+
+
 def test_float64_agrees_with_float32(tmp_path):
     raw, w = pm.read_model_dir(make_model_dir(tmp_path, "C"))
     ids = list(range(3, 40))

@@ -28,8 +28,8 @@ def real(tmp_path_factory):
     write_random_model(CFG, folder, seed=4, std=0.02, vector_std=0.02)
     raw, w = pm.read_model_dir(folder)
     requests = {f"r{i}": random_ids(CFG.vocab_size, n, 200 + i) for i, n in enumerate((300, 70, 45))}
-    want = {dt: {rid: pm.forward_logits(raw, w, toks, act_dtype=torch.bfloat16 if dt == "bfloat16" else None)
-                 for rid, toks in requests.items()} for dt in ("float32", "bfloat16")}
+    w32 = {k: v.float() for k, v in w.items()}  # converted once; the plain model converts per call
+    want = {dt: ec.expected_logits(raw, w32, requests, dt) for dt in ("float32", "bfloat16")}
     return folder, requests, want
 
 
@@ -90,19 +90,17 @@ def test_mixed_schedule_with_many_live_requests_at_real_layer_sizes(real, real_f
     requests = {f"m{i}": random_ids(CFG.vocab_size, rnd.randint(14, 40), 900 + i) for i in range(2 * max_live + 3)}
     steps = thin_wants(trace_mixed(requests, seed=9, max_live=max_live, decode_tail=4, admit=0.97))
     assert peak_live(steps) == max_live
-    act = torch.bfloat16 if dtype == "bfloat16" else None
-    want = {}
-    for rid, positions in _wanted_positions(steps).items():
-        rows = pm.forward_logits(raw, w32, requests[rid], rows=positions, act_dtype=act)
-        want[rid] = dict(zip(positions, rows))
+    wanted = _wanted_positions(steps)
+    rows = ec.expected_logits(raw, w32, requests, dtype, rows=wanted)
+    want = ec.Expected({rid: dict(zip(wanted[rid], rows[rid])) for rid in rows})
+    want.tol, want.noise = rows.tol, rows.noise
     ops = CudaOps()
     model, _cfg, _ = load_model(folder, dtype=dtype, ops=ops)
     rt = build_runtime(model, block_size=16, num_kv_blocks=peak_tokens(steps, 64) // 16, max_num_seqs=max_live,
                        cuda_graph=(dtype == "bfloat16"))
     got = run_trace(rt, steps, poison=True)
     ops.raise_if_kernel_error()
-    scale = max(float(r.abs().max()) for rows in want.values() for r in rows.values())
-    tol = ec.tolerance(dtype, scale)
+    tol = want.tol
     bad = first_mismatch(got, want, tol)
     assert bad is None, f"request {bad[0]} position {bad[1]} differs by {bad[2]:.3g} (tolerance {tol:.3g})"
     assert sum(len(v) for v in got.values()) == sum(len(v) for v in want.values())
@@ -121,6 +119,7 @@ def test_a_long_prompt_takes_the_tcgen05_swiglu_product_on_the_default_path(real
     ids = random_ids(CFG.vocab_size, 640, 77)
     positions = [0, 1, 127, 128, 300, 511, 512, 638, 639]
     want = pm.forward_logits(raw, w32, ids, rows=positions, act_dtype=torch.bfloat16)
+    tol, _noise = ec.bf16_tolerance([want], [pm.forward_logits(raw, w32, ids, rows=positions)])
     ops = CudaOps()
     assert ops.large_gemm == "auto"
     seen = []
@@ -132,7 +131,6 @@ def test_a_long_prompt_takes_the_tcgen05_swiglu_product_on_the_default_path(real
 
     ops.linear_tcgen05 = spy
     model, _cfg, _ = load_model(folder, dtype="bfloat16", ops=ops)
-    tol = ec.tolerance("bfloat16", float(want.abs().max()))
     for cuts in ((640,), (512, 128)):
         seen.clear()
         rt = build_runtime(model, block_size=16, num_kv_blocks=40, max_num_seqs=2)
