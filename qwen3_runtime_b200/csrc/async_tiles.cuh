@@ -73,6 +73,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// After a block has given up: wait for something of its own that is still in flight (copies
+// into its shared memory, MMAs into its tensor memory) before it frees and leaves.  The limit is
+// a long one of its own, so that shortening Q3_WAIT_LIMIT_CYCLES does not cut this wait short.
+#ifndef Q3_DRAIN_LIMIT_CYCLES
+#define Q3_DRAIN_LIMIT_CYCLES 2000000000ll
+#endif
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - start > Q3_DRAIN_LIMIT_CYCLES) return false;
+  return true;
+}
 // Bounded wait; on expiry records `code` in the error word and returns (the caller carries on).
 __device__ __forceinline__ void mbar_wait_report(uint32_t bar, uint32_t parity, int* error_word, int code) {
   if (mbar_try_wait(bar, parity)) return;

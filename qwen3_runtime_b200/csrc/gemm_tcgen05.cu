@@ -22,7 +22,10 @@
 //
 // Every wait on an mbarrier is bounded (about a second of SM clock): on expiry the waiter
 // raises the block's abort flag and a global error word, every role leaves its loop, TMEM is
-// freed and the block returns; the host reports the error.  No load uses cluster multicast.
+// freed and the block returns; the host reports the error.  Before it frees anything the
+// one-CTA kernel waits (bounded again, with a limit of its own) for what it still has in
+// flight: the producer for the boxes it issued into shared memory, the MMA thread for the MMAs
+// it issued into tensor memory.  No load uses cluster multicast.
 #include "async_tiles.cuh"
 
 namespace {
@@ -78,9 +81,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   static_assert(BN * NB <= ACC_COLS && BN % 32 == 0 && (BN * NB) % 16 == 0, "tile width");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 5];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
+  int issued = 0;  // producer thread: k-slices whose boxes it has issued
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
@@ -88,6 +92,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int num_kb = (K + BK - 1) / BK;
   const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[STAGES]);
   const uint32_t acc_full0 = smem_addr(&bars[2 * STAGES]), acc_empty0 = smem_addr(&bars[2 * STAGES + 2]);
+  const uint32_t drained = smem_addr(&bars[2 * STAGES + 4]);  // give-up path: the issued MMAs have finished
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -99,6 +104,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(acc_full0 + 8 * b, 1);
       mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
     }
+    mbar_init(drained, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // TMEM allocation is a warp-wide instruction; the same warp frees it at the end
@@ -126,8 +132,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
           mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, full0 + 8 * s, kb * BK, m0);
+#ifndef Q3_TEST_WITHHOLD_A_BOX  // (a test build leaves the weight boxes out: the stage never fills, a wait runs out)
           tma_load_2d(a_dst + A_BYTES, &tmap_w, full0 + 8 * s, kb * BK, n0);
           if (NB == 2) tma_load_2d(a_dst + A_BYTES + B_BYTES, &tmap_w, full0 + 8 * s, kb * BK, up_row_offset + n0);
+#endif
+          issued = g + 1;
         }
       }
     }
@@ -207,6 +216,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (abort_flag) {
+    // The block has given up.  Nothing of its own may still be under way when it frees its tensor
+    // memory and leaves its shared memory to the next block: the boxes of the last STAGES
+    // k-slices that were issued land on their stages' barriers (an earlier slice of a stage had
+    // landed before the stage was issued again), and a last commit arrives when every MMA issued
+    // so far has finished.
+    if (warp == 0 && lane == 0)
+      for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j)
+        mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
+    if (warp == 1 && lane == 0) {
+      umma_commit(drained);
+      mbar_wait_drain(drained, 0);
+    }
+    __syncthreads();
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");

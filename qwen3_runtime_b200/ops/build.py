@@ -99,21 +99,24 @@ def _digest(group: str) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(group: str) -> Path:
-    return build_dir() / f"{group}-{_digest(group)}.so"
+def library_path(group: str, variant: str = "", defines: tuple[str, ...] = ()) -> Path:
+    tag = hashlib.sha256((_digest(group) + " ".join(defines)).encode()).hexdigest()[:16] if defines else _digest(group)
+    return build_dir() / f"{group}{variant}-{tag}.so"
 
 
-def compile_group(group: str, *, verbose: bool = True) -> Path:
-    """Compile one group if its library is missing; return the library path."""
+def compile_group(group: str, *, verbose: bool = True, variant: str = "", defines: tuple[str, ...] = ()) -> Path:
+    """Compile one group if its library is missing; return the library path.  ``variant`` and
+    ``defines`` (``-D`` flags) build the same source a second time under another name (a test
+    build with other limits); the ordinary library is not touched."""
     src = CSRC / f"{group}.cu"
     if not src.is_file():
         raise KernelBuildError(f"no kernel source {src}")
-    out = library_path(group)
+    out = library_path(group, variant, defines)
     if out.is_file():
         return out
     nvcc = find_nvcc()
     tmp = out.with_name(f".{out.name}.{os.getpid()}.{threading.get_ident()}.tmp")
-    cmd = [nvcc, *NVCC_FLAGS, str(src), "-o", str(tmp), *EXTRA_FLAGS.get(group, [])]
+    cmd = [nvcc, *NVCC_FLAGS, *defines, str(src), "-o", str(tmp), *EXTRA_FLAGS.get(group, [])]
     start = time.time()
     if verbose:
         print(f"[qwen3_runtime_b200] compiling {group}.cu for sm_100a ...", file=sys.stderr, flush=True)
@@ -130,7 +133,7 @@ def compile_group(group: str, *, verbose: bool = True) -> Path:
         tmp.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed for {group}.cu:\n{log}")
     os.replace(tmp, out)
-    for old in out.parent.glob(f"{group}-*.so"):
+    for old in out.parent.glob(f"{group}{variant}-*.so"):
         if old != out:
             try:
                 old.unlink()

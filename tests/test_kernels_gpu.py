@@ -828,3 +828,45 @@ def test_kernels_refuse_sizes_they_do_not_support(ops):
         ops.linear(torch.zeros(2, 8).cuda(), torch.zeros(4, 9).cuda())
     with pytest.raises(KernelError, match="float32 and bfloat16"):
         ops.silu_mul(torch.zeros(2, 8, dtype=torch.float16).cuda(), torch.zeros(2, 4, dtype=torch.float16).cuda())
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_stays_usable(ops):
+    """The give-up path of a kernel that waits on mbarriers, run for real.  A second build of
+    the tcgen05 product, under another name, leaves the weight boxes of every stage out, so a
+    stage's barrier is a flag that nothing sets, and has short limits (about 1 ms for a wait,
+    10 ms for the wait on what is still in flight).  The kernel must come back by itself with
+    the error word set; the host must raise on it; and the next ordinary launch must be right."""
+    from ctypes import c_int, c_void_p
+
+    from qwen3_runtime_b200.ops import build
+    from qwen3_runtime_b200.ops.cuda import _SIGNATURES, KernelError
+
+    path = build.compile_group("gemm_tcgen05", variant="_withheld_box",
+                               defines=("-DQ3_WAIT_LIMIT_CYCLES=2000000ll", "-DQ3_DRAIN_LIMIT_CYCLES=20000000ll",
+                                        "-DQ3_TEST_WITHHOLD_A_BOX"))
+    import ctypes
+
+    fn = ctypes.CDLL(str(path)).q3_gemm_tcgen05
+    fn.argtypes, fn.restype = _SIGNATURES["gemm_tcgen05"]["q3_gemm_tcgen05"], c_int
+    x = rand((128, 64), torch.bfloat16, 301)
+    w = rand((256, 64), torch.bfloat16, 302, scale=0.05)
+    out = torch.zeros((128, 256), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    code = fn(0, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), 128, 256, 64,
+              err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    stop.record()
+    assert code == 0
+    torch.cuda.synchronize()  # returns: every wait in the kernel is bounded
+    assert int(err.item()) == 1, "the wait that ran out is reported"
+    assert start.elapsed_time(stop) < 2000.0
+    # the kernel table's own word in the same state: the host raises, once
+    ops._error_word(x.device).copy_(err)
+    with pytest.raises(KernelError, match="bounded wait"):
+        ops.raise_if_kernel_error()
+    ops.raise_if_kernel_error()
+    # the context is intact: the ordinary build of the same kernel gives the right product
+    got = ops.linear_tcgen05(x, w, pair=False)
+    close(got, x.float() @ w.float().t(), torch.bfloat16, "product after the aborted one", bf16_tol=1e-2)
+    ops.raise_if_kernel_error()
