@@ -83,14 +83,6 @@ _SIGNATURES = {
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, c_void_p, c_void_p],
     },
-    "decode_step": {
-        "q3_decode_step_scratch": [c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "q3_decode_step_maps": [c_void_p, c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p],
-        "q3_decode_step": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
-                           c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                           c_void_p, c_void_p, c_void_p],
-    },
     "gemm_f32": {
         "q3_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -499,61 +491,6 @@ class CudaOps:
                    _ptr(tickets))
         return out
 
-    # ---- all layers of a decode step as one kernel ---------------------------------------------
-    DECODE_STEP_TOKENS = 16
-
-    def decode_step_scratch(self, *, hidden_size, intermediate_size, num_heads, num_kv_heads, head_dim):
-        """Bytes of the scratch buffers :meth:`decode_step` needs for these sizes (attention partials,
-        their log-sum-exps, attention tickets, sums of squares, one layer's two tensor maps), or None
-        when csrc/decode_step.cu does not take the sizes (or the device)."""
-        sizes = (ctypes.c_long * 5)()
-        code = self._get("decode_step", "q3_decode_step_scratch")(hidden_size, intermediate_size, num_heads,
-                                                                  num_kv_heads, head_dim, sizes)
-        return None if code != 0 else [int(x) for x in sizes]
-
-    def decode_step_maps(self, k_pages: list, v_pages: list, *, num_kv_heads, page_size, head_dim, out) -> bool:
-        """Encode the tensor maps of every layer's key and value pages (``[pages, kv_heads, page_size,
-        head_dim]`` tensors) into ``out`` (a device buffer).  Copies synchronously: once per cache,
-        never inside a stream capture.  False: sizes the kernel does not take."""
-        L = len(k_pages)
-        kp = (ctypes.c_void_p * L)(*[t.data_ptr() for t in k_pages])
-        vp = (ctypes.c_void_p * L)(*[t.data_ptr() for t in v_pages])
-        code = self._get("decode_step", "q3_decode_step_maps")(kp, vp, L, k_pages[0].shape[0], num_kv_heads, page_size,
-                                                               head_dim, _ptr(out))
-        if code == 1:
-            return False
-        _check(code, "decode_step_maps")
-        return True
-
-    def decode_step(self, *, layers, maps, num_layers, num_tokens, hidden_size, intermediate_size, num_heads,
-                    num_kv_heads, head_dim, page_size, token_ids, embed, kv_lens, block_table, cos, sin, pairing, eps,
-                    qk_eps, scale, resid, sumsq, qkv, ctx, mid, att_o, att_lse, att_tickets, barrier, cost=None) -> bool:
-        """Embedding lookup and every layer of a step in which each of at most 16 sequences brings
-        one token, as one persistent kernel (csrc/decode_step.cu); the residual sum after the last
-        layer is left in ``resid`` (fp32 ``[16, H]``).  ``layers``: int64 ``[L, 10]`` device table of
-        pointers (q/k/v, o, gate/up and down weights; the two norms' and the q/k norms' weights;
-        the layer's key and value pages); ``maps``: what :meth:`decode_step_maps` wrote for those
-        pages.  False: the kernel refuses these sizes."""
-        args = (_ptr(layers), _ptr(maps), num_layers, num_tokens, hidden_size, intermediate_size, num_heads,
-                num_kv_heads, head_dim, page_size, embed.shape[0], _ptr(token_ids), _ptr(embed), _ptr(kv_lens),
-                _ptr(block_table), block_table.shape[1], _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
-                self.PAIRINGS[pairing], float(eps), float(qk_eps), float(scale), _ptr(resid), _ptr(sumsq), _ptr(qkv),
-                _ptr(ctx), _ptr(mid), _ptr(att_o), _ptr(att_lse), _ptr(att_tickets), _ptr(barrier),
-                _ptr(self._error_word(resid.device)), self._stream())
-        fn = self._get("decode_step", "q3_decode_step")
-        self.launches += 1
-        if self.timing is not None:
-            self._costs(*(cost or (0, 0)))
-            with self._timed("decode_step (all layers)"):
-                code = fn(*args)
-        else:
-            code = fn(*args)
-        if code == 1:
-            self.launches -= 1
-            return False
-        _check(code, "decode_step")
-        return True
-
     # ---- matrix products ----------------------------------------------------------------
     def linear(self, x, weight, out=None, out_dtype=None, partial_sums=False, bias=None):
         """See :meth:`_product`; ``bias`` (float32 ``[N]``) is added to the finished product, which
@@ -665,7 +602,6 @@ class CudaOps:
                 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
-    ERR_DECODE_STEP = 7  # csrc/decode_step.cu: a bounded wait expired
     ERR_POSITION = 16  # csrc/rope_kv.cu, csrc/attention_decode.cu: a position outside the rotation tables
 
     def _error_word(self, device) -> torch.Tensor:
@@ -682,10 +618,6 @@ class CudaOps:
             err.zero_()
             raise KernelError("a token's position lies outside the rotation tables of the position encoding: "
                               "its query and key were left unrotated and the step's output is invalid")
-        if code == self.ERR_DECODE_STEP:
-            err.zero_()
-            raise KernelError("a bounded wait inside the decode-step kernel expired (a stage of its ring or its "
-                              "barrier over the grid): the kernel gave up and its output is invalid")
         if code != 0:
             err.zero_()
             if self._tickets is not None:  # a kernel that gave up may have left tickets drawn

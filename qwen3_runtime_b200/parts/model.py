@@ -34,7 +34,6 @@ class DecoderModel:
         self.embed: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
         self.loaded = False
-        self.fused_decode = None
 
     # ---- tensors ----------------------------------------------------------------------
     def expected_tensors(self) -> dict[str, ParamSpec]:
@@ -72,15 +71,9 @@ class DecoderModel:
         self.final_norm.load({name: fetch(s.final_norm_prefix + name) for name in self.final_norm.param_specs()})
         self.head = self.embed if s.tie_word_embeddings else fetch(s.head_name).contiguous()
         self.loaded = True
-        # one kernel for all layers of a small decode step, where the arrangement of parts allows it
-        from .fused_decode import plan_fused_decode
-
-        self.fused_decode = plan_fused_decode(self)
 
     def kernel_groups(self) -> list[str]:
         groups = {"norm"}
-        if self.ctx.dtype == torch.bfloat16:
-            groups.add("decode_step")
         for part in [*self.blocks, self.final_norm]:
             groups.update(part.kernel_groups())
         return sorted(groups)
@@ -107,14 +100,8 @@ class DecoderModel:
         ``step.logit_rows`` (None when no logits are wanted)."""
         s = self.spec
         stream = ResidualStream(step.num_tokens, s.hidden_size, ids=step.token_ids, table=self.embed)
-        done = None
-        if self.fused_decode is not None and self.fused_decode.applies(step):
-            done = self.fused_decode.run(step, storage)
-        if done is not None:
-            stream.embed, stream.resid = None, done
-        else:
-            for run in s.order:
-                self.blocks[run.block].forward(stream, step, storage.view(run.cache, run.writes))
+        for run in s.order:
+            self.blocks[run.block].forward(stream, step, storage.view(run.cache, run.writes))
         if step.num_logit_rows == 0:
             return None
         h = self.final_norm.add_norm(stream, rows=step.logit_rows, num_rows=step.num_logit_rows)
