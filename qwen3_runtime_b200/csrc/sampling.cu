@@ -433,6 +433,42 @@ bias_penalty_kernel(float* __restrict__ row, int V, const int* __restrict__ bias
   }
 }
 
+// The same for several rows in one launch: block b works on row `row_index[b]` of `logits` with
+// its own slice of the packed bias entries and seen ids (offsets[b] .. offsets[b + 1]), its own
+// counts scratch and its own three penalties (params[3b .. 3b+2]).
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+bias_penalty_rows_kernel(float* __restrict__ logits, int V, const int* __restrict__ row_index,
+                         const int* __restrict__ bias_off, const int* __restrict__ bias_ids,
+                         const float* __restrict__ bias_vals, const int* __restrict__ seen_off,
+                         const int* __restrict__ seen_ids, int* __restrict__ counts, const float* __restrict__ params) {
+  const int b = blockIdx.x;
+  float* row = logits + (long)row_index[b] * V;
+  for (int i = bias_off[b] + threadIdx.x; i < bias_off[b + 1]; i += blockDim.x) {
+    const int id = bias_ids[i];
+    if (id >= 0 && id < V) atomicAdd(&row[id], bias_vals[i]);
+  }
+  const float repetition = params[3 * b], presence = params[3 * b + 1], frequency = params[3 * b + 2];
+  const int s0 = seen_off[b], s1 = seen_off[b + 1];
+  if (s1 == s0 || (repetition == 1.f && presence == 0.f && frequency == 0.f)) return;
+  int* cnt = counts + (long)b * V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  for (int i = s0 + threadIdx.x; i < s1; i += blockDim.x) {
+    const int id = seen_ids[i];
+    if (id >= 0 && id < V) atomicAdd(&cnt[id], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const int c = cnt[i];
+    if (c == 0) continue;
+    float v = row[i];
+    if (repetition != 1.f) v = v > 0.f ? v / repetition : v * repetition;
+    v -= presence;
+    v -= frequency * (float)c;
+    row[i] = v;
+  }
+}
+
 // Smallest key k such that measure({i : key(x_i) > k}) <= limit, by bisection on the 32-bit key.
 // count_mode: measure = number of elements; else measure = sum of exp(x_i - mx) / z.
 __device__ unsigned cutoff_key(const float* row, int V, bool count_mode, float limit, float mx, float z, float* red) {
@@ -688,6 +724,19 @@ Q3_EXPORT int q3_bias_penalty(float* row, int V, const int* bias_ids, const floa
     return Q3_ERR_ARGUMENT;
   bias_penalty_kernel<<<1, SAMPLE_THREADS, 0, stream>>>(row, V, bias_ids, bias_vals, n_bias, seen_ids, n_seen, counts,
                                                        repetition, presence, frequency);
+  return q3_launch_status();
+}
+
+// Bias and penalties for `n` rows of `logits` ([*, V] fp32) in one launch.  ints: row_index [n],
+// bias_off [n + 1], seen_off [n + 1], bias_ids, seen_ids packed one after the other as the offsets
+// say; floats: params [3 n] (repetition, presence, frequency), then bias_vals; counts: n * V ints.
+Q3_EXPORT int q3_bias_penalty_rows(float* logits, int V, int n, const int* row_index, const int* bias_off,
+                                   const int* bias_ids, const float* bias_vals, const int* seen_off,
+                                   const int* seen_ids, int* counts, const float* params, cudaStream_t stream) {
+  if (!logits || V < 1 || n < 0 || !row_index || !bias_off || !seen_off || !params || !counts) return Q3_ERR_ARGUMENT;
+  if (n == 0) return Q3_OK;
+  bias_penalty_rows_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, V, row_index, bias_off, bias_ids, bias_vals,
+                                                            seen_off, seen_ids, counts, params);
   return q3_launch_status();
 }
 

@@ -114,6 +114,8 @@ _SIGNATURES = {
                       c_void_p],
         "q3_bias_penalty": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                             c_float, c_void_p],
+        "q3_bias_penalty_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p],
         "q3_filter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
 }
@@ -777,6 +779,36 @@ class CudaOps:
                    n_bias, _ptr(seen), n_seen, _ptr(counts), float(repetition_penalty), float(presence_penalty),
                    float(frequency_penalty))
         return row
+
+    def bias_penalty_rows(self, logits, rows, *, logit_bias, seen_ids, repetition_penalty, presence_penalty,
+                          frequency_penalty):
+        """:meth:`bias_penalty_row` for several rows of ``logits`` at once (lists with one entry per
+        row of ``rows``): everything the rows need goes to the device as one integer and one float
+        buffer, and one launch with a block per row works on them."""
+        n, V, dev = len(rows), logits.shape[1], logits.device
+        biases = [b or {} for b in logit_bias]
+        ints, bias_off, seen_off = list(int(r) for r in rows), [0], [0]
+        for b in biases:
+            bias_off.append(bias_off[-1] + len(b))
+        for s, rp, pp, fp in zip(seen_ids, repetition_penalty, presence_penalty, frequency_penalty):
+            live = bool(s) and not (rp == 1.0 and pp == 0.0 and fp == 0.0)
+            seen_off.append(seen_off[-1] + (len(s) if live else 0))
+        packed = ints + bias_off + seen_off
+        packed += [int(k) for b in biases for k in b]
+        packed += [int(t) for s, a, z in zip(seen_ids, seen_off, seen_off[1:]) if z > a for t in s]
+        floats = [float(v) for triple in zip(repetition_penalty, presence_penalty, frequency_penalty) for v in triple]
+        floats += [float(v) for b in biases for v in b.values()]
+        host_i = torch.tensor(packed, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        host_f = torch.tensor(floats, dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+        counts = torch.empty((n, V), dtype=torch.int32, device=dev)
+        o_bias, o_seen = n, 2 * n + 1
+        o_bias_ids = 3 * n + 2
+        o_seen_ids = o_bias_ids + bias_off[-1]
+        self._call("sampling", "q3_bias_penalty_rows", "bias_penalty_rows", _ptr(logits), V, n, _ptr(host_i),
+                   _ptr(host_i[o_bias:]), _ptr(host_i[o_bias_ids:]) if bias_off[-1] else None,
+                   _ptr(host_f[3 * n:]) if bias_off[-1] else None, _ptr(host_i[o_seen:]),
+                   _ptr(host_i[o_seen_ids:]) if seen_off[-1] else None, _ptr(counts), _ptr(host_f))
+        return logits
 
     def filter_rows(self, logits, temperature, min_p, top_k, top_p):
         """Divide by the temperature, then min_p, top_k and top_p masks, in place on fp32 rows

@@ -114,12 +114,14 @@ class Sampler:
         bias and penalties per row, then one launch that divides by the temperature and applies
         min_p, top_k and top_p to the non-greedy rows."""
         out = logits.clone()
-        for i in touched:
-            p: SamplingParams = requests[i].sampling
-            if p.logit_bias or p.has_penalties():
-                self.ops.bias_penalty_row(out[i], logit_bias=p.logit_bias, seen_ids=list(requests[i].token_ids),
-                                          repetition_penalty=p.repetition_penalty,
-                                          presence_penalty=p.presence_penalty, frequency_penalty=p.frequency_penalty)
+        biased = [i for i in touched if requests[i].sampling.logit_bias or requests[i].sampling.has_penalties()]
+        if biased:  # one launch for all of them
+            ps = [requests[i].sampling for i in biased]
+            self.ops.bias_penalty_rows(out, biased, logit_bias=[p.logit_bias for p in ps],
+                                       seen_ids=[requests[i].token_ids for i in biased],
+                                       repetition_penalty=[p.repetition_penalty for p in ps],
+                                       presence_penalty=[p.presence_penalty for p in ps],
+                                       frequency_penalty=[p.frequency_penalty for p in ps])
         rows = [i for i in touched if not requests[i].sampling.is_greedy() and requests[i].sampling.needs_filter()]
         if rows:
             ps = [requests[i].sampling for i in rows]

@@ -168,6 +168,14 @@ class TorchOps:
             row.copy_(torch.where(seen, rep, row) - presence_penalty * seen.float() - frequency_penalty * counts.float())
         return row
 
+    def bias_penalty_rows(self, logits, rows, *, logit_bias, seen_ids, repetition_penalty, presence_penalty,
+                          frequency_penalty):
+        for i, b, s, rp, pp, fp in zip(rows, logit_bias, seen_ids, repetition_penalty, presence_penalty,
+                                       frequency_penalty):
+            self.bias_penalty_row(logits[i], logit_bias=b, seen_ids=list(s), repetition_penalty=rp,
+                                  presence_penalty=pp, frequency_penalty=fp)
+        return logits
+
     def filter_rows(self, logits, temperature, min_p, top_k, top_p):
         lowest = torch.finfo(torch.float32).min
         for r in range(logits.shape[0]):

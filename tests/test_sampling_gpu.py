@@ -50,3 +50,21 @@ def test_bias_penalty_kernel_matches_its_statement(ops):
     got = ops.bias_penalty_row(x.clone(), **kw)
     want = TorchOps().bias_penalty_row(x.clone(), **kw)
     assert float((got - want).abs().max()) < 1e-6
+
+
+def test_bias_and_penalties_for_several_rows_in_one_launch(ops):
+    """Rows with a bias only, penalties only, both, and nothing that bites: one launch, each row as
+    the one-row statement gives it; rows that are not named stay as they were."""
+    g = torch.Generator().manual_seed(11)
+    V = 1531
+    x = (torch.randn((6, V), generator=g) * 3).cuda()
+    rows = [4, 0, 2, 5]
+    kw = dict(logit_bias=[{3: 2.5, 1500: -4.0}, None, {7: 1.0}, None],
+              seen_ids=[[1, 2, 3], [5, 5, 5, 9, 1000], torch.randint(0, V, (300,), generator=g).tolist(), [4, 4]],
+              repetition_penalty=[1.0, 1.3, 0.8, 1.0], presence_penalty=[0.0, 0.5, 0.0, 0.0],
+              frequency_penalty=[0.0, 0.0, 0.25, 0.0])
+    got = ops.bias_penalty_rows(x.clone(), rows, **kw)
+    want = TorchOps().bias_penalty_rows(x.clone(), rows, **kw)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-6)
+    assert torch.equal(got[[1, 3]], x[[1, 3]])
+    assert not torch.equal(got[0], x[0]) and torch.equal(got[5], x[5])  # row 5: penalties that change nothing
