@@ -96,12 +96,6 @@ _SIGNATURES = {
         "q3_gemm_stream_partial": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p],
     },
-    "gemm_skinny": {
-        "q3_gemm_skinny_ranges": [c_int, c_int, c_int],
-        "q3_gemm_skinny": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p],
-        "q3_sum_planes": [c_int, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p],
-    },
     "gemm_tcgen05": {
         "q3_gemm_tcgen05": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                             c_void_p],
@@ -167,12 +161,6 @@ class CudaOps:
         # sums over ranges of K (linear(partial_sums=True)); False: always a finished product
         self.partial_sums = True
         self._parts_cache: dict[tuple, int] = {}
-        # True: bfloat16 products of 17..64 tokens on this engine's tcgen05 kernel with the weights as
-        # the 128-row operand (csrc/gemm_skinny.cu); False: the library's product.  Correct and tested,
-        # but measured slower than the library on a B200 for four of the five products of a step
-        # (3.3 against 5.3 TB/s on the output head at 64 tokens), so off.
-        self.skinny_gemm = False
-        self.SKINNY_MAX_RANGES = 8
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -506,8 +494,7 @@ class CudaOps:
         bfloat16, at most 16 tokens: one of this engine's two weight-streaming kernels
         (:meth:`_small_product`).  bfloat16, more tokens: the library product with fp32
         accumulation, as the reference's ``nn.Linear`` (qwen3_runtime/models/qwen3.py:76-77,
-        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"`` (17..64 tokens
-        with ``skinny_gemm``: the swapped-operand tcgen05 kernel of csrc/gemm_skinny.cu).
+        134-135), or this engine's tcgen05 kernel with ``large_gemm="tcgen05"``.
 
         ``partial_sums``: the caller also takes float32 ``[parts, M, N]`` whose sum over the
         first axis is the product (what :meth:`fused_norm` accepts as ``pending``).  It gets
@@ -542,9 +529,6 @@ class CudaOps:
                 out = torch.empty((M, N), dtype=odt, device=x.device)
             self._small_product(1 if odt == torch.float32 else 0, x, weight, out, M, N, K)
             return out
-        if (self.skinny_gemm and self.large_gemm == "auto" and M <= self.SKINNY_M and self._tcgen05_ok(x, weight)
-                and (out is None or (out.stride(1) == 1 and out.stride(0) >= N))):
-            return self._skinny_product(x, weight, out, out_dtype, partial_sums and self.partial_sums)
         if self.large_gemm == "tcgen05" and self._tcgen05_ok(x, weight):
             return self.linear_tcgen05(x, weight, out=out, out_dtype=out_dtype)
         if self.timing is not None:
@@ -559,45 +543,6 @@ class CudaOps:
         if out is None:
             return torch.mm(x, weight.t())
         return torch.mm(x, weight.t(), out=out)
-
-    SKINNY_M = 64
-
-    def _skinny_product(self, x, weight, out, out_dtype, planes_ok):
-        """17..64 tokens: the weights stream through tcgen05 tiles of 128 features x 64 tokens; K is cut
-        into ranges until every SM has a tile, and the ranges' fp32 planes are handed on
-        (``planes_ok``) or added up by a second small kernel."""
-        M, K = x.shape
-        N = weight.shape[0]
-        odt = out_dtype or (out.dtype if out is not None else x.dtype)
-        key = ("skinny", N, K)
-        ranges = self._parts_cache.get(key)
-        if ranges is None:
-            ranges = self._parts_cache[key] = int(
-                self._get("gemm_skinny", "q3_gemm_skinny_ranges")(N, K, self.SKINNY_MAX_RANGES))
-        err = _ptr(self._error_word(x.device))
-        if ranges > 1 and (M * N) % 4 != 0:
-            ranges = 1  # the adding kernel wants whole 16-byte pieces
-        if ranges > 1:
-            planes = torch.empty((ranges, M, N), dtype=torch.float32, device=x.device)
-            self._call("gemm_skinny", "q3_gemm_skinny", "gemm_skinny", 2, _ptr(x), x.stride(0), _ptr(weight),
-                       weight.stride(0), _ptr(planes), N, M, N, K, ranges, err)
-            if planes_ok and out is None and out_dtype is None:
-                return planes
-            if out is None or not out.is_contiguous():
-                res = torch.empty((M, N), dtype=odt, device=x.device)
-            else:
-                res = out
-            self._call("gemm_skinny", "q3_sum_planes", "sum_planes", _dtype_code(odt), _ptr(planes), ranges,
-                       planes.stride(0), _ptr(res), M * N)
-            if out is not None and res is not out:
-                out.copy_(res)
-                return out
-            return res
-        if out is None:
-            out = torch.empty((M, N), dtype=odt, device=x.device)
-        self._call("gemm_skinny", "q3_gemm_skinny", "gemm_skinny", 1 if odt == torch.float32 else 0, _ptr(x),
-                   x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, 1, err)
-        return out
 
     def _tcgen05_ok(self, x, weight) -> bool:
         return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0

@@ -66,20 +66,6 @@ def test_four_schedules_with_every_large_product_on_tcgen05(tmp_path, name):
     forced.raise_if_kernel_error()
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_four_schedules_with_the_products_of_17_to_64_tokens_on_the_skinny_kernel(tmp_path, name):
-    """The whole model with this engine's swapped-operand tcgen05 kernel wherever a step brings 17..64
-    tokens (an option that is off by default: measured slower than the library)."""
-    from qwen3_runtime_b200.ops.cuda import CudaOps
-
-    ops = CudaOps()
-    ops.skinny_gemm = True
-    before = ops.launches
-    ec.case_four_schedules(tmp_path, name, "bfloat16", ops, "cuda", lengths=(60, 37, 50, 45, 33))
-    assert "skinny" in {k[0] for k in ops._parts_cache if isinstance(k, tuple)} and ops.launches > before
-    ops.raise_if_kernel_error()
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_running_ahead_under_random_arrivals_stops_and_aborts(tmp_path, ops, dtype):
     ran_ahead = sum(ec.case_run_ahead_random(tmp_path, "A", dtype, ops, "cuda", seed, cuda_graph=True)

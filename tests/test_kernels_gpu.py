@@ -657,60 +657,6 @@ def test_gemm_stream_partial_sums(ops, M, N, K):
     ops.raise_if_kernel_error()
 
 
-@pytest.mark.parametrize("M", [17, 32, 33, 64])
-@pytest.mark.parametrize("N,K", [(6144, 2560), (2560, 4096), (2560, 9728), (19456, 2560), (301, 80), (1000, 5128),
-                                 (64, 72), (4100, 2568), (151936, 64)])
-def test_gemm_skinny(ops, M, N, K):
-    """17..64 tokens: finished products (bfloat16, float32), and the planes of a product cut over
-    ranges of K, range by range and through the norm kernel."""
-    x = rand((M, K), torch.bfloat16, 75)
-    w = rand((N, K), torch.bfloat16, 76, scale=0.05)
-    assert ops.large_gemm == "auto"
-    ops.skinny_gemm = True
-    try:
-        _check_gemm_skinny(ops, x, w, M, N, K)
-    finally:
-        ops.skinny_gemm = False
-    ops.raise_if_kernel_error()
-
-
-def _check_gemm_skinny(ops, x, w, M, N, K):
-    before = ops.launches
-    want = x.float() @ w.float().t()
-    got = ops.linear(x, w)
-    assert got.dtype == torch.bfloat16 and ops.launches > before, "one of this engine's kernels, not the library"
-    close(got, want, torch.bfloat16, "skinny bf16", bf16_tol=1e-2)
-    close(ops.linear(x, w, out_dtype=torch.float32), want, torch.float32, "skinny fp32 out", f32_tol=3e-5)
-    out = torch.empty((M, N + 8), dtype=torch.bfloat16, device="cuda")[:, :N]
-    assert ops.linear(x, w, out=out) is out
-    close(out, want, torch.bfloat16, "skinny into a strided out", bf16_tol=1e-2)
-    wide = rand((M, K + 8), torch.bfloat16, 77)
-    close(ops.linear(wide[:, :K], w), wide[:, :K].float() @ w.float().t(), torch.bfloat16, "strided x", bf16_tol=1e-2)
-    planes = ops.linear(x, w, partial_sums=True)
-    if planes.dim() == 3:
-        parts = planes.shape[0]
-        kb = -(-K // 64)
-        per = -(-kb // parts)
-        for p in range(parts):
-            a, b = p * per * 64, min(K, (p + 1) * per * 64)
-            close(planes[p], x[:, a:b].float() @ w[:, a:b].float().t(), torch.float32, f"plane {p}", f32_tol=3e-5)
-        assert torch.equal(ops.linear(x, w, partial_sums=True), planes), "the same bits every time"
-        fewer = ops.linear(x[:17], w, partial_sums=True)
-        if fewer.dim() == 3:  # (17 x N not a multiple of 4: finished instead)
-            assert torch.equal(fewer, planes[:, :17]), "rows do not depend on the others"
-        g = (1 + 0.1 * torch.randn(N, generator=torch.Generator().manual_seed(78))).cuda()
-        resid = rand((M, N), torch.float32, 79)
-        r1, r2 = resid.clone(), resid.clone()
-        o1 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-        o2 = torch.empty_like(o1)
-        ops.fused_norm(o1, g, 1e-6, resid=r1, pending=planes)
-        REF.fused_norm(o2, g, 1e-6, resid=r2, pending=planes)
-        close(o1, o2, torch.bfloat16, "planes through the norm")
-        assert torch.equal(r1, r2)
-    else:
-        close(planes, want, torch.bfloat16, "finished where K is not cut", bf16_tol=1e-2)
-
-
 @pytest.mark.parametrize("M", [1, 8, 13])
 @pytest.mark.parametrize("I,K", [(9728, 2560), (112, 80), (160, 96), (24, 4096), (301, 2560), (6, 9728)])
 def test_gated_linear_small_m(ops, small_gemm, M, I, K):
