@@ -100,7 +100,9 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  The process runs from ``start()`` to
+    ``close()``; samples are kept only inside ``with sampler:`` (a timed region), so that building a
+    model or writing its folder, with the GPU idle, does not enter the record."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -109,34 +111,48 @@ class ClockSampler:
         self.samples: list[list[str]] = []
         self.proc = None
         self.index = index
+        self.keeping = 0
 
-    def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+    def start(self):
+        if self.proc is None:
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "100"],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._read, daemon=True)
+                self.thread.start()
+            except OSError:
+                self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6:
+            if len(parts) == 6 and self.keeping:
                 self.samples.append(parts)
 
+    def __enter__(self):
+        self.start()
+        self.keeping += 1
+        return self
+
     def __exit__(self, *exc):
+        if self.keeping == 1:
+            time.sleep(0.12)  # the sample that covers the end of the region
+        self.keeping -= 1
+
+    def close(self):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+            self.proc = None
 
     def summary(self) -> dict:
+        self.close()
         sm = [int(s[0]) for s in self.samples if s[0].isdigit()]
         mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -338,6 +354,7 @@ def run_ours(args) -> dict:
     import torch
 
     K, W = args.steps, args.warmup
+    clocks = ClockSampler().start()
     max_b = max(BATCH, 64)
     tokens_needed = max_b * (args.context + 3 * K + W + 64) + PREFILL_TOKENS + 64
     engine, model, cfg, ops, build_s = build_ours("4b", args, max_num_seqs=max_b, budget=8192,
@@ -350,7 +367,6 @@ def run_ours(args) -> dict:
     for t in rt.storage.tensors:
         t.normal_(0.0, 0.5)
 
-    clocks = ClockSampler()
     trials, _ = decode_point(rt, ops, torch, rand_ids, BATCH, args.context, K, W, regions=3, sampler=clocks)
     ms_step = statistics.median(trials)
     value = BATCH * 1000.0 / ms_step
@@ -476,7 +492,7 @@ def e2e_ours(engine, args, rand_ids, torch, batch: int = BATCH, context: int | N
 # workloads run end to end under the scheduler (both arms)
 # ------------------------------------------------------------------------------------------
 
-def closed_batch_trials(engine, prompts, max_tokens, trials: int, cost, pk, torch) -> dict:
+def closed_batch_trials(engine, prompts, max_tokens, trials: int, cost, pk, torch, clocks=None) -> dict:
     """One warm-up run and ``trials`` timed runs of a closed batch; medians over the trials, the
     step mix of the last one."""
     from qwen3_runtime_b200.engine.harness import run_closed_batch, step_mix, summarize
@@ -484,7 +500,8 @@ def closed_batch_trials(engine, prompts, max_tokens, trials: int, cost, pk, torc
     runs = []
     for i in range(1 + trials):
         ahead = getattr(engine, "num_run_ahead", 0)
-        traces, records, wall = run_closed_batch(engine, prompts, max_tokens, synchronize=torch.cuda.synchronize)
+        with (clocks if clocks is not None and i > 0 else _Null()):
+            traces, records, wall = run_closed_batch(engine, prompts, max_tokens, synchronize=torch.cuda.synchronize)
         if i == 0:
             continue  # warm-up: kernels loaded, graphs captured
         s = summarize(traces, wall)
@@ -538,16 +555,17 @@ def run_workload_ours(args) -> dict:
     cases = workload_prompts(args.workload, np)
     results, cfg, build_s, engine = {}, None, 0.0, None
     clocks = ClockSampler()
-    with clocks:
-        for label, shape, prompts, max_tokens, seqs, budget in cases:
-            tokens = sum(len(p) for p in prompts) + len(prompts) * (max_tokens + 2 * PAGE)
-            engine, model, cfg, ops, build_s = build_ours(shape, args, max_num_seqs=seqs, budget=budget,
-                                                          tokens_needed=tokens + 64)
-            results[label] = closed_batch_trials(engine, prompts, max_tokens, args.trials, model_cost(cfg), pk, torch)
-            results[label]["max_num_batched_tokens"] = budget
-            ops.raise_if_kernel_error()
-            del engine, model
-            torch.cuda.empty_cache()
+    clocks.start()
+    for label, shape, prompts, max_tokens, seqs, budget in cases:
+        tokens = sum(len(p) for p in prompts) + len(prompts) * (max_tokens + 2 * PAGE)
+        engine, model, cfg, ops, build_s = build_ours(shape, args, max_num_seqs=seqs, budget=budget,
+                                                      tokens_needed=tokens + 64)
+        results[label] = closed_batch_trials(engine, prompts, max_tokens, args.trials, model_cost(cfg), pk, torch,
+                                             clocks=clocks)
+        results[label]["max_num_batched_tokens"] = budget
+        ops.raise_if_kernel_error()
+        del engine, model
+        torch.cuda.empty_cache()
     first = next(iter(results.values()))
     shape = cases[0][1]
     return _workload_line(args, "ours", shape, cfg, results, first, clocks, build_s, pk)
@@ -586,14 +604,14 @@ def run_32b_ours(args, pk) -> dict:
         t.normal_(0.0, 0.5)
     clocks = ClockSampler()
     results = {}
-    with clocks:
-        for b in (1, 8, 32):
-            trials, _ = decode_point(rt, ops, torch, rand_ids, b, context, K, W, regions=3)
-            ms = statistics.median(trials)
-            nbytes = cost.weight_bytes + b * (context + W + 1.5 * K) * cost.kv_bytes_per_token
-            results[f"decode_b{b}"] = dict(tok_s=round(b * 1e3 / ms, 1), ms_per_step=round(ms, 4),
-                                           trials_ms=[round(t, 4) for t in trials],
-                                           hbm_frac=round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4))
+    clocks.start()
+    for b in (1, 8, 32):
+        trials, _ = decode_point(rt, ops, torch, rand_ids, b, context, K, W, regions=3, sampler=clocks)
+        ms = statistics.median(trials)
+        nbytes = cost.weight_bytes + b * (context + W + 1.5 * K) * cost.kv_bytes_per_token
+        results[f"decode_b{b}"] = dict(tok_s=round(b * 1e3 / ms, 1), ms_per_step=round(ms, 4),
+                                       trials_ms=[round(t, 4) for t in trials],
+                                       hbm_frac=round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4))
     prefill_ms = prefill_point(rt, torch, rand_ids, PREFILL_TOKENS)
     _b, flops = cost.step([(0, PREFILL_TOKENS)], 1)
     results["prefill_2048"] = dict(tok_s=round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), ms=round(prefill_ms, 3),
@@ -689,19 +707,20 @@ def run_workload_reference(args) -> dict:
         cases = workload_prompts(args.workload, np)
         results, cfg, write_s = {}, None, 0.0
         clocks = ClockSampler()
-        with clocks:
-            for label, shape, prompts, max_tokens, seqs, budget in cases:
-                tokens = sum(len(p) for p in prompts) + len(prompts) * (max_tokens + 2 * PAGE) + 64
-                engine, cfg, write_s, folder = _reference_engine(args, shape, max_num_seqs=seqs, budget=budget,
-                                                                 tokens_needed=tokens)
-                results[label] = closed_batch_trials(engine, prompts, max_tokens, args.trials, None, pk, torch)
-                results[label]["max_num_batched_tokens"] = budget
-                results[label]["attention_backend"] = engine.config.attention_backend
-                del engine
-                torch.cuda.empty_cache()
-                for f in folder.iterdir():
-                    f.unlink()
-                folder.rmdir()
+        clocks.start()
+        for label, shape, prompts, max_tokens, seqs, budget in cases:
+            tokens = sum(len(p) for p in prompts) + len(prompts) * (max_tokens + 2 * PAGE) + 64
+            engine, cfg, write_s, folder = _reference_engine(args, shape, max_num_seqs=seqs, budget=budget,
+                                                             tokens_needed=tokens)
+            results[label] = closed_batch_trials(engine, prompts, max_tokens, args.trials, None, pk, torch,
+                                                 clocks=clocks)
+            results[label]["max_num_batched_tokens"] = budget
+            results[label]["attention_backend"] = engine.config.attention_backend
+            del engine
+            torch.cuda.empty_cache()
+            for f in folder.iterdir():
+                f.unlink()
+            folder.rmdir()
         first = next(iter(results.values()))
         return _workload_line(args, "reference", cases[0][1], cfg, results, first, clocks, write_s, pk)
     except Exception as exc:  # noqa: BLE001 - the arm reports why it could not run
