@@ -16,7 +16,10 @@ step: every live request gets one new token.  It prints ONE JSON line:
                 pinned host->device copy of the step's inputs, the kernels, sampling and
                 the device->host read of the new token ids (the engine runs ahead: a step's
                 ids are read while the next step, fed from the device, already runs; every
-                step's inputs are still copied in and every step's ids still read out);
+                step's inputs are still copied in and every step's ids still read out).
+                Between the prefill of the prompts and the W warm-up steps both arms pause for
+                half a second: right after a prefill at the power cap decode steps run up to
+                15 % slower for some 40 ms, which is not what a step costs;
 * ``prefill``   one 2,048-token prompt through the step function;
 * ``roofline``  bytes a decode step has to read (every weight once + the live requests'
                 keys and values) / its time, against the measured copy bandwidth;
@@ -99,6 +102,9 @@ def peaks() -> dict:
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_burst=1590.0, source="fallback")
 
 
+E2E_SETTLE_S = 0.5  # pause between the prompts' prefill and the end-to-end decode steps (e2e_steps)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi.  The process runs from ``start()`` to
     ``close()``; samples are kept only inside ``with sampler:`` (a timed region), so that building a
@@ -178,7 +184,7 @@ def flat_config(cfg, *, model: str, batch, seq_len, layers_full: int, cuda_graph
         "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
         "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
         "page_size": PAGE, "cuda_graph": bool(cuda_graph), "l2": "inputs (GBs of weights) larger than L2",
-        "run_ahead": bool(run_ahead), "build_s": round(build_s, 1),
+        "run_ahead": bool(run_ahead), "build_s": round(build_s, 1), "e2e_pause_after_prefill_s": E2E_SETTLE_S,
     }
 
 
@@ -454,6 +460,11 @@ def e2e_steps(engine, torch, batch: int, context: int, K: int, W: int, rand_ids,
 
     while any(produced[r] < 1 for r in rids):
         step()  # untimed: the prompts are prefilled in portions of the token budget
+    # the prefill of batch x context tokens runs at the power cap; the decode steps right after it
+    # are up to 15 % slower for some 40 ms while the clocks come back.  Both arms pause here, so
+    # that the timed steps are steady-state decode steps.
+    torch.cuda.synchronize()
+    time.sleep(E2E_SETTLE_S)
     for _ in range(W):
         step()
     ahead_before = getattr(engine, "num_run_ahead", 0)
