@@ -79,7 +79,15 @@ class PagedAttention(Part):
     def kernel_groups(self):
         groups = ["rope_kv", "attention_generic", *self.position.kernel_groups()]
         if self.ctx.dtype == torch.bfloat16:
-            groups += ["attention_decode", "attention_prefill", "attention_prefill_tc", "gemm_small_m", "gemm_stream"]
+            groups += ["gemm_small_m", "gemm_stream"]
+            # the specialised attention kernels that this head size can reach (ops.paged_attention)
+            group = self.num_heads // self.num_kv_heads
+            if self.head_dim in (64, 128, 256) and group <= 16:
+                groups.append("attention_decode")
+            if self.head_dim in (64, 128) and group <= 16:
+                groups.append("attention_prefill")
+            if self.head_dim == 128 and not self.window and 128 % group == 0:
+                groups.append("attention_prefill_tc")
         if self.ctx.dtype == torch.float32:
             groups.append("gemm_f32")
         return groups
