@@ -816,3 +816,11 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_stays_usable(o
     got = ops.linear_tcgen05(x, w, pair=False)
     close(got, x.float() @ w.float().t(), torch.bfloat16, "product after the aborted one", bf16_tol=1e-2)
     ops.raise_if_kernel_error()
+
+
+def test_the_sweep_behind_the_slice_count_model_runs():
+    """`python -m qwen3_runtime_b200.ops.tune decode_splits --quick`: the measurement that the
+    constants of CudaOps.decode_splits were fitted to, on a few sizes."""
+    from qwen3_runtime_b200.ops import tune
+
+    assert tune.main(["decode_splits", "--quick"]) == 0

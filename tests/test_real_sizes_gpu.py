@@ -109,19 +109,23 @@ def test_mixed_schedule_with_many_live_requests_at_real_layer_sizes(real, real_f
 
 
 def test_a_long_prompt_takes_the_tcgen05_swiglu_product_on_the_default_path(real, real_fp32_weights):
-    """A request of 640 tokens, whole and in portions of 512 + 128: with the default choice of
-    products the fused gate_up + SwiGLU product of 512 tokens and more runs on this engine's paired
-    tcgen05 kernel (seen by a spy on the kernel table), and the logits match the plain model."""
+    """A request of 1280 tokens, whole and in two portions of 640: with the default choice of
+    products the fused gate_up + SwiGLU product runs on this engine's tcgen05 kernels (seen by a spy
+    on the kernel table): 1280 tokens on pairs of SMs, 640 on single SMs (five tiles of 128 tokens
+    fill three rounds, three tiles of 256 would leave a fourth almost empty), and the logits match
+    the plain model."""
     from qwen3_runtime_b200.ops.cuda import CudaOps
 
     folder, _, _ = real
     raw, w32 = real_fp32_weights
-    ids = random_ids(CFG.vocab_size, 640, 77)
-    positions = [0, 1, 127, 128, 300, 511, 512, 638, 639]
+    ids = random_ids(CFG.vocab_size, 1280, 77)
+    positions = [0, 1, 127, 128, 300, 511, 512, 638, 639, 640, 641, 1000, 1279]
     want = pm.forward_logits(raw, w32, ids, rows=positions, act_dtype=torch.bfloat16)
     tol, _noise = ec.bf16_tolerance([want], [pm.forward_logits(raw, w32, ids, rows=positions)])
     ops = CudaOps()
     assert ops.large_gemm == "auto"
+    assert ops._tcgen05_plan(1280, CFG.intermediate_size)[0] and not ops._tcgen05_plan(640, CFG.intermediate_size)[0]
+    assert min(ops._tcgen05_plan(n, CFG.intermediate_size)[2] for n in (640, 1280)) >= ops.TCGEN05_MIN_SHARE
     seen = []
     real_tc = ops.linear_tcgen05
 
@@ -131,9 +135,9 @@ def test_a_long_prompt_takes_the_tcgen05_swiglu_product_on_the_default_path(real
 
     ops.linear_tcgen05 = spy
     model, _cfg, _ = load_model(folder, dtype="bfloat16", ops=ops)
-    for cuts in ((640,), (512, 128)):
+    for cuts in ((1280,), (640, 640)):
         seen.clear()
-        rt = build_runtime(model, block_size=16, num_kv_blocks=40, max_num_seqs=2)
+        rt = build_runtime(model, block_size=16, num_kv_blocks=80, max_num_seqs=2)
         rc = rt.cache.open("long")
         rows, start = [], 0
         for n in cuts:
