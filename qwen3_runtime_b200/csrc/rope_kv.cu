@@ -93,18 +93,19 @@ __global__ void qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int row_strid
                                               const int* __restrict__ token_seq,
                                               const int* __restrict__ block_table, int max_pages,
                                               T* __restrict__ kpages, T* __restrict__ vpages, int ps,
-                                              int num_tokens, int write_kv, int pairing,
+                                              int tph_shift, int write_kv, int pairing,
                                               int* __restrict__ error_word) {
+  // grid (tokens, blocks over one token's heads): no division finds a thread's token and head
   const int tph = D / 16;  // threads per head: a power of two, at most 16
   const int heads = write_kv ? nq + 2 * nkv : nq;
   pdl_wait();
   pdl_launch_dependents();
-  const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long item = gid / tph;
-  const int c = (int)(gid - item * tph);
-  const bool live = item < (long)num_tokens * heads;
-  const int t = live ? (int)(item / heads) : 0;
-  const int hi = live ? (int)(item - (long)t * heads) : 0;
+  const int u = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x;
+  const int hi_raw = u >> tph_shift;
+  const int c = u & (tph - 1);
+  const bool live = hi_raw < heads;
+  const int hi = live ? hi_raw : 0;
   const int half = D / 2;
   T* x = qkv + (long)t * row_stride + (long)hi * D;
   const int p = positions[t];
@@ -182,18 +183,23 @@ Q3_EXPORT int q3_qk_norm_rope_store(int dtype, void* qkv, int row_stride, int nq
                    rk_aligned16(vpages) && rk_aligned16(q_w) && rk_aligned16(k_w) && rk_aligned16(cos_t) &&
                    rk_aligned16(sin_t);
   if (vec) {
-    const long threads_total = (long)num_tokens * (write_kv ? nq + 2 * nkv : nq) * tph;
-    const unsigned vblocks = (unsigned)((threads_total + 255) / 256);
+    // a token's threads in blocks of 128 (Qwen3 sizes: 48 heads x 8 threads = 3 blocks, none idle)
+    const int per_token = (write_kv ? nq + 2 * nkv : nq) * tph;
+    int tph_shift = 0;
+    while ((1 << tph_shift) < tph) ++tph_shift;
+    const int vthreads = 128;
+    const dim3 vgrid((unsigned)num_tokens, (unsigned)((per_token + vthreads - 1) / vthreads));
+    if (vgrid.y > 65535) return Q3_ERR_UNSUPPORTED;
     cudaError_t err;
     if (dtype == Q3_DTYPE_F32)
-      err = launch_pdl(qk_norm_rope_store_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (float*)qkv,
+      err = launch_pdl(qk_norm_rope_store_vec_kernel<float>, vgrid, dim3(vthreads), 0, stream, (float*)qkv,
                        row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-                       block_table, max_pages, (float*)kpages, (float*)vpages, ps, num_tokens, write_kv, pairing,
+                       block_table, max_pages, (float*)kpages, (float*)vpages, ps, tph_shift, write_kv, pairing,
                        error_word);
     else if (dtype == Q3_DTYPE_BF16)
-      err = launch_pdl(qk_norm_rope_store_vec_kernel<bf16>, dim3(vblocks), dim3(256), 0, stream, (bf16*)qkv,
+      err = launch_pdl(qk_norm_rope_store_vec_kernel<bf16>, vgrid, dim3(vthreads), 0, stream, (bf16*)qkv,
                        row_stride, nq, nkv, D, q_w, k_w, eps, cos_t, sin_t, max_pos, positions, token_seq,
-                       block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, num_tokens, write_kv, pairing,
+                       block_table, max_pages, (bf16*)kpages, (bf16*)vpages, ps, tph_shift, write_kv, pairing,
                        error_word);
     else
       return Q3_ERR_ARGUMENT;
