@@ -136,7 +136,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   unsigned char* q_s = smem;                  // [16][D] bf16
   unsigned char* kv_s = smem + 16 * D * 2;    // stages x (K tile, V tile); 1024-byte aligned
   unsigned char* new_s = kv_s + (size_t)stages * 2 * TILE_BYTES;  // FUSED: the newest key, then value, [2][D]
-  // after the last tile the ring is reused: the warps' results [WARPS][16][D] + [WARPS][16][2]
+  // after the last tile the ring is reused: the warps' results [WARPS][16][D + 8] + [WARPS][16][2]
 
   if (!FUSED) pdl_wait();  // keys and values of the newest token come from the kernel before this one
   const int split = blockIdx.x, kvh = blockIdx.y;
@@ -409,17 +409,17 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
-  float* o_s = reinterpret_cast<float*>(kv_s);          // [WARPS][16][D]
-  float* ml_s = o_s + WARPS * 16 * D;                   // [WARPS][16][2]
+  // rows of D + 8 floats: the 8 rows that a warp stores at once then fall into different banks
+  constexpr int OS = D + 8;
+  float* o_s = reinterpret_cast<float*>(kv_s);          // [WARPS][16][OS]
+  float* ml_s = o_s + WARPS * 16 * OS;                  // [WARPS][16][2]
   {
     const int r0 = lane >> 2, c0 = 2 * (lane & 3);
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-      float* base = o_s + ((size_t)warp * 16) * D + i * 8 + c0;
-      base[(size_t)r0 * D] = o[i][0];
-      base[(size_t)r0 * D + 1] = o[i][1];
-      base[(size_t)(r0 + 8) * D] = o[i][2];
-      base[(size_t)(r0 + 8) * D + 1] = o[i][3];
+      float* base = o_s + ((size_t)warp * 16) * OS + i * 8 + c0;
+      *reinterpret_cast<float2*>(base + (size_t)r0 * OS) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(base + (size_t)(r0 + 8) * OS) = make_float2(o[i][2], o[i][3]);
     }
     if ((lane & 3) == 0) {
       ml_s[(warp * 16 + r0) * 2] = m_run[0];
@@ -440,7 +440,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
       const float mw = ml_s[(w * 16 + g) * 2];
       const float f = mw == -INFINITY ? 0.f : exp2f((mw - m) * scale_log2);
       l += ml_s[(w * 16 + g) * 2 + 1] * f;
-      acc += o_s[((size_t)w * 16 + g) * D + d] * f;
+      acc += o_s[((size_t)w * 16 + g) * OS + d] * f;
     }
     const int head = kvh * G + g;
     const float val = acc / l;
@@ -477,7 +477,7 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
                   int num_splits, const NewToken& nt, int* error_word, int* tickets, cudaStream_t stream) {
   const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
-  const size_t merge = (size_t)WARPS * 16 * D * 4 + WARPS * 16 * 2 * 4;
+  const size_t merge = (size_t)WARPS * 16 * (D + 8) * 4 + WARPS * 16 * 2 * 4;
   const size_t smem = 16 * D * 2 + (FUSED ? 2 * D * 2 : 0) + (pipe > merge ? pipe : merge);
   if (smem > 227 * 1024) return Q3_ERR_UNSUPPORTED;
   if (num_splits > 1 && (!mid_o || !mid_lse)) return Q3_ERR_ARGUMENT;
