@@ -106,13 +106,40 @@ __device__ __forceinline__ bool drew_last_ticket(int* ticket, int num_splits) {
   return last;
 }
 
+// The first `slices` of the `num_splits` places that each head's partial results have.
 template <int D>
 __device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
-                                           long first_head, int G, int num_splits, bf16* __restrict__ out_rows) {
+                                           long first_head, int G, int num_splits, int slices,
+                                           bf16* __restrict__ out_rows) {
   constexpr int PER_ROW = D / 4 < 32 ? D / 4 : 32;  // threads on one row, 4 values each
   for (int g = threadIdx.x / PER_ROW; g < G; g += THREADS / PER_ROW)
-    merge_row<D>(mid_o + (first_head + g) * num_splits * D, mid_lse + (first_head + g) * num_splits, num_splits,
+    merge_row<D>(mid_o + (first_head + g) * num_splits * D, mid_lse + (first_head + g) * num_splits, slices,
                  out_rows + (long)g * D, threadIdx.x % PER_ROW, PER_ROW);
+}
+
+// The launch's slice count is made for its longest sequence.  A shorter sequence is cut into fewer
+// slices of about that length (at least one), so that a batch of mixed lengths does not end up with
+// many blocks of a few keys beside a few long ones.  Called by every thread of the block; `span` is
+// this sequence's keys from the first visible tile on.
+__device__ __forceinline__ int slices_of(const int* __restrict__ kv_lens, const int* __restrict__ seq_list,
+                                         int num_seqs, int window, int num_splits, int span) {
+  if (num_splits <= 1) return 1;
+  __shared__ int longest_of_warp[WARPS];
+  int longest = 0;
+  for (int i = threadIdx.x; i < num_seqs; i += THREADS) {
+    const int n = kv_lens[seq_list ? seq_list[i] : i];
+    const int first = window > 0 ? max(0, n - window) : 0;
+    longest = max(longest, n - (first & ~(TILE - 1)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+  if ((threadIdx.x & 31) == 0) longest_of_warp[threadIdx.x >> 5] = longest;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) longest = max(longest, longest_of_warp[w]);
+  int slice = (longest + num_splits - 1) / num_splits;
+  slice = max(TILE, (slice + TILE - 1) & ~(TILE - 1));
+  return min(num_splits, max(1, (span + slice - 1) / slice));
 }
 
 // FUSED: `q` is the raw q/k/v projection; the block norms and rotates its own queries, and the
@@ -150,21 +177,24 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int begin0 = lo & ~(TILE - 1);
   const int total = kv_len - begin0;
-  int per = (total + num_splits - 1) / num_splits;
+  const int slices = slices_of(kv_lens, seq_list, gridDim.z, window, num_splits, total);
+  if (split >= slices) return;  // a sequence shorter than the longest: fewer slices, this block has none
+  int per = (total + slices - 1) / slices;
   per = (per + TILE - 1) & ~(TILE - 1);
   const int k_begin = begin0 + split * per;
   const int k_end = min(kv_len, k_begin + per);
   const int* bt = block_table + (long)seq * max_pages;
 
-  int* ticket = tickets && num_splits > 1 ? tickets + (long)slot * nkv + kvh : nullptr;
+  int* ticket = tickets && slices > 1 ? tickets + (long)slot * nkv + kvh : nullptr;
   if (k_begin >= k_end) {  // nothing visible in this slice
-    if (num_splits > 1 && tid < G)
+    if (slices > 1 && tid < G)
       mid_lse[((long)slot * nq + kvh * G + tid) * num_splits + split] = -INFINITY;
     if (ticket) {
       if (FUSED) pdl_wait();  // the ticket words and `out` belong to the kernels before this one until then
       pdl_launch_dependents();
-      if (drew_last_ticket(ticket, num_splits))
-        merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
+      if (drew_last_ticket(ticket, slices))
+        merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
+                      out + ((long)tok * nq + kvh * G) * D);
     }
     return;
   }
@@ -444,30 +474,37 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
     }
     const int head = kvh * G + g;
     const float val = acc / l;
-    if (num_splits == 1) {
+    if (slices == 1) {
       out[((long)tok * nq + head) * D + d] = __float2bfloat16_rn(val);
     } else {
       mid_o[(((long)slot * nq + head) * num_splits + split) * D + d] = val;
       if (d == 0) mid_lse[((long)slot * nq + head) * num_splits + split] = m * scale_log2 + log2f(l);
     }
   }
-  if (ticket && drew_last_ticket(ticket, num_splits))
-    merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
+  if (ticket && drew_last_ticket(ticket, slices))
+    merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
+                  out + ((long)tok * nq + kvh * G) * D);
 }
 
 // The merge as a kernel of its own: one block per (kv head, sequence).
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
-                      const int* __restrict__ cu_seqlens, const int* __restrict__ seq_list,
-                      bf16* __restrict__ out, int nq, int nkv, int num_splits) {
+                      const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ seq_list, bf16* __restrict__ out, int nq, int nkv, int window,
+                      int num_splits) {
   pdl_wait();
   pdl_launch_dependents();
   const int slot = blockIdx.y, kvh = blockIdx.x;
   const int seq = seq_list ? seq_list[slot] : slot;
   const int tok = cu_seqlens[seq];
   const int G = nq / nkv;
-  merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, out + ((long)tok * nq + kvh * G) * D);
+  const int kv_len = kv_lens[seq];
+  const int lo = window > 0 ? max(0, kv_len - window) : 0;
+  const int slices = slices_of(kv_lens, seq_list, gridDim.y, window, num_splits, kv_len - (lo & ~(TILE - 1)));
+  if (slices == 1) return;  // a sequence in one slice: its block wrote the result itself
+  merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
+                out + ((long)tok * nq + kvh * G) * D);
 }
 
 template <int D, bool FUSED>
@@ -515,7 +552,8 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
   if (num_splits > 1 && !tickets) {
     dim3 cgrid(nkv, num_seqs);
     if (launch_pdl(decode_combine_kernel<D>, cgrid, dim3(THREADS), 0, stream, (const float*)mid_o,
-                   (const float*)mid_lse, cu_seqlens, seq_list, out, nq, nkv, num_splits) != cudaSuccess)
+                   (const float*)mid_lse, kv_lens, cu_seqlens, seq_list, out, nq, nkv, window, num_splits) !=
+        cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   return Q3_OK;

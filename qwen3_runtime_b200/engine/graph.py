@@ -2,11 +2,13 @@
 
 A step in which every request brings exactly one token launches a few hundred small
 kernels; replaying them from a captured graph removes the launch cost.  One graph per
-(batch-size bucket, block-table width bucket): the batch is padded to the bucket with
+(batch-size bucket, block-table width bucket, what the parts' choosers answer for the
+step's lengths): the batch is padded to the bucket with
 dummy sequences that write to the cache's scratch page, the step's integer metadata is
 copied into a fixed device buffer that the captured kernels read, and logits come out
-of a fixed buffer.  Kernel choices inside a captured step depend on the bucket only,
-never on the lengths of the moment.
+of a fixed buffer.  Kernel choices inside a captured step depend on the key only: on the
+buckets, and on the lengths of the moment only through the choosers' answers
+(``Part.step_choosers``), e.g. the slice count of decode attention.
 Parity: qwen3_runtime/engine/cuda_graph.py:79-249 (one graph per batch size, static
 input and logits buffers, metadata refreshed outside the capture).
 """
@@ -39,7 +41,7 @@ class DecodeGraphs:
     def __init__(self, runner, batch_sizes):
         self.runner = runner
         self.sizes = sorted(int(s) for s in batch_sizes)
-        self.captured: dict[tuple[int, int], _Captured] = {}
+        self.captured: dict[tuple, _Captured] = {}
         self.replays = 0
 
     def try_run(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
@@ -53,10 +55,12 @@ class DecodeGraphs:
             return None
         need = max((len(t) for e in entries for t in e.cache.tables), default=1)
         width = max(8, 1 << (max(need, 1) - 1).bit_length())
-        key = (bucket, width)
+        # what the parts' kernels choose from the lengths of the moment is part of the key
+        choices = self.runner.model.step_choices([e.cache.num_computed + 1 for e in entries])
+        key = (bucket, width, tuple(sorted(choices.items())))
         cap = self.captured.get(key)
         if cap is None:
-            cap = self._capture(key)
+            cap = self._capture(key, choices)
         self._fill(cap, entries, bucket, width, need_context=False)
         if device_tokens is not None:  # ids that only the device knows, over the placeholders
             self.runner.builder.last_token_ids.copy_(device_tokens)
@@ -75,19 +79,20 @@ class DecodeGraphs:
                                scratch_slot=r.storage.scratch_slot, device_buffer=cap.meta, all_rows=True,
                                need_context=need_context)
 
-    def _capture(self, key) -> _Captured:
+    def _capture(self, key, choices: dict) -> _Captured:
         """Warm up and capture a step made of padding rows only: every row reads and writes the
         scratch page and the scratch state slot, so neither the warm-up run nor the capture
         touches a live request's keys, values or state (a state layer advanced by the warm-up
         and again by the first replay would count that token twice).  The real step's metadata
         is copied into ``meta`` afterwards, by :meth:`try_run`, and only then replayed."""
-        bucket, width = key
+        bucket, width = key[:2]
         r = self.runner
         n_paged = len(r.cache.paged_groups)
         meta = torch.zeros(8 * bucket + 64 + n_paged * bucket * width, dtype=torch.int32, device=r.device)
         cap = _Captured(torch.cuda.CUDAGraph(), meta, None)
         step = self._fill(cap, [], bucket, width)
         step.captured_width = width
+        step.choices = dict(choices)
         # warm up on a side stream (loads kernels, builds shared tables), then capture
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream(r.device))

@@ -59,6 +59,8 @@ class ModelRunner:
                                       scratch_slot=self.storage.scratch_slot)
             if device_tokens is not None:
                 self.builder.last_token_ids.copy_(device_tokens)
+            if step.decode_only:
+                step.choices = self.model.step_choices(step.host_kv_lens)
             logits = self.model.forward(step, self.storage)
         else:
             logits = logits if logits.numel() else None

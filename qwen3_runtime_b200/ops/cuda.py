@@ -164,6 +164,7 @@ class CudaOps:
         # sums over ranges of K (linear(partial_sums=True)); False: always a finished product
         self.partial_sums = True
         self._parts_cache: dict[tuple, int] = {}
+        self._slices_cache: dict[tuple, int] = {}
         if not torch.cuda.is_available():
             raise KernelsUnavailable(
                 "qwen3_runtime_b200 runs on a CUDA device only (built for NVIDIA B200, sm_100a); "
@@ -326,7 +327,7 @@ class CudaOps:
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
-                        token_seq, positions, out, page_size, scale, window, step=None):
+                        token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None):
         """Causal attention of every token of the step over its sequence's pages."""
         T = out.shape[0]
         if head_dim % 8 or head_dim > 256:
@@ -338,7 +339,8 @@ class CudaOps:
                 q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, k_pages=k_pages,
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
-                max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step)
+                max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step,
+                num_splits=decode_slices)
         if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
@@ -415,20 +417,26 @@ class CudaOps:
     TICKETS = 1 << 16  # ticket words for the merge by the last block: sequences x kv heads of one launch
     DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
 
-    def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 128) -> int:
-        """How many slices each sequence's keys are cut into.  Depends only on sizes that are fixed
-        for a captured step.  The cost of a choice, in units of the time one key takes to stream when
-        every block slot (3 x SMs) is busy: while all blocks fit the slots, keys per slice + 12 per
-        slice (the last block of a pair merges them); beyond that, waves x (keys per slice + 384),
-        the 384 being what a block pays besides its keys (lengths, block table and first tile at the
-        start, the warps' merge and the ticket at the end), which a full machine no longer hides;
-        waves are whole up to six and blocks / slots + 1/2 beyond (blocks of equal length start and
-        end together at first and drift apart later).  Slices are at least 192 keys long, 64 with at
-        most 32 (sequence, kv head) pairs.  The constants are fitted to a sweep of 1..128 sequences x
-        256..16384 keys x 1..64 slices on a B200 (8 kv heads of 128): the choice is within 0.6 % of the
+    def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 128,
+                      total_kv_len: int | None = None) -> int:
+        """How many slices the longest sequence's keys are cut into (the kernel cuts a shorter one
+        into fewer slices of about the same length, so a batch whose lengths add up to
+        ``total_kv_len`` counts as ``total_kv_len / max_kv_len`` sequences of the longest length;
+        without it, all are taken to be that long).  The cost of a choice, in units of the time one
+        key takes to stream when every block slot (3 x SMs) is busy: while all blocks fit the slots,
+        keys per slice + 12 per slice (the last block of a pair merges them); beyond that, waves x
+        (keys per slice + 384), the 384 being what a block pays besides its keys (lengths, block
+        table and first tile at the start, the warps' merge and the ticket at the end), which a full
+        machine no longer hides; waves are whole up to six and blocks / slots + 1/2 beyond (blocks of
+        equal length start and end together at first and drift apart later).  Slices are at least
+        192 keys long, 64 with at most 32 (sequence, kv head) pairs.  The constants are fitted to a
+        sweep of 1..128 sequences x 256..16384 keys x 1..64 slices on a B200 (8 kv heads of 128,
+        ``python -m qwen3_runtime_b200.ops.tune decode_splits``): the choice is within 0.6 % of the
         best one on average and 13 % at worst.  The reference's rule for an RTX 4090 has the same
         inputs (qwen3_runtime/kernels/triton_decode.py:122-133)."""
-        pairs = max(1, num_seqs * num_kv_heads)
+        max_kv_len = max(1, max_kv_len)
+        seqs = num_seqs if total_kv_len is None else min(num_seqs, max(1.0, total_kv_len / max_kv_len))
+        pairs = max(1.0, seqs * num_kv_heads)
         slots = self.DECODE_BLOCKS_PER_SM * self.SM_COUNT
         per_key = head_dim / 128.0  # a key of a smaller head streams faster; the fixed parts do not
         fixed, per_slice = 384.0 / per_key, 12.0 / per_key
@@ -438,7 +446,7 @@ class CudaOps:
             per = -(-(-(-max_kv_len // splits)) // 64) * 64
             if splits > 1 and per < floor:
                 break
-            blocks = pairs * splits
+            blocks = math.ceil(pairs * splits)
             if blocks <= slots:
                 cost = per + per_slice * splits
             else:
@@ -448,6 +456,21 @@ class CudaOps:
             if best_cost is None or cost < best_cost:
                 best, best_cost = splits, cost
         return best
+
+    def decode_slices_for(self, kv_lens: list[int], num_kv_heads: int, head_dim: int, window: int | None) -> int:
+        """:meth:`decode_splits` for a decode step whose sequences have these lengths (asked once per
+        step by the attention parts' chooser; answers are kept by the sizes the model looks at)."""
+        if window:
+            kv_lens = [min(n, int(window) + 63) for n in kv_lens]
+        longest, total = max(kv_lens, default=1), sum(kv_lens)
+        key = (len(kv_lens), num_kv_heads, head_dim, -(-longest // 64), -(-total // 64))
+        slices = self._slices_cache.get(key)
+        if slices is None:
+            if len(self._slices_cache) > 8192:
+                self._slices_cache.clear()
+            slices = self._slices_cache[key] = self.decode_splits(len(kv_lens), num_kv_heads, 64 * key[3], head_dim,
+                                                                  total_kv_len=64 * key[4])
+        return slices
 
     def decode_new_token_ok(self, qkv, *, num_heads, num_kv_heads, head_dim, cos, q_weight, k_weight) -> bool:
         """Whether the split-KV kernel can make q, k and v of the newest token itself (per-head

@@ -29,6 +29,7 @@ class PagedAttention(Part):
         self.qk_norm_eps = spec.get("qk_norm_eps")
         self.window = spec.get("window") or None
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        self._slices_choice = ("decode_slices", self.num_kv_heads, self.head_dim, self.window)
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.head_dim % 16 or self.head_dim > 256:
@@ -92,6 +93,14 @@ class PagedAttention(Part):
             groups.append("gemm_f32")
         return groups
 
+    def step_choosers(self):
+        """Into how many slices the split-KV decode kernel cuts the longest sequence's keys."""
+        model = getattr(self.ops, "decode_slices_for", None)
+        if model is None or self.ctx.dtype != torch.bfloat16 or self.head_dim not in (64, 128, 256):
+            return {}
+        nkv, D, window = self.num_kv_heads, self.head_dim, self.window
+        return {self._slices_choice: lambda kv_lens: model(kv_lens, nkv, D, window)}
+
     def cache_spec(self):
         return KVLayerSpec(self.num_kv_heads, self.head_dim, self.window)
 
@@ -111,6 +120,7 @@ class PagedAttention(Part):
         block_table = step.block_tables[cache.paged_index]
         ctx_out = torch.empty((T, self.q_size), dtype=h.dtype, device=h.device)
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        slices = step.choices.get(self._slices_choice)
         fusable = getattr(ops, "decode_new_token_ok", None)
         if (fusable is not None and step.decode_only and cache.writes
                 and fusable(qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -125,7 +135,7 @@ class PagedAttention(Part):
                 max_kv_len=width * cache.page_size or step.max_kv_len,
                 new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin,
                                pairing=self.pairing),
-                step=step)
+                num_splits=slices, step=step)
             return self._project_out(ctx_out)
         ops.qk_norm_rope_store(
             qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -138,7 +148,7 @@ class PagedAttention(Part):
             qkv, qkv.stride(0), num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
             head_dim=self.head_dim, k_pages=cache.k_pages, v_pages=cache.v_pages, block_table=block_table,
             token_seq=step.token_seq, positions=step.positions, out=ctx_out, page_size=cache.page_size,
-            scale=self.scale, window=self.window, step=step)
+            scale=self.scale, window=self.window, step=step, **({"decode_slices": slices} if slices else {}))
         return self._project_out(ctx_out)
 
     def _project_out(self, ctx_out: torch.Tensor) -> torch.Tensor:

@@ -70,6 +70,11 @@ class StepContext:
     # longest sequence has to size it from ``captured_width * page_size`` then, not from
     # ``max_kv_len``, because the graph is replayed for longer sequences of the same width.
     captured_width: int = 0
+    # In a step in which every sequence brings one token: what the parts' choosers (Part.step_choosers)
+    # answered for the step's lengths, by name.  A captured step is specialised by these values:
+    # they are part of its graph's key, and a part must let nothing else about the lengths of the
+    # moment decide what it launches.
+    choices: dict = field(default_factory=dict)
     extras: dict = field(default_factory=dict)  # per-step scratch shared by the layers of a step
 
 
@@ -88,6 +93,14 @@ class Part:
         self.ops = ctx.ops
 
     def param_specs(self) -> dict[str, ParamSpec]:
+        return {}
+
+    def step_choosers(self) -> dict:
+        """``{name: function(kv_lens) -> hashable}``: choices that this part's kernels make from the
+        lengths (tokens in the cache after the step, one per sequence) of a step in which every
+        sequence brings one token, e.g. into how many slices the keys are cut.  Parts that answer
+        with the same name make the same choice; it is worked out once per step and reaches
+        ``forward`` as ``step.choices[name]``.  A part made of parts passes its parts' choosers on."""
         return {}
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:

@@ -41,6 +41,9 @@ class PreNormBlock(Part):
     def kernel_groups(self):
         return [g for part in self.children.values() for g in part.kernel_groups()]
 
+    def step_choosers(self):
+        return {name: fn for part in self.children.values() for name, fn in part.step_choosers().items()}
+
     def cache_spec(self):
         return self.mixer.cache_spec()
 

@@ -31,6 +31,9 @@ class DecoderModel:
             block = self.blocks[index]
             if hasattr(block, "exit_to") and all(n is not None for n in norms):
                 block.exit_to(norms)
+        self.choosers: dict = {}
+        for block in self.blocks:
+            self.choosers.update(block.step_choosers())
         self.embed: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
         self.loaded = False
@@ -93,6 +96,10 @@ class DecoderModel:
             if not run.writes and specs[run.cache] != self.blocks[run.block].cache_spec():
                 raise ValueError(f"a run entry reads cache layer {run.cache} whose layout differs from its own")
         return CacheLayout(specs)
+
+    def step_choices(self, kv_lens: list[int]) -> dict:
+        """What the parts' choosers answer for a step of one-token sequences with these lengths."""
+        return {name: fn(kv_lens) for name, fn in self.choosers.items()} if kv_lens else {}
 
     # ---- one step -----------------------------------------------------------------------
     def forward(self, step: StepContext, storage) -> torch.Tensor | None:

@@ -185,6 +185,32 @@ def case_many_live(tmp_path, name, dtype, ops, device, max_live, *, cuda_graph=F
     return got
 
 
+def case_mixed_lengths_decoding_together(tmp_path, name, dtype, ops, device, *, cuda_graph=True,
+                                         lengths=(790, 57, 300, 90, 48, 520), tail=40):
+    """Requests of very different lengths decoding side by side: the split-KV kernel cuts the
+    longest into the step's slice count and the shorter ones into fewer slices; the count is chosen
+    from the lengths of the moment, changes while the requests grow, and with captured steps each
+    value has a graph of its own."""
+    folder = make_model_dir(tmp_path, name)
+    requests = requests_for(name, lengths, seed=41)
+    want = plain_logits(folder, requests, dtype)
+    ps = TINY[name]["page_size"]
+    steps = []
+    for i, (rid, toks) in enumerate(requests.items()):
+        head = len(toks) - tail
+        steps.append({"step": i, "entries": [{"id": rid, "tokens": toks[:head], "want": [head - 1]}], "end": []})
+    for j in range(tail):
+        steps.append({"step": len(requests) + j, "end": list(requests) if j == tail - 1 else [],
+                      "entries": [{"id": rid, "tokens": [toks[len(toks) - tail + j]], "want": [0]}
+                                  for rid, toks in requests.items()]})
+    rt = make_runtime(folder, name, dtype, ops, device, num_pages=peak_tokens(steps, 64) // ps + 1,
+                      max_live=len(requests), cuda_graph=cuda_graph)
+    got = run_trace(rt, steps)
+    check_against(got, want, dtype, f"{name} {dtype} mixed lengths decoding together",
+                  positions=(tail + 1) * len(requests))
+    return rt
+
+
 def case_greedy_many(tmp_path, name, dtype, ops, device, num_requests, *, cuda_graph=True, max_tokens=6):
     """Greedy generation of ``num_requests`` requests side by side under the scheduler (a token
     budget that cuts the prompts, a decode batch of that size, captured or not)."""

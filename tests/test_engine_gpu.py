@@ -120,3 +120,18 @@ def test_greedy_generation_of_many_requests_side_by_side(tmp_path, ops, num, nam
     eng = ec.case_greedy_many(tmp_path, name, dtype, ops, "cuda", num, cuda_graph=cuda_graph)
     if cuda_graph and num <= 64:
         assert eng.runner.graphs.replays > 0
+
+
+@pytest.mark.parametrize("cuda_graph", [True, False])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_requests_of_mixed_lengths_decoding_together(tmp_path, ops, name, cuda_graph):
+    """Short and long requests in one decode batch: fewer slices for the shorter ones, the slice
+    count from the lengths of the moment; a captured step for every value it takes."""
+    rt = ec.case_mixed_lengths_decoding_together(tmp_path, name, "bfloat16", ops, "cuda", cuda_graph=cuda_graph)
+    ops.raise_if_kernel_error()
+    assert not bool(ops._tickets.any()), "every ticket word is zero again"
+    if cuda_graph:
+        keys = list(rt.runner.graphs.captured)
+        assert rt.runner.graphs.replays == 40
+        counts = {dict(k[2]).popitem()[1] for k in keys}
+        assert len(keys) >= 2 and len(counts) >= 2 and max(counts) > 1, f"one graph per slice count: {keys}"
