@@ -120,23 +120,31 @@ __device__ __forceinline__ void merge_pair(const float* __restrict__ mid_o, cons
 // The launch's slice count is made for its longest sequence.  A shorter sequence is cut into fewer
 // slices of about that length (at least one), so that a batch of mixed lengths does not end up with
 // many blocks of a few keys beside a few long ones.  Called by every thread of the block; `span` is
-// this sequence's keys from the first visible tile on.
+// this sequence's keys from the first visible tile on; `longest_len` (may be null) points at the
+// length of the launch's longest sequence, which the blocks otherwise work out for themselves.
 __device__ __forceinline__ int slices_of(const int* __restrict__ kv_lens, const int* __restrict__ seq_list,
-                                         int num_seqs, int window, int num_splits, int span) {
+                                         int num_seqs, int window, int num_splits, int span,
+                                         const int* __restrict__ longest_len) {
   if (num_splits <= 1) return 1;
-  __shared__ int longest_of_warp[WARPS];
   int longest = 0;
-  for (int i = threadIdx.x; i < num_seqs; i += THREADS) {
-    const int n = kv_lens[seq_list ? seq_list[i] : i];
+  if (longest_len) {  // the caller knows the longest sequence of the launch: one load, nothing to agree on
+    const int n = *longest_len;
     const int first = window > 0 ? max(0, n - window) : 0;
-    longest = max(longest, n - (first & ~(TILE - 1)));
+    longest = n - (first & ~(TILE - 1));
+  } else {
+    __shared__ int longest_of_warp[WARPS];
+    for (int i = threadIdx.x; i < num_seqs; i += THREADS) {
+      const int n = kv_lens[seq_list ? seq_list[i] : i];
+      const int first = window > 0 ? max(0, n - window) : 0;
+      longest = max(longest, n - (first & ~(TILE - 1)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+    if ((threadIdx.x & 31) == 0) longest_of_warp[threadIdx.x >> 5] = longest;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) longest = max(longest, longest_of_warp[w]);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
-  if ((threadIdx.x & 31) == 0) longest_of_warp[threadIdx.x >> 5] = longest;
-  __syncthreads();
-#pragma unroll
-  for (int w = 0; w < WARPS; ++w) longest = max(longest, longest_of_warp[w]);
   int slice = (longest + num_splits - 1) / num_splits;
   slice = max(TILE, (slice + TILE - 1) & ~(TILE - 1));
   return min(num_splits, max(1, (span + slice - 1) / slice));
@@ -156,7 +164,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
                         const int* __restrict__ seq_list, bf16* __restrict__ out, float* __restrict__ mid_o,
                         float* __restrict__ mid_lse, int nq, int nkv, int ps, float scale_log2, int window,
                         int num_splits, int stages, NewToken nt, int* __restrict__ error_word,
-                        int* __restrict__ tickets) {
+                        int* __restrict__ tickets, const int* __restrict__ longest_len) {
   constexpr int CHUNKS = D / 8;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -177,7 +185,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* kp
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int begin0 = lo & ~(TILE - 1);
   const int total = kv_len - begin0;
-  const int slices = slices_of(kv_lens, seq_list, gridDim.z, window, num_splits, total);
+  const int slices = slices_of(kv_lens, seq_list, gridDim.z, window, num_splits, total, longest_len);
   if (split >= slices) return;  // a sequence shorter than the longest: fewer slices, this block has none
   int per = (total + slices - 1) / slices;
   per = (per + TILE - 1) & ~(TILE - 1);
@@ -492,7 +500,7 @@ __global__ void __launch_bounds__(THREADS)
 decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__ mid_lse,
                       const int* __restrict__ kv_lens, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ seq_list, bf16* __restrict__ out, int nq, int nkv, int window,
-                      int num_splits) {
+                      int num_splits, const int* __restrict__ longest_len) {
   pdl_wait();
   pdl_launch_dependents();
   const int slot = blockIdx.y, kvh = blockIdx.x;
@@ -501,7 +509,8 @@ decode_combine_kernel(const float* __restrict__ mid_o, const float* __restrict__
   const int G = nq / nkv;
   const int kv_len = kv_lens[seq];
   const int lo = window > 0 ? max(0, kv_len - window) : 0;
-  const int slices = slices_of(kv_lens, seq_list, gridDim.y, window, num_splits, kv_len - (lo & ~(TILE - 1)));
+  const int slices =
+      slices_of(kv_lens, seq_list, gridDim.y, window, num_splits, kv_len - (lo & ~(TILE - 1)), longest_len);
   if (slices == 1) return;  // a sequence in one slice: its block wrote the result itself
   merge_pair<D>(mid_o, mid_lse, (long)slot * nq + kvh * G, G, num_splits, slices,
                 out + ((long)tok * nq + kvh * G) * D);
@@ -511,7 +520,8 @@ template <int D, bool FUSED>
 int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* vpages, const int* block_table,
                   int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, bf16* out,
                   float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int ps, float scale, int window,
-                  int num_splits, const NewToken& nt, int* error_word, int* tickets, cudaStream_t stream) {
+                  int num_splits, const NewToken& nt, int* error_word, int* tickets, const int* longest_len,
+                  cudaStream_t stream) {
   const int stages = 2;  // more stages mean fewer blocks per SM; measured equal at best
   const size_t pipe = (size_t)stages * 2 * TILE * D * 2;
   const size_t merge = (size_t)WARPS * 16 * (D + 8) * 4 + WARPS * 16 * 2 * 4;
@@ -546,14 +556,14 @@ int launch_decode(const bf16* q, int q_stride, const bf16* kpages, const bf16* v
     const float scale_log2 = scale * 1.4426950408889634f;
     if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, FUSED>, q, q_stride, kpages, vpages, block_table,
                            max_pages, kv_lens, cu_seqlens, seq_list, out, mid_o, mid_lse, nq, nkv, ps, scale_log2,
-                           window, num_splits, stages, nt, error_word, tickets) != cudaSuccess)
+                           window, num_splits, stages, nt, error_word, tickets, longest_len) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   if (num_splits > 1 && !tickets) {
     dim3 cgrid(nkv, num_seqs);
     if (launch_pdl(decode_combine_kernel<D>, cgrid, dim3(THREADS), 0, stream, (const float*)mid_o,
-                   (const float*)mid_lse, kv_lens, cu_seqlens, seq_list, out, nq, nkv, window, num_splits) !=
-        cudaSuccess)
+                   (const float*)mid_lse, kv_lens, cu_seqlens, seq_list, out, nq, nkv, window, num_splits,
+                   longest_len) != cudaSuccess)
       return Q3_ERR_LAUNCH;
   }
   return Q3_OK;
@@ -564,7 +574,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
                     int max_pages, const int* kv_lens, const int* cu_seqlens, const int* seq_list, void* out,
                     float* mid_o, float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
                     int window, int num_splits, const NewToken& nt, int* error_word, int* tickets,
-                    cudaStream_t stream) {
+                    const int* longest_len, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !kv_lens || !cu_seqlens || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1 || num_splits < 1) return Q3_ERR_ARGUMENT;
   if (nq / nkv > 16 || q_stride % 8) return Q3_ERR_UNSUPPORTED;
@@ -575,7 +585,7 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
     return launch_decode<DIM, FUSED>((const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages,          \
                                      block_table, max_pages, kv_lens, cu_seqlens, seq_list, (bf16*)out, mid_o,    \
                                      mid_lse, num_seqs, nq, nkv, ps, scale, window, num_splits, nt, error_word,   \
-                                     tickets, stream)
+                                     tickets, longest_len, stream)
   switch (D) {
     Q3_DECODE_CASE(64);
     Q3_DECODE_CASE(128);
@@ -597,14 +607,18 @@ int dispatch_decode(const void* q, int q_stride, const void* kpages, const void*
 // them the slices of a sequence and kv head are merged by whichever of their blocks finishes
 // last, without them by a second kernel; the bits are the same.  Calls that share ticket words
 // must not overlap (one stream, or words of their own).
+// num_splits is the slice count of the longest sequence; a shorter one is cut into fewer slices of
+// about the same length.  longest_len: null, or a device pointer to the length of the longest of the
+// `num_seqs` sequences (saves every block working it out from kv_lens).
 Q3_EXPORT int q3_paged_attention_decode(const void* q, int q_stride, const void* kpages, const void* vpages,
                                         const int* block_table, int max_pages, const int* kv_lens,
                                         const int* cu_seqlens, const int* seq_list, void* out, float* mid_o,
                                         float* mid_lse, int num_seqs, int nq, int nkv, int D, int ps, float scale,
-                                        int window, int num_splits, int* tickets, cudaStream_t stream) {
+                                        int window, int num_splits, int* tickets, const int* longest_len,
+                                        cudaStream_t stream) {
   return dispatch_decode<false>(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                 out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, NewToken{},
-                                nullptr, tickets, stream);
+                                nullptr, tickets, longest_len, stream);
 }
 
 // The same, with the work of q3_qk_norm_rope_store folded in: `qkv` is the raw output of the
@@ -621,7 +635,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
                                               float scale, int window, int num_splits, const float* q_w,
                                               const float* k_w, float eps, const float* cos_t, const float* sin_t,
                                               int max_pos, int pairing, int* error_word, int* tickets,
-                                              cudaStream_t stream) {
+                                              const int* longest_len, cudaStream_t stream) {
   if ((cos_t && (!sin_t || max_pos < 1)) || (!q_w) != (!k_w) || pairing < 0 || pairing > 1) return Q3_ERR_ARGUMENT;
   const uintptr_t bits = (uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages | (uintptr_t)q_w | (uintptr_t)k_w |
                          (uintptr_t)cos_t | (uintptr_t)sin_t;
@@ -629,7 +643,7 @@ Q3_EXPORT int q3_paged_attention_decode_fused(const void* qkv, int q_stride, voi
   NewToken nt{q_w, k_w, cos_t, sin_t, (bf16*)kpages, (bf16*)vpages, eps, max_pos, pairing};
   return dispatch_decode<true>(qkv, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens, seq_list,
                                out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window, num_splits, nt,
-                               error_word, tickets, stream);
+                               error_word, tickets, longest_len, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -705,5 +719,5 @@ Q3_EXPORT int q3_paged_attention_decode_no_alloc(const void* q, int q_stride, co
   float* mid_lse = scratch + partials * D; // [num_seqs, nq, num_splits]
   return q3_paged_attention_decode(q, q_stride, kpages, vpages, block_table, max_pages, kv_lens, cu_seqlens,
                                    seq_list, out, mid_o, mid_lse, num_seqs, nq, nkv, D, ps, scale, window,
-                                   num_splits, nullptr, stream);
+                                   num_splits, nullptr, nullptr, stream);
 }

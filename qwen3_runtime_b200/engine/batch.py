@@ -99,6 +99,7 @@ class BatchBuilder:
         sec("ids")[:n] = toks
         sec("pos")[:n] = starts
         sec("kv")[:n] = starts + 1
+        sec("kvmax")[0] = int(starts.max()) + 1
         for g, windowed in enumerate(last["windowed"]):
             bt = None
             for b, e in enumerate(entries):
@@ -185,7 +186,7 @@ class BatchBuilder:
         rows: list[int] = []
         # section offsets inside the int32 buffer (each 4-int aligned => 16-byte aligned)
         off, sections = 0, {}
-        for name, size in (("ids", T), ("pos", T), ("seq", T), ("cu", B + 1), ("kv", B), ("slot", B),
+        for name, size in (("ids", T), ("pos", T), ("seq", T), ("cu", B + 1), ("kv", B), ("kvmax", 1), ("slot", B),
                            ("rows", T), ("single", B), *[(f"bt{g}", B * width) for g in range(n_paged)]):
             sections[name] = (off, size)
             off += _round_up(size, 4)
@@ -232,6 +233,7 @@ class BatchBuilder:
             cu[b + 1] = t
             kv[b] = 1
             slot[b] = scratch_slot
+        sec("kvmax")[0] = kv[:B].max()
         singles = [b for b, n in enumerate(lens) if n == 1] + list(range(B_real, B))
         sec("single")[:len(singles)] = singles
         if all_rows:
@@ -264,7 +266,7 @@ class BatchBuilder:
         return StepContext(
             num_tokens=T, num_seqs=B,
             token_ids=dsec("ids"), positions=dsec("pos"), token_seq=dsec("seq"), cu_seqlens=dsec("cu"),
-            kv_lens=dsec("kv"), state_slots=dsec("slot"),
+            kv_lens=dsec("kv"), kv_longest=dsec("kvmax"), state_slots=dsec("slot"),
             block_tables=[dsec(f"bt{g}").view(B, width) for g in range(n_paged)],
             logit_rows=dsec("rows", R), num_logit_rows=R,
             max_query_len=max(lens, default=1), max_kv_len=int(kv[:B].max()),

@@ -70,11 +70,11 @@ _SIGNATURES = {
     "attention_decode": {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_float, c_int, c_int, c_void_p, c_void_p],
+                                      c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "q3_paged_attention_decode_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float,
-                                            c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                                            c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     },
     "attention_prefill": {
         "q3_paged_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -340,7 +340,7 @@ class CudaOps:
                 v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens, cu_seqlens=step.cu_seqlens,
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
                 max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step,
-                num_splits=decode_slices)
+                num_splits=decode_slices, longest=getattr(step, "kv_longest", None))
         if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
@@ -417,60 +417,63 @@ class CudaOps:
     TICKETS = 1 << 16  # ticket words for the merge by the last block: sequences x kv heads of one launch
     DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
 
-    def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 128,
-                      total_kv_len: int | None = None) -> int:
-        """How many slices the longest sequence's keys are cut into (the kernel cuts a shorter one
-        into fewer slices of about the same length, so a batch whose lengths add up to
-        ``total_kv_len`` counts as ``total_kv_len / max_kv_len`` sequences of the longest length;
-        without it, all are taken to be that long).  The cost of a choice, in units of the time one
-        key takes to stream when every block slot (3 x SMs) is busy: while all blocks fit the slots,
-        keys per slice + 12 per slice (the last block of a pair merges them); beyond that, waves x
-        (keys per slice + 384), the 384 being what a block pays besides its keys (lengths, block
-        table and first tile at the start, the warps' merge and the ticket at the end), which a full
-        machine no longer hides; waves are whole up to six and blocks / slots + 1/2 beyond (blocks of
-        equal length start and end together at first and drift apart later).  Slices are at least
-        192 keys long, 64 with at most 32 (sequence, kv head) pairs.  The constants are fitted to a
-        sweep of 1..128 sequences x 256..16384 keys x 1..64 slices on a B200 (8 kv heads of 128,
-        ``python -m qwen3_runtime_b200.ops.tune decode_splits``): the choice is within 0.6 % of the
-        best one on average and 13 % at worst.  The reference's rule for an RTX 4090 has the same
-        inputs (qwen3_runtime/kernels/triton_decode.py:122-133)."""
-        max_kv_len = max(1, max_kv_len)
-        seqs = num_seqs if total_kv_len is None else min(num_seqs, max(1.0, total_kv_len / max_kv_len))
-        pairs = max(1.0, seqs * num_kv_heads)
-        slots = self.DECODE_BLOCKS_PER_SM * self.SM_COUNT
-        per_key = head_dim / 128.0  # a key of a smaller head streams faster; the fixed parts do not
-        fixed, per_slice = 384.0 / per_key, 12.0 / per_key
-        floor = 64 if pairs <= 32 else 192
-        best, best_cost = 1, None
-        for splits in range(1, max(1, min(64, max_kv_len // 64)) + 1):
-            per = -(-(-(-max_kv_len // splits)) // 64) * 64
-            if splits > 1 and per < floor:
-                break
-            blocks = math.ceil(pairs * splits)
-            if blocks <= slots:
-                cost = per + per_slice * splits
-            else:
-                waves = blocks / slots
-                waves = -(-blocks // slots) if waves <= 6 else waves + 0.5
-                cost = waves * (per + fixed) + per_slice * splits
-            if best_cost is None or cost < best_cost:
-                best, best_cost = splits, cost
-        return best
+    def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 128) -> int:
+        """How many slices each sequence's keys are cut into when all that is known is their number
+        and an upper bound of their length (a captured step without :meth:`decode_slices_for`)."""
+        return self._decode_slices([-(-max(1, max_kv_len) // 64)] * max(1, num_seqs), num_kv_heads, head_dim)
 
     def decode_slices_for(self, kv_lens: list[int], num_kv_heads: int, head_dim: int, window: int | None) -> int:
-        """:meth:`decode_splits` for a decode step whose sequences have these lengths (asked once per
-        step by the attention parts' chooser; answers are kept by the sizes the model looks at)."""
-        if window:
-            kv_lens = [min(n, int(window) + 63) for n in kv_lens]
-        longest, total = max(kv_lens, default=1), sum(kv_lens)
-        key = (len(kv_lens), num_kv_heads, head_dim, -(-longest // 64), -(-total // 64))
+        """Into how many slices the split-KV kernel cuts the longest of these sequences (asked once
+        per decode step by the attention parts' chooser; answers are kept by the sequences' lengths
+        in tiles of 64 keys)."""
+        cap = (int(window) + 63) if window else None
+        tiles = tuple(-(-(n if cap is None or n < cap else cap) // 64) for n in kv_lens)
+        key = (num_kv_heads, head_dim, tiles)
         slices = self._slices_cache.get(key)
         if slices is None:
             if len(self._slices_cache) > 8192:
                 self._slices_cache.clear()
-            slices = self._slices_cache[key] = self.decode_splits(len(kv_lens), num_kv_heads, 64 * key[3], head_dim,
-                                                                  total_kv_len=64 * key[4])
+            slices = self._slices_cache[key] = self._decode_slices(tiles, num_kv_heads, head_dim)
         return slices
+
+    def _decode_slices(self, tiles, num_kv_heads: int, head_dim: int) -> int:
+        """The slice count for sequences of ``tiles`` x 64 keys.  With ``s`` slices the longest
+        sequence is cut into slices of ``ceil(longest / s)`` tiles and every other sequence into as
+        many slices of that length as it needs (the kernel's rule), which gives the number of
+        blocks.  The cost of a choice, in units of the time one key takes to stream when every block
+        slot (3 x SMs) is busy: while all blocks fit the slots, keys per slice + 12 per slice (the
+        last block of a pair merges them); beyond that, waves x (keys per slice + 384), the 384 being
+        what a block pays besides its keys (lengths, block table and first tile at the start, the
+        warps' merge and the ticket at the end), which a full machine no longer hides; waves are
+        whole up to six and blocks / slots + 1/2 beyond (blocks of equal length start and end
+        together at first and drift apart later).  Slices are at least 192 keys long, 64 with at most
+        32 (sequence, kv head) pairs.  The constants are fitted to a sweep of 1..128 sequences x
+        256..16384 keys x 1..64 slices on a B200 (8 kv heads of 128,
+        ``python -m qwen3_runtime_b200.ops.tune decode_splits``): the choice is within 0.6 % of the
+        best one on average and 13 % at worst for sequences of one length, and within a few percent
+        for the mixed batches tried.  The reference's rule for an RTX 4090 looks at the number of
+        sequences and the longest one (qwen3_runtime/kernels/triton_decode.py:122-133)."""
+        import numpy as np
+
+        t = np.asarray(tiles, dtype=np.int64)
+        t = t[t > 0]
+        if t.size == 0:
+            return 1
+        longest = int(t.max())
+        slots = self.DECODE_BLOCKS_PER_SM * self.SM_COUNT
+        per_key = head_dim / 128.0  # a key of a smaller head streams faster; the fixed parts do not
+        fixed, per_slice = 384.0 / per_key, 12.0 / per_key
+        floor = 1 if t.size * num_kv_heads <= 32 else 3  # tiles
+        counts = np.arange(1, min(64, longest) + 1)
+        slice_tiles = -(-longest // counts)
+        counts = counts[(slice_tiles >= floor) | (counts == 1)]
+        slice_tiles = -(-longest // counts)
+        blocks = num_kv_heads * (-(-t[None, :] // slice_tiles[:, None])).sum(axis=1)
+        per = 64.0 * slice_tiles
+        waves = blocks / slots
+        waves = np.where(waves <= 6, np.ceil(waves), waves + 0.5)
+        cost = np.where(blocks <= slots, per, waves * (per + fixed)) + per_slice * counts
+        return int(counts[int(np.argmin(cost))])
 
     def decode_new_token_ok(self, qkv, *, num_heads, num_kv_heads, head_dim, cos, q_weight, k_weight) -> bool:
         """Whether the split-KV kernel can make q, k and v of the newest token itself (per-head
@@ -483,13 +486,16 @@ class CudaOps:
     def paged_attention_decode(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages,
                                block_table, kv_lens, cu_seqlens, out, page_size, scale, window, num_seqs,
                                max_kv_len, seq_list=None, num_splits=None, new_token=None, step=None,
-                               merge_kernel=False):
+                               merge_kernel=False, longest=None):
         """Split-KV attention for sequences that bring one token each (csrc/attention_decode.cu).
         ``new_token`` (q_weight, k_weight, eps, cos, sin, optionally pairing): ``q`` is the raw q/k/v
         projection and the kernel also does the work of :meth:`qk_norm_rope_store` for the newest
         position of each sequence, ``kv_lens - 1``.  The slices of a sequence and kv head are merged
         by whichever of their blocks finishes last (a ticket word per pair); ``merge_kernel=True``
-        asks for the second kernel that callers without ticket words get (the bits are the same)."""
+        asks for the second kernel that callers without ticket words get (the bits are the same).
+        ``num_splits`` is the slice count of the longest sequence (a shorter one gets fewer slices of
+        about the same length); ``longest``: a device int32 holding the longest of the sequences'
+        lengths, when the caller has it (else every block works it out from ``kv_lens``)."""
         if out.dtype != torch.bfloat16 or head_dim not in (64, 128, 256) or num_heads // num_kv_heads > 16:
             raise KernelError("paged_attention_decode: bfloat16, head_dim 64/128/256 and groups of at most 16 only")
         if window:
@@ -517,13 +523,13 @@ class CudaOps:
                        num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
                        splits, _ptr(new_token["q_weight"]), _ptr(new_token["k_weight"]), float(new_token["eps"]),
                        _ptr(cos), _ptr(sin), cos.shape[0] if cos is not None else 0,
-                       self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets))
+                       self.PAIRINGS[new_token.get("pairing", "half")], err, _ptr(tickets), _ptr(longest))
             return out
         self._call("attention_decode", "q3_paged_attention_decode", "paged_attention_decode",
                    _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                    _ptr(kv_lens), _ptr(cu_seqlens), _ptr(seq_list), _ptr(out), _ptr(mid_o), _ptr(mid_lse),
                    num_seqs, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits,
-                   _ptr(tickets))
+                   _ptr(tickets), _ptr(longest))
         return out
 
     # ---- matrix products ----------------------------------------------------------------

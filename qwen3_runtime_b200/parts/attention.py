@@ -135,7 +135,7 @@ class PagedAttention(Part):
                 max_kv_len=width * cache.page_size or step.max_kv_len,
                 new_token=dict(q_weight=self.q_norm_weight, k_weight=self.k_norm_weight, eps=eps, cos=cos, sin=sin,
                                pairing=self.pairing),
-                num_splits=slices, step=step)
+                num_splits=slices, longest=step.kv_longest, step=step)
             return self._project_out(ctx_out)
         ops.qk_norm_rope_store(
             qkv, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,

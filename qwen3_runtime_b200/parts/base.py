@@ -60,6 +60,7 @@ class StepContext:
     max_query_len: int  # host copies of batch extremes, for kernel choice
     max_kv_len: int
     decode_only: bool  # every sequence brings exactly one token
+    kv_longest: torch.Tensor | None = None  # [1] the largest of kv_lens, on the device
     single_seqs: torch.Tensor | None = None  # [num_single] sequences that bring exactly one token
     num_single: int = 0
     # host copies (lists) for parts that need them without a device read

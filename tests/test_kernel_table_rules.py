@@ -11,12 +11,18 @@ class Table:
 
     DECODE_BLOCKS_PER_SM = 3
     SM_COUNT = 148
-    _slices_cache: dict = {}
+
+    def __init__(self):
+        self._slices_cache = {}
+
     decode_splits = CudaOps.decode_splits
+    decode_slices_for = CudaOps.decode_slices_for
+    _decode_slices = CudaOps._decode_slices
+    _tcgen05_plan = CudaOps._tcgen05_plan
 
 
-def slices(num_seqs, kv_heads, longest, head_dim=128, total=None):
-    return Table().decode_splits(num_seqs, kv_heads, longest, head_dim, total_kv_len=total)
+def slices(num_seqs, kv_heads, longest, head_dim=128):
+    return Table().decode_splits(num_seqs, kv_heads, longest, head_dim)
 
 
 def test_slice_counts_of_decode_attention():
@@ -27,28 +33,32 @@ def test_slice_counts_of_decode_attention():
     assert slices(64, 8, 768) == 1 and slices(64, 8, 4096) in (4, 5) and slices(32, 8, 1024) == 1
     # never slices of less than 64 keys, and none at all for a handful of keys
     rnd = random.Random(0)
-    for _ in range(2000):
+    for _ in range(500):
         B, L, D = rnd.randint(1, 300), rnd.randint(1, 40000), rnd.choice([64, 128, 256])
         s = slices(B, rnd.choice([1, 2, 4, 8]), L, D)
         assert 1 <= s <= 64 and (s == 1 or -(-L // s) >= 33), (B, L, D, s)
     assert slices(5, 8, 63) == 1 and slices(1, 1, 1) == 1
 
 
-def test_a_batch_of_mixed_lengths_counts_as_fewer_sequences_of_the_longest():
-    # 48 sequences of 4096 keys fill the slots with one block per pair; when they add up to
-    # half of that, the longest ones can be cut in two
-    assert slices(48, 8, 4096) == 1
-    assert slices(48, 8, 4096, total=24 * 4096) == 2
-    assert slices(48, 8, 4096, total=48 * 4096) == 1
-    # the answer for a list of lengths; a window bounds what a sequence counts for
+def test_a_batch_of_mixed_lengths_is_cut_by_its_own_block_count():
+    table = Table()
+    # 48 sequences of 4096 keys fill the slots with one block per pair
+    assert table.decode_slices_for([4096] * 48, 8, 128, None) == 1
+    # one long sequence among short ones: the long one is cut until the slots are full; the short
+    # ones stay whole (the kernel gives a shorter sequence fewer slices)
+    assert table.decode_slices_for([4096] + [200] * 47, 8, 128, None) == 8
+    # lengths spread over 64..4096: slices of about a thousand keys
+    rnd = random.Random(1)
+    assert table.decode_slices_for([rnd.randint(64, 4096) for _ in range(48)], 8, 128, None) in (3, 4, 5, 6)
+    # the same lengths, the same answer as for one length; a window bounds what a sequence counts for
+    assert table.decode_slices_for([4100] * 8, 8, 128, None) == slices(8, 8, 4100) == 6
     lens = [4096] * 3 + [100] * 45
-    assert CudaOps.decode_slices_for(Table(), lens, 8, 128, None) == slices(48, 8, 4096, total=sum(lens))
-    assert CudaOps.decode_slices_for(Table(), lens, 8, 128, 200) == CudaOps.decode_slices_for(
-        Table(), [263] * 3 + [100] * 45, 8, 128, None)
+    assert table.decode_slices_for(lens, 8, 128, 200) == table.decode_slices_for([263] * 3 + [100] * 45, 8, 128, None)
+    assert table.decode_slices_for([], 8, 128, None) == 1
 
 
 def test_which_tcgen05_kernel_a_fused_swiglu_product_goes_to():
-    plan = lambda M, I: CudaOps._tcgen05_plan(Table, M, I)  # noqa: E731
+    plan = Table()._tcgen05_plan
     # 1280 tokens x 9728: five token tiles of 256 on pairs; 640: five tiles of 128 on single SMs
     # (three tiles of 256 would leave a quarter of the last one and most of a fourth round empty)
     assert plan(1280, 9728)[0] and not plan(640, 9728)[0]

@@ -402,14 +402,15 @@ def decode_problem(nq, nkv, D, ps, lens, seed):
 MERGE_KERNEL = False  # set by the decode_loader fixture: the slices are merged by a second kernel
 
 
-def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list=None, out=None, merge_kernel=None):
+def run_decode(ops, pr, nq, nkv, D, ps, lens, window=None, splits=None, seq_list=None, out=None, merge_kernel=None,
+               longest=None):
     out = out if out is not None else torch.zeros((pr["T"], nq * D), dtype=torch.bfloat16, device="cuda")
     n = len(lens) if seq_list is None else seq_list.numel()
     ops.paged_attention_decode(pr["q"], pr["q"].stride(0), num_heads=nq, num_kv_heads=nkv, head_dim=D,
                                k_pages=pr["k"], v_pages=pr["v"], block_table=pr["bt"], kv_lens=pr["kv_lens"],
                                cu_seqlens=pr["cu"], out=out, page_size=ps, scale=1 / math.sqrt(D), window=window,
                                num_seqs=n, max_kv_len=max(lens), seq_list=seq_list, num_splits=splits,
-                               merge_kernel=MERGE_KERNEL if merge_kernel is None else merge_kernel)
+                               merge_kernel=MERGE_KERNEL if merge_kernel is None else merge_kernel, longest=longest)
     return out
 
 
@@ -453,6 +454,17 @@ def test_decode_attention_merge_by_last_block_gives_the_bits_of_the_merge_kernel
             for _ in range(3):
                 got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits, merge_kernel=False)
                 assert torch.equal(got, want), (splits, window)
+            # the longest length handed in by the caller: the same slices as when the blocks find it
+            # (with a window the blocks look for the longest visible span, which need not be the
+            # longest sequence's: the cut may differ by a tile then, the result only by rounding)
+            known = torch.tensor([max(lens)], dtype=torch.int32, device="cuda")
+            for merge_kernel in (False, True):
+                got = run_decode(ops, pr, nq, nkv, D, ps, lens, window=window, splits=splits,
+                                 merge_kernel=merge_kernel, longest=known)
+                if window is None:
+                    assert torch.equal(got, want), (splits, window, "longest given")
+                else:
+                    close(got, want, torch.bfloat16, "longest given, window", bf16_tol=1e-2)
             assert not bool(ops._tickets.any())
 
 
