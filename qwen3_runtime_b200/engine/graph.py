@@ -43,6 +43,10 @@ class DecodeGraphs:
         self.sizes = sorted(int(s) for s in batch_sizes)
         self.captured: dict[tuple, _Captured] = {}
         self.replays = 0
+        # one memory pool for all captured steps: they never run at the same time (one stream), so
+        # the buffers inside one may be the buffers inside another; only what a capture hands out
+        # (its logits) stays its own
+        self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
 
     def try_run(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """Logits for the entries that want them (an empty tensor when none does), or None
@@ -107,7 +111,7 @@ class DecodeGraphs:
         was_enabled = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(cap.graph):
+            with torch.cuda.graph(cap.graph, pool=self.pool):
                 cap.logits = r.model.forward(step, r.storage)
         finally:
             if was_enabled:

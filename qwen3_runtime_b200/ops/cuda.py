@@ -379,12 +379,14 @@ class CudaOps:
                            step.num_seqs, work, num_heads, num_kv_heads, head_dim, page_size, float(scale),
                            int(window or 0), 1)
             if step.num_single:
-                longest = max(kv for kv, n in zip(step.host_kv_lens, qlens) if n == 1)
+                singles = [kv for kv, n in zip(step.host_kv_lens, qlens) if n == 1]
+                longest = max(singles)
                 self.paged_attention_decode(
                     q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                     k_pages=k_pages, v_pages=v_pages, block_table=block_table, kv_lens=step.kv_lens,
                     cu_seqlens=step.cu_seqlens, out=out, page_size=page_size, scale=scale, window=window,
-                    num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs, step=step)
+                    num_seqs=step.num_single, max_kv_len=longest, seq_list=step.single_seqs, step=step,
+                    num_splits=self.decode_slices_for(singles, num_kv_heads, head_dim, window))
             return out
         if self.timing is not None and step is not None:
             self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out))
