@@ -417,7 +417,9 @@ class CudaOps:
 
     SM_COUNT = 148  # of a B200; replaced by the device's own count when the table is built
     TICKETS = 1 << 16  # ticket words for the merge by the last block: sequences x kv heads of one launch
-    DECODE_BLOCKS_PER_SM = 3  # of the split-KV kernel (registers and shared memory both allow three)
+    # blocks of the split-KV kernel that an SM holds, by head size (registers allow 4 / 3 / 2,
+    # shared memory 6 / 3 / 1)
+    DECODE_BLOCKS_PER_SM = {64: 4, 128: 3, 256: 1}
 
     def decode_splits(self, num_seqs: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 128) -> int:
         """How many slices each sequence's keys are cut into when all that is known is their number
@@ -443,7 +445,7 @@ class CudaOps:
         sequence is cut into slices of ``ceil(longest / s)`` tiles and every other sequence into as
         many slices of that length as it needs (the kernel's rule), which gives the number of
         blocks.  The cost of a choice, in units of the time one key takes to stream when every block
-        slot (3 x SMs) is busy: while all blocks fit the slots, keys per slice + 12 per slice (the
+        slot (3 per SM at head size 128) is busy: while all blocks fit the slots, keys per slice + 12 per slice (the
         last block of a pair merges them); beyond that, waves x (keys per slice + 384), the 384 being
         what a block pays besides its keys (lengths, block table and first tile at the start, the
         warps' merge and the ticket at the end), which a full machine no longer hides; waves are
@@ -462,9 +464,10 @@ class CudaOps:
         if t.size == 0:
             return 1
         longest = int(t.max())
-        slots = self.DECODE_BLOCKS_PER_SM * self.SM_COUNT
-        per_key = head_dim / 128.0  # a key of a smaller head streams faster; the fixed parts do not
-        fixed, per_slice = 384.0 / per_key, 12.0 / per_key
+        slots = self.DECODE_BLOCKS_PER_SM.get(head_dim, 3) * self.SM_COUNT
+        # a key of a smaller head streams faster, what a block pays besides its keys stays; merging a
+        # slice costs in proportion to the head size, like a key
+        fixed, per_slice = 384.0 * 128.0 / head_dim, 12.0
         floor = 1 if t.size * num_kv_heads <= 32 else 3  # tiles
         counts = np.arange(1, min(64, longest) + 1)
         slice_tiles = -(-longest // counts)

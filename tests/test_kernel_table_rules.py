@@ -9,7 +9,7 @@ from qwen3_runtime_b200.ops.cuda import CudaOps
 class Table:
     """What the rules read from a kernel table of a B200."""
 
-    DECODE_BLOCKS_PER_SM = 3
+    DECODE_BLOCKS_PER_SM = CudaOps.DECODE_BLOCKS_PER_SM
     SM_COUNT = 148
 
     def __init__(self):
