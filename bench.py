@@ -17,8 +17,8 @@ step: every live request gets one new token.  It prints ONE JSON line:
                 the device->host read of the new token ids (the engine runs ahead: a step's
                 ids are read while the next step, fed from the device, already runs; every
                 step's inputs are still copied in and every step's ids still read out).
-                Between the prefill of the prompts and the W warm-up steps both arms pause for
-                half a second: right after a prefill at the power cap decode steps run up to
+                Between the prefill of the prompts and the W warm-up steps both arms decode 40
+                untimed steps: right after a prefill at the power cap decode steps run up to
                 15 % slower for some 40 ms, which is not what a step costs;
 * ``prefill``   one 2,048-token prompt through the step function;
 * ``roofline``  bytes a decode step has to read (every weight once + the live requests'
@@ -102,7 +102,7 @@ def peaks() -> dict:
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_burst=1590.0, source="fallback")
 
 
-E2E_SETTLE_S = 0.5  # pause between the prompts' prefill and the end-to-end decode steps (e2e_steps)
+E2E_SETTLE_STEPS = 40  # untimed decode steps between the prompts' prefill and the W warm-up steps (e2e_steps)
 
 
 class ClockSampler:
@@ -184,7 +184,7 @@ def flat_config(cfg, *, model: str, batch, seq_len, layers_full: int, cuda_graph
         "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
         "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
         "page_size": PAGE, "cuda_graph": bool(cuda_graph), "l2": "inputs (GBs of weights) larger than L2",
-        "run_ahead": bool(run_ahead), "build_s": round(build_s, 1), "e2e_pause_after_prefill_s": E2E_SETTLE_S,
+        "run_ahead": bool(run_ahead), "build_s": round(build_s, 1), "e2e_steps_after_prefill": E2E_SETTLE_STEPS,
     }
 
 
@@ -362,7 +362,7 @@ def run_ours(args) -> dict:
     K, W = args.steps, args.warmup
     clocks = ClockSampler().start()
     max_b = max(BATCH, 64)
-    tokens_needed = max_b * (args.context + 3 * K + W + 64) + PREFILL_TOKENS + 64
+    tokens_needed = max_b * (args.context + 3 * K + W + E2E_SETTLE_STEPS + 64) + PREFILL_TOKENS + 64
     engine, model, cfg, ops, build_s = build_ours("4b", args, max_num_seqs=max_b, budget=8192,
                                                   tokens_needed=tokens_needed)
     rt = engine.runtime
@@ -447,7 +447,8 @@ def e2e_steps(engine, torch, batch: int, context: int, K: int, W: int, rand_ids,
     """Decode steps through ``engine.step()``: host token ids in, sampled ids out, every step.
     Works for this engine and for the reference's (the same three calls)."""
     prompts = [rand_ids(context) for _ in range(batch)]
-    rids = [engine.add_request(p, max_tokens=W + K + 8, sampling=make_sampling()) for p in prompts]
+    rids = [engine.add_request(p, max_tokens=E2E_SETTLE_STEPS + W + K + 8, sampling=make_sampling())
+            for p in prompts]
     produced = {rid: 0 for rid in rids}
 
     def step():
@@ -461,11 +462,10 @@ def e2e_steps(engine, torch, batch: int, context: int, K: int, W: int, rand_ids,
     while any(produced[r] < 1 for r in rids):
         step()  # untimed: the prompts are prefilled in portions of the token budget
     # the prefill of batch x context tokens runs at the power cap; the decode steps right after it
-    # are up to 15 % slower for some 40 ms while the clocks come back.  Both arms pause here, so
-    # that the timed steps are steady-state decode steps.
-    torch.cuda.synchronize()
-    time.sleep(E2E_SETTLE_S)
-    for _ in range(W):
+    # are up to 15 % slower for some 40 ms while the clocks come back (and an idle pause instead
+    # lets them fall).  Both arms decode E2E_SETTLE_STEPS untimed steps first, so that the timed
+    # steps are steady-state decode steps.
+    for _ in range(E2E_SETTLE_STEPS + W):
         step()
     ahead_before = getattr(engine, "num_run_ahead", 0)
     torch.cuda.synchronize()
@@ -492,7 +492,7 @@ def e2e_ours(engine, args, rand_ids, torch, batch: int = BATCH, context: int | N
     r = e2e_steps(engine, torch, batch, context, K, W, rand_ids, SamplingParams)
     # per step: ids, positions, sequence index, logit rows (4 B each per request), cu_seqlens,
     # kv_lens, slots, and one block-table row per request; back: one int32 token id per request
-    width = 1 << ((context + W + K + 8) // PAGE).bit_length()
+    width = 1 << ((context + E2E_SETTLE_STEPS + W + K + 8) // PAGE).bit_length()
     h2d = 4 * (4 * batch + (batch + 1) + 2 * batch + batch * width)
     return dict(value=round(r["tokens"] / r["seconds"], 1), unit="tokens/s",
                 ms_per_step=round(r["seconds"] * 1000.0 / K, 4), h2d_bytes_per_step=h2d,
@@ -606,7 +606,8 @@ def run_32b_ours(args, pk) -> dict:
 
     K, W = args.steps, args.warmup
     context = 1024
-    tokens = 32 * (context + 2 * K + W + 64) + 8 * (context + K + W + 64) + PREFILL_TOKENS + 64
+    tokens = (32 * (context + 2 * K + W + 64) + 8 * (context + K + W + E2E_SETTLE_STEPS + 64)
+              + PREFILL_TOKENS + 64)
     engine, model, cfg, ops, build_s = build_ours("32b", args, max_num_seqs=32, budget=8192, tokens_needed=tokens)
     rt = engine.runtime
     cost = model_cost(cfg)
@@ -677,7 +678,8 @@ def run_reference(args) -> dict:
 
         K, W = args.steps, args.warmup
         engine, cfg, write_s, _folder = _reference_engine(args, "4b", max_num_seqs=BATCH, budget=8192,
-                                                          tokens_needed=BATCH * (args.context + K + W + 64))
+                                                          tokens_needed=BATCH * (args.context + K + W
+                                                                                 + E2E_SETTLE_STEPS + 64))
         from qwen3_runtime.sampling_params import SamplingParams as RefSamplingParams
 
         clocks = ClockSampler()
